@@ -1,0 +1,193 @@
+/*
+ * sushiblas_cuda.h -- C ABI of the B200 (sm_100a) backend for the SushiBLAS fp32 GEMM path.
+ *
+ * This is the boundary the C++ Engine dispatches to.  Its GEMM entry points take the
+ * argument list of the reference's internal dispatcher
+ *     gemm_dispatch<float>(queue, layout, transA, transB, m, n, k, alpha,
+ *                          a, lda, str_a, b, ldb, str_b, beta, c, ldc, str_c, batch, deps)
+ * (src/ops/blas/level3/gemm.cpp:44-51), i.e. of the two oneMKL calls it forwards to
+ * (gemm.cpp:58 gemm_batch, gemm.cpp:63 gemm): element-typed pointers, leading dimensions
+ * and batch strides in elements, 64-bit sizes.  The sycl::queue becomes a context handle
+ * plus a device index; event dependencies become stream order.
+ *
+ * Conventions
+ *  - plain C types only; every function returns SUSHI_CUDA_OK (0) or a negative code;
+ *    nothing throws across this boundary; sushi_cuda_last_error() gives the text;
+ *  - matrices are ROW-MAJOR (the column-major case of gemm.cpp:66-78 is served by the
+ *    caller swapping operands: C^T = op(B)^T * op(A)^T);
+ *  - GEMM pointers are device pointers unless the function name ends in _host;
+ *  - GEMM calls are asynchronous on the context's stream of that device; call
+ *    sushi_cuda_sync() before reading results on the host;
+ *  - there is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef SUSHIBLAS_CUDA_H
+#define SUSHIBLAS_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define SUSHI_CUDA_API __declspec(dllexport)
+#else
+#define SUSHI_CUDA_API __attribute__((visibility("default")))
+#endif
+
+typedef struct sushi_cuda_ctx sushi_cuda_ctx;
+
+enum sushi_cuda_status
+{
+    SUSHI_CUDA_OK = 0,
+    SUSHI_CUDA_ERR_INVALID_ARG = -1,    /* bad size, leading dimension, pointer or index   */
+    SUSHI_CUDA_ERR_CUDA = -2,           /* a CUDA runtime / driver call failed             */
+    SUSHI_CUDA_ERR_NO_DEVICE = -3,      /* no usable CUDA device                           */
+    SUSHI_CUDA_ERR_OOM = -4,            /* device or pinned-host allocation failed         */
+    SUSHI_CUDA_ERR_KERNEL_TIMEOUT = -5, /* a bounded in-kernel wait expired (see _sync)    */
+    SUSHI_CUDA_ERR_COMM = -6,           /* NCCL missing or a collective failed             */
+    SUSHI_CUDA_ERR_UNSUPPORTED = -7     /* request outside what this build supports        */
+};
+
+/* Kernel family used by the GEMM entry points. */
+enum sushi_cuda_gemm_variant
+{
+    SUSHI_GEMM_AUTO = 0,   /* tensor-core 3xTF32 when the problem can fill its tiles, else SIMT */
+    SUSHI_GEMM_SIMT = 1,   /* fp32 FFMA tiles (exact fp32 products, fp32 accumulation)          */
+    SUSHI_GEMM_TC3X = 2    /* tcgen05 3xTF32 (hi/lo split, fp32 accumulation in TMEM)           */
+};
+
+/* ---- context ------------------------------------------------------------------------
+ * Replaces the sycl::queue / RuntimeContext pair the reference passes around
+ * (include/SushiRuntime/execution/runtime_context.hpp:42-96, get_queue(xpu_index)).
+ * devices == NULL or n_devices == 0 selects device 0 (or $SUSHI_CUDA_DEVICE). The `dev`
+ * argument of the other calls indexes this list.                                         */
+SUSHI_CUDA_API int sushi_cuda_device_count(int* count);
+SUSHI_CUDA_API int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx** out);
+SUSHI_CUDA_API int sushi_cuda_destroy(sushi_cuda_ctx* ctx);
+SUSHI_CUDA_API const char* sushi_cuda_last_error(sushi_cuda_ctx* ctx);
+
+/* Waits for everything queued on the device's stream (RuntimeContext::wait_all,
+ * runtime_context.hpp:90) and reports a kernel-side bounded-wait expiry, if any.          */
+SUSHI_CUDA_API int sushi_cuda_sync(sushi_cuda_ctx* ctx, int dev);
+
+/* Run on a caller-owned stream (a cudaStream_t passed as void*; NULL restores the
+ * context's own stream).  Lets a host framework time or order the calls with its events. */
+SUSHI_CUDA_API int sushi_cuda_set_stream(sushi_cuda_ctx* ctx, int dev, void* cuda_stream);
+SUSHI_CUDA_API int sushi_cuda_get_stream(sushi_cuda_ctx* ctx, int dev, void** cuda_stream);
+
+SUSHI_CUDA_API int sushi_cuda_set_gemm_variant(sushi_cuda_ctx* ctx, int variant);
+/* Number of kernels this context has launched so far (all devices). */
+SUSHI_CUDA_API int sushi_cuda_launch_count(sushi_cuda_ctx* ctx, int64_t* launches);
+
+/* Optional per-kernel timing for measurement harnesses: when enabled, every GEMM call brackets
+ * its operand pre-pass and its main kernel with CUDA events on the launching stream.
+ * _read() waits for the stream, returns the accumulated device milliseconds and launch counts
+ * since the last read and resets them.  Off by default (the reference has no profiler; its
+ * TaskMetadata names exist "for profilers", include/SushiRuntime/graph/task_types.hpp:90-129). */
+SUSHI_CUDA_API int sushi_cuda_kernel_timing_enable(sushi_cuda_ctx* ctx, int enable);
+SUSHI_CUDA_API int sushi_cuda_kernel_timing_read(sushi_cuda_ctx* ctx, int dev,
+                                                 double* gemm_ms, int64_t* gemm_launches,
+                                                 double* prepass_ms, int64_t* prepass_launches);
+
+/* ---- storage ------------------------------------------------------------------------
+ * Replace USMAllocator::allocate / deallocate (include/SushiRuntime/memory/
+ * usm_allocator.hpp:43-71) for AllocStrategy::DEVICE (cudaMalloc) and HOST (pinned), and
+ * the queue.memcpy staging the reference uses for DEVICE tensors (src/io.cpp:73-78).
+ * Copies are asynchronous on the device's stream.                                         */
+SUSHI_CUDA_API int sushi_cuda_malloc(sushi_cuda_ctx* ctx, int dev, size_t bytes, void** ptr);
+SUSHI_CUDA_API int sushi_cuda_free(sushi_cuda_ctx* ctx, int dev, void* ptr);
+SUSHI_CUDA_API int sushi_cuda_host_alloc(sushi_cuda_ctx* ctx, size_t bytes, void** ptr);
+SUSHI_CUDA_API int sushi_cuda_host_free(sushi_cuda_ctx* ctx, void* ptr);
+SUSHI_CUDA_API int sushi_cuda_memcpy_h2d(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes);
+SUSHI_CUDA_API int sushi_cuda_memcpy_d2h(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes);
+SUSHI_CUDA_API int sushi_cuda_memcpy_d2d(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes);
+SUSHI_CUDA_API int sushi_cuda_memset(sushi_cuda_ctx* ctx, int dev, void* dst, int byte, size_t bytes);
+
+/* ---- GEMM ---------------------------------------------------------------------------
+ * C <- alpha * op(A) * op(B) + beta * C, row-major, op(X) = X or X^T.
+ * Replaces oneapi::mkl::blas::row_major::gemm (call site gemm.cpp:63).
+ * C is not read when beta == 0.  lda >= (transA ? m : k), ldb >= (transB ? k : n),
+ * ldc >= n (each at least 1).                                                             */
+SUSHI_CUDA_API int sushi_cuda_sgemm(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                    int64_t m, int64_t n, int64_t k, float alpha,
+                                    const float* a, int64_t lda,
+                                    const float* b, int64_t ldb,
+                                    float beta, float* c, int64_t ldc);
+
+/* Batch i uses a + i*stride_a, b + i*stride_b, c + i*stride_c.
+ * Replaces oneapi::mkl::blas::row_major::gemm_batch (call site gemm.cpp:58).              */
+SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                    int64_t m, int64_t n, int64_t k, float alpha,
+                                                    const float* a, int64_t lda, int64_t stride_a,
+                                                    const float* b, int64_t ldb, int64_t stride_b,
+                                                    float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                    int64_t batch);
+
+/* Same operation on HOST buffers (the SHARED / HOST strategies of the reference, whose
+ * tensors callers fill and read on the host: tests/test_common.hpp:36-58): stages A, B
+ * (and C when beta != 0) to the device, runs the GEMM, stages C back; all queued on the
+ * stream.  Buffers should be pinned (sushi_cuda_host_alloc) for the copies to overlap.    */
+SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched_host(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                         int64_t m, int64_t n, int64_t k, float alpha,
+                                                         const float* a, int64_t lda, int64_t stride_a,
+                                                         const float* b, int64_t ldb, int64_t stride_b,
+                                                         float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                         int64_t batch);
+
+/* Bytes of device scratch the 3xTF32 path would use for this problem (0 for SIMT). The
+ * context grows its scratch on demand; sushi_cuda_reserve_workspace() does it up front so
+ * that no allocation happens inside a timed or latency-critical region.                   */
+SUSHI_CUDA_API int sushi_cuda_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, size_t* bytes);
+SUSHI_CUDA_API int sushi_cuda_reserve_workspace(sushi_cuda_ctx* ctx, int dev, size_t bytes);
+
+/* ---- multi-GPU layer (one process per GPU) --------------------------------------------
+ * No counterpart in the reference (it has no collective call site); the partitioning
+ * follows the independence of C's row blocks / batch entries in the calls above.
+ * sushi_cuda_partition(): contiguous block [first, first+count) of `total` owned by
+ * `rank` of `nranks` (block size ceil(total/nranks), trailing ranks may be short/empty). */
+SUSHI_CUDA_API int sushi_cuda_partition(int64_t total, int nranks, int rank, int64_t* first, int64_t* count);
+
+/* NCCL bootstrap: rank 0 creates a 128-byte id, the host program broadcasts it by any
+ * means, every rank then joins.  NCCL is loaded at run time (dlopen of libnccl.so.2).     */
+SUSHI_CUDA_API int sushi_cuda_comm_unique_id(void* id128);
+SUSHI_CUDA_API int sushi_cuda_comm_init_rank(sushi_cuda_ctx* ctx, int dev, const void* id128, int nranks, int rank);
+SUSHI_CUDA_API int sushi_cuda_comm_destroy(sushi_cuda_ctx* ctx);
+
+/* Row-block sharded GEMM (A NN/TN..., B replicated).  Global problem m x n x k.  `a_local`
+ * holds this rank's rows of op(A): for trans_a == 0 the rows [first, first+count) of A
+ * (count x k, leading dimension lda); for trans_a != 0 the matching columns of the stored
+ * k x m matrix, i.e. a k x count block with leading dimension lda.  `c_full` is the whole
+ * m x n result buffer on this rank: the rank computes its own row block in place and the
+ * blocks are all-gathered (NCCL over NVLink) slab by slab so that the exchange of one slab
+ * overlaps the multiplication of the next.  With beta != 0 only the rank's own block of
+ * c_full needs valid input.  gather == 0 skips the exchange (C stays sharded).            */
+SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                int64_t m, int64_t n, int64_t k, float alpha,
+                                                const float* a_local, int64_t lda,
+                                                const float* b, int64_t ldb,
+                                                float beta, float* c_full, int64_t ldc, int gather);
+
+/* Batch-index sharded strided-batched GEMM: the rank owns batches [first, first+count) of
+ * the global `batch`; a_local / b_local point at its first owned batch; c_full is the whole
+ * batch x m x n result (contiguous: ldc == n, stride_c == m*n is required when gather != 0). */
+SUSHI_CUDA_API int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                  int64_t m, int64_t n, int64_t k, float alpha,
+                                                  const float* a_local, int64_t lda, int64_t stride_a,
+                                                  const float* b_local, int64_t ldb, int64_t stride_b,
+                                                  float beta, float* c_full, int64_t ldc, int64_t stride_c,
+                                                  int64_t batch, int gather);
+
+/* ---- harness helper --------------------------------------------------------------------
+ * Counter-based uniform [-1,1) fill: element i = ((hash(seed, first_index+i) >> 8) * 2^-23) - 1,
+ * bit-identical to the host generator used by the tests.  The reference fills benchmark
+ * inputs with oneMKL philox (src/ops/math/random/uniform.cpp:41-65), whose stream no test
+ * pins; only the distribution is matched.                                                 */
+SUSHI_CUDA_API int sushi_cuda_fill_uniform(sushi_cuda_ctx* ctx, int dev, float* dst, int64_t count,
+                                           uint64_t seed, int64_t first_index);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUSHIBLAS_CUDA_H */

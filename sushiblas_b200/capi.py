@@ -1,0 +1,261 @@
+"""ctypes binding of the C ABI in include/sushiblas_cuda.h.
+
+Thin by design: every method forwards to exactly one exported function and raises
+``SushiCudaError`` on a non-zero status.  There is no fallback: if the shared library is
+missing it is an error, and every compute call needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+from ._build import LIB_PATH
+
+_i64 = ctypes.c_int64
+_f32 = ctypes.c_float
+_int = ctypes.c_int
+_vp = ctypes.c_void_p
+_sz = ctypes.c_size_t
+
+GEMM_AUTO, GEMM_SIMT, GEMM_TC3X = 0, 1, 2
+
+# name -> (restype, argtypes); mirrors include/sushiblas_cuda.h one to one
+SIGNATURES = {
+    "sushi_cuda_device_count": (_int, [ctypes.POINTER(_int)]),
+    "sushi_cuda_init": (_int, [ctypes.POINTER(_int), _int, ctypes.POINTER(_vp)]),
+    "sushi_cuda_destroy": (_int, [_vp]),
+    "sushi_cuda_last_error": (ctypes.c_char_p, [_vp]),
+    "sushi_cuda_sync": (_int, [_vp, _int]),
+    "sushi_cuda_set_stream": (_int, [_vp, _int, _vp]),
+    "sushi_cuda_get_stream": (_int, [_vp, _int, ctypes.POINTER(_vp)]),
+    "sushi_cuda_set_gemm_variant": (_int, [_vp, _int]),
+    "sushi_cuda_launch_count": (_int, [_vp, ctypes.POINTER(_i64)]),
+    "sushi_cuda_kernel_timing_enable": (_int, [_vp, _int]),
+    "sushi_cuda_kernel_timing_read": (_int, [_vp, _int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_i64),
+                                             ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_i64)]),
+    "sushi_cuda_malloc": (_int, [_vp, _int, _sz, ctypes.POINTER(_vp)]),
+    "sushi_cuda_free": (_int, [_vp, _int, _vp]),
+    "sushi_cuda_host_alloc": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "sushi_cuda_host_free": (_int, [_vp, _vp]),
+    "sushi_cuda_memcpy_h2d": (_int, [_vp, _int, _vp, _vp, _sz]),
+    "sushi_cuda_memcpy_d2h": (_int, [_vp, _int, _vp, _vp, _sz]),
+    "sushi_cuda_memcpy_d2d": (_int, [_vp, _int, _vp, _vp, _sz]),
+    "sushi_cuda_memset": (_int, [_vp, _int, _vp, _int, _sz]),
+    "sushi_cuda_sgemm": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
+                                _f32, _vp, _i64]),
+    "sushi_cuda_sgemm_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
+                                                _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
+    "sushi_cuda_sgemm_strided_batched_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
+                                                     _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
+    "sushi_cuda_gemm_workspace_bytes": (_int, [_i64, _i64, _i64, _i64, ctypes.POINTER(_sz)]),
+    "sushi_cuda_reserve_workspace": (_int, [_vp, _int, _sz]),
+    "sushi_cuda_partition": (_int, [_i64, _int, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "sushi_cuda_comm_unique_id": (_int, [_vp]),
+    "sushi_cuda_comm_init_rank": (_int, [_vp, _int, _vp, _int, _int]),
+    "sushi_cuda_comm_destroy": (_int, [_vp]),
+    "sushi_cuda_sgemm_row_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
+                                            _f32, _vp, _i64, _int]),
+    "sushi_cuda_sgemm_batch_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
+                                              _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
+    "sushi_cuda_fill_uniform": (_int, [_vp, _int, _vp, _i64, ctypes.c_uint64, _i64]),
+}
+
+_LIB = None
+
+
+class SushiCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"sushi_cuda error {code}: {message}")
+        self.code = code
+
+
+def load_library(path: Optional[str] = None):
+    """dlopen libsushiblas_cuda.so and attach the prototypes.  Never builds, never falls back."""
+    global _LIB
+    if _LIB is not None and path is None:
+        return _LIB
+    path = path or os.environ.get("SUSHIBLAS_CUDA_LIB", LIB_PATH)
+    if not os.path.exists(path):
+        raise FileNotFoundError(
+            f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(the library has no CPU fallback)")
+    lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError if the .so does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib
+
+
+def partition(total: int, nranks: int, rank: int):
+    """Contiguous block of `total` owned by `rank` (pure host arithmetic; no GPU needed)."""
+    lib = load_library()
+    first, count = _i64(), _i64()
+    rc = lib.sushi_cuda_partition(total, nranks, rank, ctypes.byref(first), ctypes.byref(count))
+    if rc != 0:
+        raise SushiCudaError(rc, lib.sushi_cuda_last_error(None).decode())
+    return first.value, count.value
+
+
+def workspace_bytes(m: int, n: int, k: int, batch: int = 1) -> int:
+    lib = load_library()
+    out = _sz()
+    rc = lib.sushi_cuda_gemm_workspace_bytes(m, n, k, batch, ctypes.byref(out))
+    if rc != 0:
+        raise SushiCudaError(rc, lib.sushi_cuda_last_error(None).decode())
+    return out.value
+
+
+def _addr(x) -> Optional[int]:
+    """Device/host address from an int, a torch tensor or a numpy array."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(f"cannot take the address of {type(x)!r}")
+
+
+class SushiCuda:
+    """One context (``sushi_cuda_ctx``).  ``dev`` arguments index the device list given here."""
+
+    def __init__(self, devices: Optional[Sequence[int]] = None):
+        self.lib = load_library()
+        self._ctx = _vp()
+        if devices:
+            arr = (_int * len(devices))(*devices)
+            rc = self.lib.sushi_cuda_init(arr, len(devices), ctypes.byref(self._ctx))
+        else:
+            rc = self.lib.sushi_cuda_init(None, 0, ctypes.byref(self._ctx))
+        if rc != 0:
+            raise SushiCudaError(rc, self.lib.sushi_cuda_last_error(None).decode())
+
+    # -- plumbing
+    def _check(self, rc: int):
+        if rc != 0:
+            raise SushiCudaError(rc, self.lib.sushi_cuda_last_error(self._ctx).decode())
+
+    def close(self):
+        if self._ctx:
+            self.lib.sushi_cuda_destroy(self._ctx)
+            self._ctx = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sync(self._ctx, dev))
+
+    def set_stream(self, stream_ptr: Optional[int], dev: int = 0):
+        self._check(self.lib.sushi_cuda_set_stream(self._ctx, dev, stream_ptr))
+
+    def get_stream(self, dev: int = 0) -> int:
+        out = _vp()
+        self._check(self.lib.sushi_cuda_get_stream(self._ctx, dev, ctypes.byref(out)))
+        return out.value or 0
+
+    def set_gemm_variant(self, variant: int):
+        self._check(self.lib.sushi_cuda_set_gemm_variant(self._ctx, variant))
+
+    def launch_count(self) -> int:
+        out = _i64()
+        self._check(self.lib.sushi_cuda_launch_count(self._ctx, ctypes.byref(out)))
+        return out.value
+
+    def kernel_timing_enable(self, enable: bool):
+        self._check(self.lib.sushi_cuda_kernel_timing_enable(self._ctx, int(enable)))
+
+    def kernel_timing_read(self, dev: int = 0):
+        """(gemm_ms, gemm_launches, prepass_ms, prepass_launches) since the last read."""
+        g, p = ctypes.c_double(), ctypes.c_double()
+        gl, pl = _i64(), _i64()
+        self._check(self.lib.sushi_cuda_kernel_timing_read(self._ctx, dev, ctypes.byref(g), ctypes.byref(gl),
+                                                           ctypes.byref(p), ctypes.byref(pl)))
+        return g.value, gl.value, p.value, pl.value
+
+    # -- storage
+    def malloc(self, nbytes: int, dev: int = 0) -> int:
+        out = _vp()
+        self._check(self.lib.sushi_cuda_malloc(self._ctx, dev, nbytes, ctypes.byref(out)))
+        return out.value
+
+    def free(self, ptr: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_free(self._ctx, dev, ptr))
+
+    def host_alloc(self, nbytes: int) -> int:
+        out = _vp()
+        self._check(self.lib.sushi_cuda_host_alloc(self._ctx, nbytes, ctypes.byref(out)))
+        return out.value
+
+    def host_free(self, ptr: int):
+        self._check(self.lib.sushi_cuda_host_free(self._ctx, ptr))
+
+    def memcpy_h2d(self, dst, src, nbytes: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_memcpy_h2d(self._ctx, dev, _addr(dst), _addr(src), nbytes))
+
+    def memcpy_d2h(self, dst, src, nbytes: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_memcpy_d2h(self._ctx, dev, _addr(dst), _addr(src), nbytes))
+
+    def memcpy_d2d(self, dst, src, nbytes: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_memcpy_d2d(self._ctx, dev, _addr(dst), _addr(src), nbytes))
+
+    def memset(self, dst, byte: int, nbytes: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_memset(self._ctx, dev, _addr(dst), byte, nbytes))
+
+    def reserve_workspace(self, nbytes: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_reserve_workspace(self._ctx, dev, nbytes))
+
+    # -- GEMM (device pointers)
+    def sgemm(self, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm(self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha,
+                                              _addr(a), lda, _addr(b), ldb, beta, _addr(c), ldc))
+
+    def sgemm_strided_batched(self, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,
+                              beta, c, ldc, stride_c, batch, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_strided_batched(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
+            _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch))
+
+    # -- GEMM (host pointers, staged)
+    def sgemm_strided_batched_host(self, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,
+                                   beta, c, ldc, stride_c, batch, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_strided_batched_host(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
+            _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch))
+
+    # -- multi-GPU
+    def comm_unique_id(self) -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        self._check(self.lib.sushi_cuda_comm_unique_id(buf))
+        return buf.raw
+
+    def comm_init_rank(self, unique_id: bytes, nranks: int, rank: int, dev: int = 0):
+        buf = ctypes.create_string_buffer(unique_id, 128)
+        self._check(self.lib.sushi_cuda_comm_init_rank(self._ctx, dev, buf, nranks, rank))
+
+    def comm_destroy(self):
+        self._check(self.lib.sushi_cuda_comm_destroy(self._ctx))
+
+    def sgemm_row_sharded(self, trans_a, trans_b, m, n, k, alpha, a_local, lda, b, ldb, beta, c_full, ldc,
+                          gather: bool = True, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_row_sharded(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a_local), lda, _addr(b), ldb,
+            beta, _addr(c_full), ldc, int(gather)))
+
+    def sgemm_batch_sharded(self, trans_a, trans_b, m, n, k, alpha, a_local, lda, stride_a, b_local, ldb, stride_b,
+                            beta, c_full, ldc, stride_c, batch, gather: bool = True, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_batch_sharded(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a_local), lda, stride_a,
+            _addr(b_local), ldb, stride_b, beta, _addr(c_full), ldc, stride_c, batch, int(gather)))
+
+    # -- harness helper
+    def fill_uniform(self, dst, count: int, seed: int, first_index: int = 0, dev: int = 0):
+        self._check(self.lib.sushi_cuda_fill_uniform(self._ctx, dev, _addr(dst), count, seed, first_index))

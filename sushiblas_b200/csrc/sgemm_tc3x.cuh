@@ -1,0 +1,523 @@
+// sgemm_tc3x.cuh -- fp32-accurate GEMM on the sm_100a tensor cores (tcgen05, 3xTF32).
+//
+// Replaces the closed sgemm the reference forwards to (oneapi::mkl::blas::row_major::gemm /
+// gemm_batch, src/ops/blas/level3/gemm.cpp:58,63) for problems large enough to fill tiles.
+//
+//   C[bi] <- alpha * (Ahi*Bhi + Ahi*Blo + Alo*Bhi) + beta * C[bi]
+//
+// Operands arrive pre-split by split_tf32.cuh as K-major hi/lo planes
+//   plane[batch][hi|lo][k_block][row_pad][16]
+// and are fetched by TMA (cp.async.bulk.tensor.4d, SWIZZLE_64B) into a 3-stage ring of
+// 64 KB stages: {A: 256 rows x 16 k x 2 planes, B: 256 rows x 16 k x 2 planes}.
+// A CTA owns a 256 x 256 tile of C as two 128 x 256 fp32 accumulators in tensor memory
+// (2 x 256 of the 512 TMEM columns).  Roles (320 threads, one CTA per SM, persistent):
+//   warp 0      TMA producer (one lane issues; waits on empty[], arms full[])
+//   warp 1      TMEM allocation + MMA issue: per stage 2 halves x 2 k-steps x 3 products of
+//               tcgen05.mma.kind::tf32 (M128 N256 K8); tcgen05.commit frees the stage
+//   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns), transpose through swizzled
+//               shared memory, then alpha*acc + beta*C with 128-bit stores that are
+//               contiguous along each row of C (8 lanes cover one 128-byte row segment)
+// Why 256 x 256: with both planes of both operands streamed per k-block, a CTA moves
+// 8*(BM+BN) bytes per 3*BM*BN tensor-core MACs; 256 x 256 keeps that at ~43 B/clk/SM of L2
+// bandwidth at full tensor rate, where 128 x 256 would need 64 B/clk/SM.
+//
+// Every wait in this kernel is bounded: on expiry the waiter records a code in *status,
+// raises a CTA-wide abort flag, every role leaves its loop, in-flight copies and MMAs are
+// drained with bounded waits, TMEM is freed and the kernel returns.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace sushi {
+namespace tc3x {
+
+constexpr int BM = 256, BN = 256, BK = 16;
+constexpr int STAGES = 3;
+constexpr int PLANE_BYTES = 256 * BK * 4;             // one 256-row plane of one k-block: 16 KB
+constexpr int OPERAND_BYTES = 2 * PLANE_BYTES;        // hi + lo: 32 KB
+constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;        // A + B: 64 KB
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;          // 320
+constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;          // per epilogue warp: 32 rows x 32 cols
+constexpr int SMEM_CTRL_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + SMEM_CTRL_BYTES + 1024;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 12;                           // tile rasterisation group (rows of tiles)
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;  // 1 s per wait
+constexpr unsigned long long DRAIN_LIMIT_NS = 2000000ull;    // 2 ms per drain wait
+
+// status codes written to *status (first writer wins)
+enum : int { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA_FULL = 2, ST_TIMEOUT_MMA_ACC = 3,
+             ST_TIMEOUT_EPILOGUE = 4 };
+
+struct Params
+{
+    float* c;
+    int64_t m, n;
+    int64_t ldc, stride_c;
+    int32_t num_kb;
+    int32_t tiles_m, tiles_n;
+    int64_t total_tiles;           // tiles_m * tiles_n * batch
+    float alpha, beta;
+    int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (own expiry or someone else's).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int code, unsigned long long limit_ns)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;)
+    {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (((++spins) & 0xFF) == 0)
+        {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > limit_ns)
+            {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2, int32_t c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], kind::tf32, issued by one thread.
+__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, SWIZZLE_64B: rows of 64 bytes, 8-row groups
+// 512 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1.
+__device__ __forceinline__ uint64_t make_desc_sw64(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;
+    return d;
+}
+
+// Instruction descriptor: D fp32, A/B tf32, both K-major, N = 256, M = 128.
+constexpr uint32_t IDESC_TF32_M128_N256 =
+    (1u << 4) | (2u << 7) | (2u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+
+struct TileCoord { int64_t bi; int32_t tm, tn; };
+
+__device__ __forceinline__ TileCoord decode_tile(int64_t t, int32_t tiles_m, int32_t tiles_n)
+{
+    const int64_t per = (int64_t)tiles_m * tiles_n;
+    TileCoord tc;
+    tc.bi = t / per;
+    const int32_t r = (int32_t)(t % per);
+    const int32_t group = GROUP_M * tiles_n;
+    const int32_t gid = r / group;
+    const int32_t first_m = gid * GROUP_M;
+    const int32_t gm = min(tiles_m - first_m, GROUP_M);
+    tc.tm = first_m + (r % group) % gm;
+    tc.tn = (r % group) / gm;
+    return tc;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment keeps every plane base on a swizzle-pattern boundary
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stage_base = smem;
+    uint8_t* epi_base = smem + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_base + EPI_WARPS * EPI_STAGE_BYTES);
+    // bars[0..2] full, [3..5] empty, [6] acc_full, [7..8] acc_empty, [9] drain
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 11);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const uint32_t full0 = smem_u32(bars + 0), empty0 = smem_u32(bars + 3);
+    const uint32_t acc_full = smem_u32(bars + 6), acc_empty0 = smem_u32(bars + 7);
+    const uint32_t drain = smem_u32(bars + 9);
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty0, EPI_WARPS / 2);
+        mbar_init(acc_empty0 + 8, EPI_WARPS / 2);
+        mbar_init(drain, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t first_tile = blockIdx.x;
+    const int64_t tile_step = gridDim.x;
+
+    if (warp == 0)
+    {
+        // ------------------------------------------------------------ TMA producer
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = first_tile; t < p.total_tiles && ok; t += tile_step)
+        {
+            const TileCoord tc = decode_tile(t, p.tiles_m, p.tiles_n);
+            for (int32_t kb = 0; kb < p.num_kb && ok; ++kb, ++it)
+            {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                int okl = 1;
+                if (lane == 0)
+                {
+                    okl = mbar_wait_bounded(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER, WAIT_LIMIT_NS);
+                    if (okl)
+                    {
+                        const uint32_t dst = smem_u32(stage_base + s * STAGE_BYTES);
+                        const uint32_t bar = full0 + 8 * s;
+                        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                        tma_load_4d(dst, &map_a, bar, 0, tc.tm * BM, kb, (int32_t)(tc.bi * 2));
+                        tma_load_4d(dst + OPERAND_BYTES, &map_b, bar, 0, tc.tn * BN, kb, (int32_t)(tc.bi * 2));
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+            }
+        }
+        if (!ok && lane == 0)
+        {
+            // drain: wait (bounded) for the loads already issued into the ring
+            const uint32_t lo = it > STAGES ? it - STAGES : 0;
+            for (uint32_t j = lo; j < it; ++j)
+            {
+                const uint32_t bar = full0 + 8 * (j % STAGES), par = (j / STAGES) & 1;
+                const unsigned long long t0 = globaltimer_ns();
+                while (!mbar_try_wait(bar, par) && globaltimer_ns() - t0 < DRAIN_LIMIT_NS) {}
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp == 1)
+    {
+        // ------------------------------------------------------------ MMA issuer
+        uint32_t it = 0, tl = 0;
+        bool ok = true;
+        for (int64_t t = first_tile; t < p.total_tiles && ok; t += tile_step, ++tl)
+        {
+            for (int32_t kb = 0; kb < p.num_kb && ok; ++kb, ++it)
+            {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                int okl = 1;
+                if (lane == 0)
+                {
+                    okl = mbar_wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, WAIT_LIMIT_NS);
+                    if (okl && kb == 0)
+                    {
+                        // both accumulator halves must have been drained by the previous tile's epilogue
+                        okl = mbar_wait_bounded(acc_empty0, (tl & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS) &&
+                              mbar_wait_bounded(acc_empty0 + 8, (tl & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS);
+                    }
+                    if (okl)
+                    {
+                        tcgen05_fence_after();
+                        const uint32_t a_addr = smem_u32(stage_base + s * STAGE_BYTES);
+                        const uint32_t b_addr = a_addr + OPERAND_BYTES;
+                        const uint64_t b_hi = make_desc_sw64(b_addr);
+                        const uint64_t b_lo = make_desc_sw64(b_addr + PLANE_BYTES);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                        {
+                            const uint64_t a_hi = make_desc_sw64(a_addr + h * (128 * BK * 4));
+                            const uint64_t a_lo = make_desc_sw64(a_addr + PLANE_BYTES + h * (128 * BK * 4));
+                            const uint32_t d = tmem_base + h * 256;
+#pragma unroll
+                            for (int ks = 0; ks < BK / 8; ++ks)
+                            {
+                                const uint64_t koff = (uint64_t)((ks * 8 * 4) >> 4);   // +32 bytes per k-step
+                                const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
+                                // small terms first, then the leading product
+                                tcgen05_mma_tf32(d, a_lo + koff, b_hi + koff, IDESC_TF32_M128_N256, acc);
+                                tcgen05_mma_tf32(d, a_hi + koff, b_lo + koff, IDESC_TF32_M128_N256, 1u);
+                                tcgen05_mma_tf32(d, a_hi + koff, b_hi + koff, IDESC_TF32_M128_N256, 1u);
+                            }
+                        }
+                        tcgen05_commit(empty0 + 8 * s);               // stage reusable once these MMAs retire
+                        if (kb == p.num_kb - 1) tcgen05_commit(acc_full);  // accumulators complete
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+            }
+        }
+        if (!ok && lane == 0)
+        {
+            // drain outstanding MMAs before TMEM is released
+            tcgen05_commit(drain);
+            const unsigned long long t0 = globaltimer_ns();
+            while (!mbar_try_wait(drain, 0) && globaltimer_ns() - t0 < DRAIN_LIMIT_NS) {}
+        }
+        __syncwarp();
+    }
+    else
+    {
+        // ------------------------------------------------------------ epilogue warps
+        const int ew = warp - 2;                 // 0..7
+        const int h = ew >> 2;                   // accumulator half (rows h*128 ..)
+        const int q = warp & 3;                  // TMEM lane quarter this warp may access
+        float4* stg = reinterpret_cast<float4*>(epi_base + ew * EPI_STAGE_BYTES);   // [32 rows][8 float4]
+        const bool has_beta = (p.beta != 0.0f);
+        uint32_t tl = 0;
+        bool ok = true;
+        for (int64_t t = first_tile; t < p.total_tiles && ok; t += tile_step, ++tl)
+        {
+            const TileCoord tc = decode_tile(t, p.tiles_m, p.tiles_n);
+            int okl = mbar_wait_bounded(acc_full, tl & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
+            ok = __all_sync(0xffffffffu, okl) != 0;
+            if (!ok) break;
+            tcgen05_fence_after();
+
+            float* __restrict__ cb = p.c + tc.bi * p.stride_c;
+            const int64_t row_base = (int64_t)tc.tm * BM + h * 128 + q * 32;   // first row of this warp
+            const int64_t col_base = (int64_t)tc.tn * BN;
+            const bool vec_ok = ((p.ldc & 3) == 0) && ((p.stride_c & 3) == 0) &&
+                                ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
+            const int rsub = lane >> 3, c4 = lane & 7;
+
+            if (row_base < p.m)
+            {
+                for (int chunk = 0; chunk < BN / 32; ++chunk)
+                {
+                    const int64_t col0 = col_base + chunk * 32;
+                    if (col0 >= p.n) break;
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256 + chunk * 32);
+                    tcgen05_ld_32x32b_x32(taddr, v);
+
+                    // old C values for the beta term, fetched while the TMEM load is in flight
+                    float4 old[8];
+                    const int64_t gcol = col0 + c4 * 4;
+                    if (has_beta && vec_ok)
+                    {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                        {
+                            const int64_t grow = row_base + i * 4 + rsub;
+                            old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (grow < p.m && gcol + 3 < p.n)
+                                old[i] = *reinterpret_cast<const float4*>(cb + grow * p.ldc + gcol);
+                        }
+                    }
+                    tcgen05_wait_ld();
+
+                    // registers (row = lane, 32 columns) -> shared, float4 index XOR-swizzled by row
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                    {
+                        float4 w;
+                        w.x = __uint_as_float(v[4 * j + 0]); w.y = __uint_as_float(v[4 * j + 1]);
+                        w.z = __uint_as_float(v[4 * j + 2]); w.w = __uint_as_float(v[4 * j + 3]);
+                        stg[lane * 8 + (j ^ (lane & 7))] = w;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                    {
+                        const int r = i * 4 + rsub;
+                        const float4 a = stg[r * 8 + (c4 ^ (r & 7))];
+                        const int64_t grow = row_base + r;
+                        if (grow >= p.m || gcol >= p.n) continue;
+                        float* dst = cb + grow * p.ldc + gcol;
+                        if (vec_ok && gcol + 3 < p.n)
+                        {
+                            float4 o;
+                            o.x = p.alpha * a.x; o.y = p.alpha * a.y; o.z = p.alpha * a.z; o.w = p.alpha * a.w;
+                            if (has_beta)
+                            {
+                                o.x = fmaf(p.beta, old[i].x, o.x); o.y = fmaf(p.beta, old[i].y, o.y);
+                                o.z = fmaf(p.beta, old[i].z, o.z); o.w = fmaf(p.beta, old[i].w, o.w);
+                            }
+                            *reinterpret_cast<float4*>(dst) = o;
+                        }
+                        else
+                        {
+                            const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                            {
+                                if (gcol + j < p.n)
+                                {
+                                    float o = p.alpha * av[j];
+                                    if (has_beta) o = fmaf(p.beta, dst[j], o);
+                                    dst[j] = o;
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            // this warp is done reading accumulator half h of this tile
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * h);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1)
+    {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn)
+    {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// Tensor map over plane[batch*2][num_kb][rows_pad][16]; box = {16 k, 256 rows, 1 k-block, 2 planes}.
+inline bool make_plane_map(CUtensorMap* map, const float* planes, int64_t rows_pad, int64_t num_kb, int64_t batch)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t gdim[4] = {(cuuint64_t)BK, (cuuint64_t)rows_pad, (cuuint64_t)num_kb, (cuuint64_t)(2 * batch)};
+    cuuint64_t gstr[3] = {(cuuint64_t)BK * 4, (cuuint64_t)rows_pad * BK * 4, (cuuint64_t)num_kb * rows_pad * BK * 4};
+    cuuint32_t box[4] = {(cuuint32_t)BK, 256u, 1u, 2u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(planes), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// planes_a / planes_b as written by launch_split_tf32 for op(A) (rows = m) and op(B)^T (rows = n).
+inline cudaError_t launch_sgemm_tc3x(const float* planes_a, const float* planes_b, float* c,
+                                     int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
+                                     float alpha, float beta, int* status, int sm_count, cudaStream_t st)
+{
+    // per-device attribute; cheap enough to set on every launch
+    cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const int64_t m_pad = (m + 255) / 256 * 256, n_pad = (n + 255) / 256 * 256;
+    const int64_t num_kb = (k + BK - 1) / BK;
+    CUtensorMap map_a, map_b;
+    if (!make_plane_map(&map_a, planes_a, m_pad, num_kb, batch)) return cudaErrorInvalidValue;
+    if (!make_plane_map(&map_b, planes_b, n_pad, num_kb, batch)) return cudaErrorInvalidValue;
+    Params p;
+    p.c = c; p.m = m; p.n = n; p.ldc = ldc; p.stride_c = stride_c;
+    p.num_kb = (int32_t)num_kb;
+    p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
+    p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
+    p.alpha = alpha; p.beta = beta; p.status = status;
+    const int64_t grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
+    if (grid <= 0) return cudaSuccess;
+    sgemm_tc3x_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    return cudaGetLastError();
+}
+
+} // namespace tc3x
+} // namespace sushi

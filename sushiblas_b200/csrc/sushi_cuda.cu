@@ -1,0 +1,830 @@
+// sushi_cuda.cu -- C ABI of the sm_100a backend (declared in include/sushiblas_cuda.h).
+//
+// Owns: the per-device context (stream, scratch, status word), storage calls
+// (cudaMalloc / pinned host + explicit copies, replacing the USM allocator of
+// include/SushiRuntime/memory/usm_allocator.hpp:43-71), kernel selection, and the
+// NCCL-based multi-GPU layer.  There is no CPU fallback anywhere in this file.
+#include "../../include/sushiblas_cuda.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "sgemm_simt.cuh"
+#include "split_tf32.cuh"
+#include "sgemm_tc3x.cuh"
+
+namespace {
+
+struct DeviceState
+{
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;        // active stream (own or caller's)
+    void* workspace = nullptr;            // 3xTF32 operand planes
+    size_t workspace_bytes = 0;
+    void* stage[3] = {nullptr, nullptr, nullptr};   // device staging for the *_host entry points
+    size_t stage_bytes[3] = {0, 0, 0};
+    int* status = nullptr;                // device word written by bounded in-kernel waits
+    int* status_host = nullptr;           // pinned mirror
+    // kernel timing (off by default): event triples {before pre-pass, before GEMM, after GEMM}
+    std::vector<cudaEvent_t> timing_events;
+    size_t timing_used = 0;
+    std::vector<int> timing_prepass_launches;
+};
+
+// minimal NCCL surface, resolved at run time
+typedef struct ncclComm* ncclComm_t;
+struct Id128 { char bytes[128]; };   // ncclUniqueId
+struct NcclApi
+{
+    void* handle = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(ncclComm_t*, int, Id128, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+constexpr int NCCL_FLOAT32 = 7;
+
+NcclApi g_nccl;
+std::mutex g_nccl_mutex;
+thread_local std::string g_tls_error;
+
+} // namespace
+
+struct sushi_cuda_ctx
+{
+    std::vector<DeviceState> devs;
+    std::string last_error;
+    int variant = SUSHI_GEMM_AUTO;
+    std::atomic<int64_t> launches{0};
+    bool timing = false;
+    // multi-GPU (one process per GPU: a single communicator bound to one device index)
+    ncclComm_t comm = nullptr;
+    int comm_dev = -1, nranks = 1, rank = 0;
+    cudaStream_t comm_stream = nullptr;
+    std::vector<cudaEvent_t> slab_events;
+    cudaEvent_t comm_done = nullptr;
+};
+
+namespace {
+
+int set_error(sushi_cuda_ctx* ctx, int code, const std::string& msg)
+{
+    if (ctx) ctx->last_error = msg; else g_tls_error = msg;
+    return code;
+}
+
+int cuda_fail(sushi_cuda_ctx* ctx, cudaError_t e, const char* what)
+{
+    std::string msg = std::string(what) + ": " + cudaGetErrorString(e);
+    int code = (e == cudaErrorMemoryAllocation) ? SUSHI_CUDA_ERR_OOM
+             : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) ? SUSHI_CUDA_ERR_NO_DEVICE
+             : SUSHI_CUDA_ERR_CUDA;
+    return set_error(ctx, code, msg);
+}
+
+#define SC_CUDA(ctx, call)                                              \
+    do { cudaError_t e__ = (call); if (e__ != cudaSuccess) return cuda_fail((ctx), e__, #call); } while (0)
+
+DeviceState* get_dev(sushi_cuda_ctx* ctx, int dev)
+{
+    if (!ctx || dev < 0 || dev >= (int)ctx->devs.size()) return nullptr;
+    return &ctx->devs[dev];
+}
+
+int grow(sushi_cuda_ctx* ctx, DeviceState& d, void** buf, size_t* have, size_t need)
+{
+    if (need <= *have) return SUSHI_CUDA_OK;
+    if (*buf)
+    {
+        SC_CUDA(ctx, cudaStreamSynchronize(d.stream));
+        SC_CUDA(ctx, cudaFree(*buf));
+        *buf = nullptr; *have = 0;
+    }
+    SC_CUDA(ctx, cudaMalloc(buf, need));
+    *have = need;
+    return SUSHI_CUDA_OK;
+}
+
+int64_t extent(int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t batch)
+{
+    if (rows <= 0 || cols <= 0 || batch <= 0) return 0;
+    return (batch - 1) * stride + (rows - 1) * ld + cols;
+}
+
+int validate_gemm(sushi_cuda_ctx* ctx, int64_t m, int64_t n, int64_t k, const float* a, int64_t lda,
+                  const float* b, int64_t ldb, const float* c, int64_t ldc, int ta, int tb,
+                  int64_t sa, int64_t sb, int64_t sc, int64_t batch)
+{
+    if (m < 0 || n < 0 || k < 0 || batch < 0)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: negative dimension");
+    const int64_t a_cols = ta ? m : k, b_cols = tb ? k : n;
+    if (lda < (a_cols > 1 ? a_cols : 1)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: lda too small");
+    if (ldb < (b_cols > 1 ? b_cols : 1)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: ldb too small");
+    if (ldc < (n > 1 ? n : 1)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: ldc too small");
+    if (sa < 0 || sb < 0 || sc < 0) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: negative batch stride");
+    if (m > 0 && n > 0 && batch > 0)
+    {
+        if (!c) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: C is null");
+        if (k > 0 && (!a || !b)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: A or B is null");
+        if (batch > 1 && sc < extent(m, n, ldc, 0, 1))
+            return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: stride_c makes batches of C overlap");
+    }
+    return SUSHI_CUDA_OK;
+}
+
+// Kernel choice for SUSHI_GEMM_AUTO: the tensor-core path pays a pre-pass and works in
+// 256 x 256 tiles, so it needs enough k to amortise the split and enough tiles to occupy SMs.
+bool prefer_tc3x(int64_t m, int64_t n, int64_t k, int64_t batch, int sm_count)
+{
+    if (k < 128 || m < 128 || n < 128) return false;
+    const double tiles = (double)((m + 255) / 256) * (double)((n + 255) / 256) * (double)batch;
+    const double waves = tiles <= sm_count ? 1.0 : (double)((int64_t)(tiles + sm_count - 1) / sm_count);
+    // tensor path: 1536 clk per 16-k block per tile (+ pre-pass ~ 12 B per operand element at 5 TB/s)
+    const double t_tc = waves * ((double)((k + 15) / 16) * 1536.0 / 1.5e9) +
+                        12.0 * (double)batch * (double)k * (double)(m + n) / 5.0e12 + 6e-6;
+    const double t_simt = 2.0 * (double)m * (double)n * (double)k * (double)batch / 25.0e12 + 3e-6;
+    return t_tc < t_simt;
+}
+
+int check_variant_env(int current)
+{
+    const char* e = getenv("SUSHI_GEMM_VARIANT");
+    if (!e) return current;
+    if (!strcmp(e, "simt") || !strcmp(e, "1")) return SUSHI_GEMM_SIMT;
+    if (!strcmp(e, "tc3x") || !strcmp(e, "2")) return SUSHI_GEMM_TC3X;
+    return current;
+}
+
+// Records the next timing event of the current triple (no-op unless timing is enabled).
+int timing_mark(sushi_cuda_ctx* ctx, DeviceState& d, int which, int prepass_launches)
+{
+    if (!ctx->timing) return SUSHI_CUDA_OK;
+    if (which == 0)
+    {
+        while (d.timing_events.size() < d.timing_used + 3)
+        {
+            cudaEvent_t e;
+            SC_CUDA(ctx, cudaEventCreate(&e));
+            d.timing_events.push_back(e);
+        }
+        d.timing_prepass_launches.push_back(prepass_launches);
+    }
+    SC_CUDA(ctx, cudaEventRecord(d.timing_events[d.timing_used + which], d.stream));
+    if (which == 2) d.timing_used += 3;
+    return SUSHI_CUDA_OK;
+}
+
+int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int64_t n, int64_t k, float alpha,
+             const float* a, int64_t lda, int64_t sa, const float* b, int64_t ldb, int64_t sb,
+             float beta, float* c, int64_t ldc, int64_t sc, int64_t batch)
+{
+    if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d.device));
+    if (k == 0 || alpha == 0.0f)
+    {
+        if (beta == 1.0f) return SUSHI_CUDA_OK;
+        const int64_t total = m * n * batch;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > (int64_t)d.sm_count * 16) blocks = (int64_t)d.sm_count * 16;
+        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d.stream>>>(c, m, n, ldc, sc, batch, beta);
+        ctx->launches++;
+        SC_CUDA(ctx, cudaGetLastError());
+        return SUSHI_CUDA_OK;
+    }
+    int variant = ctx->variant;
+    if (variant == SUSHI_GEMM_AUTO)
+        variant = prefer_tc3x(m, n, k, batch, d.sm_count) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+
+    if (variant == SUSHI_GEMM_TC3X)
+    {
+        const size_t bytes_a = sushi::split_plane_bytes(m, k, batch);
+        const size_t bytes_b = sushi::split_plane_bytes(n, k, batch);
+        int rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_a + bytes_b);
+        if (rc != SUSHI_CUDA_OK) return rc;
+        float* planes_a = static_cast<float*>(d.workspace);
+        float* planes_b = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_a);
+        if ((rc = timing_mark(ctx, d, 0, 2)) != SUSHI_CUDA_OK) return rc;
+        SC_CUDA(ctx, sushi::launch_split_tf32(a, planes_a, m, k, lda, sa, batch, /*k_contig=*/!ta, d.sm_count, d.stream));
+        SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b, n, k, ldb, sb, batch, /*k_contig=*/tb != 0, d.sm_count, d.stream));
+        if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
+        SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(planes_a, planes_b, c, m, n, k, ldc, sc, batch, alpha, beta,
+                                                   d.status, d.sm_count, d.stream));
+        if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
+        ctx->launches += 3;
+        return SUSHI_CUDA_OK;
+    }
+
+    sushi::SimtGemmArgs g;
+    g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.stride_a = sa; g.stride_b = sb; g.stride_c = sc; g.tiles_m = 0; g.tiles_n = 0;
+    g.alpha = alpha; g.beta = beta;
+    int rc = timing_mark(ctx, d, 0, 0);
+    if (rc == SUSHI_CUDA_OK) rc = timing_mark(ctx, d, 1, 0);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, sushi::launch_sgemm_simt(g, ta != 0, tb != 0, batch, d.sm_count, d.stream));
+    if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
+    ctx->launches++;
+    return SUSHI_CUDA_OK;
+}
+
+bool load_nccl(std::string* err)
+{
+    std::lock_guard<std::mutex> lock(g_nccl_mutex);
+    if (g_nccl.handle) return true;
+    const char* names[] = {getenv("SUSHI_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    void* h = nullptr;
+    for (const char* nm : names)
+    {
+        if (!nm) continue;
+        h = dlopen(nm, RTLD_NOW | RTLD_GLOBAL);
+        if (h) break;
+    }
+    if (!h) { *err = std::string("cannot load libnccl.so.2: ") + dlerror(); return false; }
+    NcclApi api;
+    api.handle = h;
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
+    api.Broadcast = reinterpret_cast<decltype(api.Broadcast)>(dlsym(h, "ncclBroadcast"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(dlsym(h, "ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(dlsym(h, "ncclGroupEnd"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+    if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.Broadcast ||
+        !api.GroupStart || !api.GroupEnd || !api.GetErrorString)
+    {
+        *err = "libnccl is missing a required symbol";
+        return false;
+    }
+    g_nccl = api;
+    return true;
+}
+
+int nccl_fail(sushi_cuda_ctx* ctx, int rc, const char* what)
+{
+    return set_error(ctx, SUSHI_CUDA_ERR_COMM, std::string(what) + ": " + g_nccl.GetErrorString(rc));
+}
+
+#define SC_NCCL(ctx, call)                                              \
+    do { int r__ = (call); if (r__ != 0) return nccl_fail((ctx), r__, #call); } while (0)
+
+__global__ void fill_uniform_kernel(float* dst, int64_t count, uint64_t key, int64_t first)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
+    {
+        uint64_t z = ((uint64_t)(first + i) ^ key) + 0x9E3779B97F4A7C15ull;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z = z ^ (z >> 31);
+        const uint32_t u = (uint32_t)(z >> 32) >> 8;
+        dst[i] = (float)u * 1.1920928955078125e-07f - 1.0f;   // u * 2^-23 - 1, exact
+    }
+}
+
+uint64_t splitmix64_host(uint64_t x)
+{
+    uint64_t z = x + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+} // namespace
+
+// ======================================================================== context
+extern "C" int sushi_cuda_device_count(int* count)
+{
+    if (!count) return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "device_count: null output");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) { *count = 0; return cuda_fail(nullptr, e, "cudaGetDeviceCount"); }
+    *count = n;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx** out)
+{
+    if (!out) return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "init: null output");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaGetDeviceCount");
+    if (count == 0) return set_error(nullptr, SUSHI_CUDA_ERR_NO_DEVICE, "no CUDA device");
+
+    std::vector<int> ids;
+    if (devices && n_devices > 0) ids.assign(devices, devices + n_devices);
+    else
+    {
+        const char* env = getenv("SUSHI_CUDA_DEVICE");
+        ids.push_back(env ? atoi(env) : 0);
+    }
+    sushi_cuda_ctx* ctx = new sushi_cuda_ctx();
+    ctx->variant = check_variant_env(SUSHI_GEMM_AUTO);
+    for (int id : ids)
+    {
+        if (id < 0 || id >= count)
+        {
+            set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "init: device index out of range");
+            sushi_cuda_destroy(ctx);
+            return SUSHI_CUDA_ERR_INVALID_ARG;
+        }
+        DeviceState d;
+        d.device = id;
+        cudaDeviceProp prop;
+        bool ok = cudaSetDevice(id) == cudaSuccess && cudaGetDeviceProperties(&prop, id) == cudaSuccess;
+        if (ok && prop.major != 10)
+        {
+            set_error(nullptr, SUSHI_CUDA_ERR_UNSUPPORTED, "this library is built for sm_100a (B200) only");
+            sushi_cuda_destroy(ctx);
+            return SUSHI_CUDA_ERR_UNSUPPORTED;
+        }
+        ok = ok && cudaStreamCreateWithFlags(&d.own_stream, cudaStreamNonBlocking) == cudaSuccess;
+        ok = ok && cudaMalloc(&d.status, sizeof(int)) == cudaSuccess;
+        ok = ok && cudaMemset(d.status, 0, sizeof(int)) == cudaSuccess;
+        ok = ok && cudaMallocHost(&d.status_host, sizeof(int)) == cudaSuccess;
+        if (!ok)
+        {
+            cuda_fail(nullptr, cudaGetLastError(), "device set-up");
+            ctx->devs.push_back(d);
+            sushi_cuda_destroy(ctx);
+            return SUSHI_CUDA_ERR_CUDA;
+        }
+        d.stream = d.own_stream;
+        d.sm_count = prop.multiProcessorCount;
+        ctx->devs.push_back(d);
+    }
+    *out = ctx;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
+{
+    if (!ctx) return SUSHI_CUDA_OK;
+    sushi_cuda_comm_destroy(ctx);
+    for (DeviceState& d : ctx->devs)
+    {
+        cudaSetDevice(d.device);
+        if (d.own_stream) cudaStreamSynchronize(d.own_stream);
+        if (d.workspace) cudaFree(d.workspace);
+        for (void* s : d.stage) if (s) cudaFree(s);
+        if (d.status) cudaFree(d.status);
+        if (d.status_host) cudaFreeHost(d.status_host);
+        for (cudaEvent_t e : d.timing_events) cudaEventDestroy(e);
+        if (d.own_stream) cudaStreamDestroy(d.own_stream);
+    }
+    delete ctx;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" const char* sushi_cuda_last_error(sushi_cuda_ctx* ctx)
+{
+    return ctx ? ctx->last_error.c_str() : g_tls_error.c_str();
+}
+
+extern "C" int sushi_cuda_sync(sushi_cuda_ctx* ctx, int dev)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sync: bad context or device index");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaMemcpyAsync(d->status_host, d->status, sizeof(int), cudaMemcpyDeviceToHost, d->stream));
+    SC_CUDA(ctx, cudaStreamSynchronize(d->stream));
+    if (ctx->comm_stream && ctx->comm_dev == dev) SC_CUDA(ctx, cudaStreamSynchronize(ctx->comm_stream));
+    if (*d->status_host != 0)
+    {
+        char msg[128];
+        snprintf(msg, sizeof msg, "a bounded in-kernel wait expired (code %d)", *d->status_host);
+        cudaMemsetAsync(d->status, 0, sizeof(int), d->stream);
+        return set_error(ctx, SUSHI_CUDA_ERR_KERNEL_TIMEOUT, msg);
+    }
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_set_stream(sushi_cuda_ctx* ctx, int dev, void* cuda_stream)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "set_stream: bad context or device index");
+    d->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : d->own_stream;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_get_stream(sushi_cuda_ctx* ctx, int dev, void** cuda_stream)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !cuda_stream) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "get_stream: bad argument");
+    *cuda_stream = d->stream;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_set_gemm_variant(sushi_cuda_ctx* ctx, int variant)
+{
+    if (!ctx || variant < SUSHI_GEMM_AUTO || variant > SUSHI_GEMM_TC3X)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "set_gemm_variant: bad argument");
+    ctx->variant = variant;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_launch_count(sushi_cuda_ctx* ctx, int64_t* launches)
+{
+    if (!ctx || !launches) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "launch_count: bad argument");
+    *launches = ctx->launches.load();
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_kernel_timing_enable(sushi_cuda_ctx* ctx, int enable)
+{
+    if (!ctx) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "kernel_timing_enable: null context");
+    ctx->timing = enable != 0;
+    for (DeviceState& d : ctx->devs) { d.timing_used = 0; d.timing_prepass_launches.clear(); }
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_kernel_timing_read(sushi_cuda_ctx* ctx, int dev, double* gemm_ms, int64_t* gemm_launches,
+                                             double* prepass_ms, int64_t* prepass_launches)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !gemm_ms || !gemm_launches || !prepass_ms || !prepass_launches)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "kernel_timing_read: bad argument");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaStreamSynchronize(d->stream));
+    double g = 0.0, p = 0.0;
+    int64_t gl = 0, pl = 0;
+    for (size_t i = 0; i + 2 < d->timing_used + 1 && i < d->timing_used; i += 3)
+    {
+        float ms = 0.0f;
+        SC_CUDA(ctx, cudaEventElapsedTime(&ms, d->timing_events[i], d->timing_events[i + 1]));
+        p += ms;
+        SC_CUDA(ctx, cudaEventElapsedTime(&ms, d->timing_events[i + 1], d->timing_events[i + 2]));
+        g += ms;
+        gl += 1;
+        pl += d->timing_prepass_launches[i / 3];
+    }
+    *gemm_ms = g; *gemm_launches = gl; *prepass_ms = p; *prepass_launches = pl;
+    d->timing_used = 0;
+    d->timing_prepass_launches.clear();
+    return SUSHI_CUDA_OK;
+}
+
+// ======================================================================== storage
+extern "C" int sushi_cuda_malloc(sushi_cuda_ctx* ctx, int dev, size_t bytes, void** ptr)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !ptr || bytes == 0) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "malloc: bad argument");
+    *ptr = nullptr;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaMalloc(ptr, bytes));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_free(sushi_cuda_ctx* ctx, int dev, void* ptr)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "free: bad context or device index");
+    if (!ptr) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaFree(ptr));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_host_alloc(sushi_cuda_ctx* ctx, size_t bytes, void** ptr)
+{
+    if (!ctx || !ptr || bytes == 0) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "host_alloc: bad argument");
+    *ptr = nullptr;
+    SC_CUDA(ctx, cudaSetDevice(ctx->devs[0].device));
+    SC_CUDA(ctx, cudaHostAlloc(ptr, bytes, cudaHostAllocPortable));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_host_free(sushi_cuda_ctx* ctx, void* ptr)
+{
+    if (!ctx) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "host_free: null context");
+    if (!ptr) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaFreeHost(ptr));
+    return SUSHI_CUDA_OK;
+}
+
+static int copy_async(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes, cudaMemcpyKind kind,
+                      const char* what)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, std::string(what) + ": bad context or device index");
+    if (bytes == 0) return SUSHI_CUDA_OK;
+    if (!dst || !src) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, std::string(what) + ": null pointer");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, kind, d->stream));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_memcpy_h2d(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes)
+{ return copy_async(ctx, dev, dst, src, bytes, cudaMemcpyHostToDevice, "memcpy_h2d"); }
+extern "C" int sushi_cuda_memcpy_d2h(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes)
+{ return copy_async(ctx, dev, dst, src, bytes, cudaMemcpyDeviceToHost, "memcpy_d2h"); }
+extern "C" int sushi_cuda_memcpy_d2d(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes)
+{ return copy_async(ctx, dev, dst, src, bytes, cudaMemcpyDeviceToDevice, "memcpy_d2d"); }
+
+extern "C" int sushi_cuda_memset(sushi_cuda_ctx* ctx, int dev, void* dst, int byte, size_t bytes)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "memset: bad context or device index");
+    if (bytes == 0) return SUSHI_CUDA_OK;
+    if (!dst) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "memset: null pointer");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaMemsetAsync(dst, byte, bytes, d->stream));
+    return SUSHI_CUDA_OK;
+}
+
+// ======================================================================== GEMM
+extern "C" int sushi_cuda_sgemm_strided_batched(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                int64_t m, int64_t n, int64_t k, float alpha,
+                                                const float* a, int64_t lda, int64_t stride_a,
+                                                const float* b, int64_t ldb, int64_t stride_b,
+                                                float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                int64_t batch)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm: bad context or device index");
+    int rc = validate_gemm(ctx, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, stride_a, stride_b, stride_c, batch);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc,
+                    stride_c, batch);
+}
+
+extern "C" int sushi_cuda_sgemm(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                int64_t m, int64_t n, int64_t k, float alpha,
+                                const float* a, int64_t lda, const float* b, int64_t ldb,
+                                float beta, float* c, int64_t ldc)
+{
+    return sushi_cuda_sgemm_strided_batched(ctx, dev, trans_a, trans_b, m, n, k, alpha, a, lda, 0, b, ldb, 0,
+                                            beta, c, ldc, 0, 1);
+}
+
+extern "C" int sushi_cuda_sgemm_strided_batched_host(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                     int64_t m, int64_t n, int64_t k, float alpha,
+                                                     const float* a, int64_t lda, int64_t stride_a,
+                                                     const float* b, int64_t ldb, int64_t stride_b,
+                                                     float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                     int64_t batch)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_host: bad context or device index");
+    int rc = validate_gemm(ctx, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, stride_a, stride_b, stride_c, batch);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    const size_t ea = (size_t)extent(trans_a ? k : m, trans_a ? m : k, lda, stride_a, batch) * sizeof(float);
+    const size_t eb = (size_t)extent(trans_b ? n : k, trans_b ? k : n, ldb, stride_b, batch) * sizeof(float);
+    const size_t ec = (size_t)extent(m, n, ldc, stride_c, batch) * sizeof(float);
+    const size_t need[3] = {ea ? ea : 4, eb ? eb : 4, ec};
+    for (int i = 0; i < 3; ++i)
+        if ((rc = grow(ctx, *d, &d->stage[i], &d->stage_bytes[i], need[i])) != SUSHI_CUDA_OK) return rc;
+    float* da = static_cast<float*>(d->stage[0]);
+    float* db = static_cast<float*>(d->stage[1]);
+    float* dc = static_cast<float*>(d->stage[2]);
+    if (ea) SC_CUDA(ctx, cudaMemcpyAsync(da, a, ea, cudaMemcpyHostToDevice, d->stream));
+    if (eb) SC_CUDA(ctx, cudaMemcpyAsync(db, b, eb, cudaMemcpyHostToDevice, d->stream));
+    // C goes up when it is read (beta != 0) or when its buffer has gaps the copy back must preserve
+    const bool dense_c = (ldc == n) && (batch == 1 || stride_c == m * n);
+    if (beta != 0.0f || !dense_c) SC_CUDA(ctx, cudaMemcpyAsync(dc, c, ec, cudaMemcpyHostToDevice, d->stream));
+    rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, da, lda, stride_a, db, ldb, stride_b, beta, dc, ldc,
+                  stride_c, batch);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaMemcpyAsync(c, dc, ec, cudaMemcpyDeviceToHost, d->stream));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, size_t* bytes)
+{
+    if (!bytes || m < 0 || n < 0 || k < 0 || batch < 0)
+        return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "gemm_workspace_bytes: bad argument");
+    *bytes = sushi::split_plane_bytes(m, k, batch) + sushi::split_plane_bytes(n, k, batch);
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_reserve_workspace(sushi_cuda_ctx* ctx, int dev, size_t bytes)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "reserve_workspace: bad context or device index");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    return grow(ctx, *d, &d->workspace, &d->workspace_bytes, bytes);
+}
+
+// ======================================================================== multi-GPU
+extern "C" int sushi_cuda_partition(int64_t total, int nranks, int rank, int64_t* first, int64_t* count)
+{
+    if (total < 0 || nranks <= 0 || rank < 0 || rank >= nranks || !first || !count)
+        return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "partition: bad argument");
+    const int64_t block = (total + nranks - 1) / nranks;
+    int64_t lo = block * rank;
+    if (lo > total) lo = total;
+    int64_t hi = lo + block;
+    if (hi > total) hi = total;
+    *first = lo;
+    *count = hi - lo;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_comm_unique_id(void* id128)
+{
+    if (!id128) return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "comm_unique_id: null output");
+    std::string err;
+    if (!load_nccl(&err)) return set_error(nullptr, SUSHI_CUDA_ERR_COMM, err);
+    int rc = g_nccl.GetUniqueId(id128);
+    if (rc != 0) return nccl_fail(nullptr, rc, "ncclGetUniqueId");
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_comm_init_rank(sushi_cuda_ctx* ctx, int dev, const void* id128, int nranks, int rank)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !id128 || nranks < 1 || rank < 0 || rank >= nranks)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "comm_init_rank: bad argument");
+    if (ctx->comm) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "comm_init_rank: communicator already exists");
+    std::string err;
+    if (!load_nccl(&err)) return set_error(ctx, SUSHI_CUDA_ERR_COMM, err);
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    Id128 id;
+    memcpy(id.bytes, id128, sizeof id.bytes);
+    SC_NCCL(ctx, g_nccl.CommInitRank(&ctx->comm, nranks, id, rank));
+    ctx->comm_dev = dev; ctx->nranks = nranks; ctx->rank = rank;
+    SC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
+    SC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_comm_destroy(sushi_cuda_ctx* ctx)
+{
+    if (!ctx) return SUSHI_CUDA_OK;
+    if (ctx->comm_stream) { cudaStreamSynchronize(ctx->comm_stream); }
+    if (ctx->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm);
+    ctx->comm = nullptr;
+    for (cudaEvent_t e : ctx->slab_events) cudaEventDestroy(e);
+    ctx->slab_events.clear();
+    if (ctx->comm_done) { cudaEventDestroy(ctx->comm_done); ctx->comm_done = nullptr; }
+    if (ctx->comm_stream) { cudaStreamDestroy(ctx->comm_stream); ctx->comm_stream = nullptr; }
+    ctx->comm_dev = -1; ctx->nranks = 1; ctx->rank = 0;
+    return SUSHI_CUDA_OK;
+}
+
+namespace {
+
+// Exchange `units` owned units (rows or batches; `unit_elems` floats each, contiguous) of every
+// rank, restricted to local unit range [u0, u1) of each rank's block.  In place in c_full.
+int gather_slab(sushi_cuda_ctx* ctx, float* c_full, int64_t total_units, int64_t unit_elems, int64_t u0, int64_t u1)
+{
+    const bool even = (total_units % ctx->nranks) == 0;
+    const int64_t block = (total_units + ctx->nranks - 1) / ctx->nranks;
+    if (even && u0 == 0 && u1 == block)
+    {
+        // whole blocks of equal size: one in-place all-gather
+        SC_NCCL(ctx, g_nccl.AllGather(c_full + (int64_t)ctx->rank * block * unit_elems, c_full,
+                                      (size_t)(block * unit_elems), NCCL_FLOAT32, ctx->comm, ctx->comm_stream));
+        return SUSHI_CUDA_OK;
+    }
+    // slab of each rank's block: every rank is the root of its own piece
+    SC_NCCL(ctx, g_nccl.GroupStart());
+    for (int r = 0; r < ctx->nranks; ++r)
+    {
+        int64_t first, count;
+        sushi_cuda_partition(total_units, ctx->nranks, r, &first, &count);
+        const int64_t lo = u0 < count ? u0 : count, hi = u1 < count ? u1 : count;
+        if (hi <= lo) continue;
+        float* piece = c_full + (first + lo) * unit_elems;
+        int rc = g_nccl.Broadcast(piece, piece, (size_t)((hi - lo) * unit_elems), NCCL_FLOAT32, r, ctx->comm,
+                                  ctx->comm_stream);
+        if (rc != 0) { g_nccl.GroupEnd(); return nccl_fail(ctx, rc, "ncclBroadcast"); }
+    }
+    SC_NCCL(ctx, g_nccl.GroupEnd());
+    return SUSHI_CUDA_OK;
+}
+
+int ensure_events(sushi_cuda_ctx* ctx, size_t n)
+{
+    while (ctx->slab_events.size() < n)
+    {
+        cudaEvent_t e;
+        SC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        ctx->slab_events.push_back(e);
+    }
+    return SUSHI_CUDA_OK;
+}
+
+} // namespace
+
+extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                            int64_t m, int64_t n, int64_t k, float alpha,
+                                            const float* a_local, int64_t lda,
+                                            const float* b, int64_t ldb,
+                                            float beta, float* c_full, int64_t ldc, int gather)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_row_sharded: bad context or device index");
+    const int nranks = ctx->comm ? ctx->nranks : 1, rank = ctx->comm ? ctx->rank : 0;
+    if (ctx->comm && ctx->comm_dev != dev)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_row_sharded: communicator is bound to another device");
+    int64_t first, count;
+    sushi_cuda_partition(m, nranks, rank, &first, &count);
+    // validate against the local block (lda is checked for the stored layout of the local block)
+    int rc = validate_gemm(ctx, count, n, k, a_local, lda, b, ldb, c_full, ldc, trans_a, trans_b, 0, 0, 0, 1);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    const bool do_gather = gather != 0 && nranks > 1;
+    if (do_gather && ldc != n)
+        return set_error(ctx, SUSHI_CUDA_ERR_UNSUPPORTED, "sgemm_row_sharded: gathering needs ldc == n");
+    float* c_block = c_full + first * ldc;
+    if (!do_gather)
+        return run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1);
+
+    // Slab pipeline: multiply slab s on the compute stream, exchange it on the comm stream.
+    const int64_t block = (m + nranks - 1) / nranks;
+    int64_t slabs = block / 2048;                 // >= 2048 rows per slab keeps the tile grid full
+    if (slabs < 1) slabs = 1;
+    if (slabs > 8) slabs = 8;
+    int64_t slab_rows = (block + slabs - 1) / slabs;
+    slab_rows = (slab_rows + 255) / 256 * 256;
+    slabs = (block + slab_rows - 1) / slab_rows;
+    if ((rc = ensure_events(ctx, (size_t)slabs)) != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    for (int64_t s = 0; s < slabs; ++s)
+    {
+        const int64_t u0 = s * slab_rows, u1 = (u0 + slab_rows < block) ? u0 + slab_rows : block;
+        const int64_t lo = u0 < count ? u0 : count, hi = u1 < count ? u1 : count;
+        if (hi > lo)
+        {
+            const float* a_slab = trans_a ? a_local + lo : a_local + lo * lda;
+            rc = run_gemm(ctx, *d, trans_a, trans_b, hi - lo, n, k, alpha, a_slab, lda, 0, b, ldb, 0, beta,
+                          c_block + lo * ldc, ldc, 0, 1);
+            if (rc != SUSHI_CUDA_OK) return rc;
+        }
+        SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[s], d->stream));
+        SC_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->slab_events[s], 0));
+        if ((rc = gather_slab(ctx, c_full, m, n, u0, u1)) != SUSHI_CUDA_OK) return rc;
+    }
+    // later work on the compute stream sees the gathered C
+    SC_CUDA(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->comm_done, 0));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                              int64_t m, int64_t n, int64_t k, float alpha,
+                                              const float* a_local, int64_t lda, int64_t stride_a,
+                                              const float* b_local, int64_t ldb, int64_t stride_b,
+                                              float beta, float* c_full, int64_t ldc, int64_t stride_c,
+                                              int64_t batch, int gather)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_batch_sharded: bad context or device index");
+    const int nranks = ctx->comm ? ctx->nranks : 1, rank = ctx->comm ? ctx->rank : 0;
+    if (ctx->comm && ctx->comm_dev != dev)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_batch_sharded: communicator is bound to another device");
+    int64_t first, count;
+    if (batch < 0) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_batch_sharded: negative batch");
+    sushi_cuda_partition(batch, nranks, rank, &first, &count);
+    int rc = validate_gemm(ctx, m, n, k, a_local, lda, b_local, ldb, c_full, ldc, trans_a, trans_b, stride_a,
+                           stride_b, stride_c, count);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    const bool do_gather = gather != 0 && nranks > 1;
+    if (do_gather && (ldc != n || stride_c != m * n))
+        return set_error(ctx, SUSHI_CUDA_ERR_UNSUPPORTED, "sgemm_batch_sharded: gathering needs contiguous C");
+    rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a_local, lda, stride_a, b_local, ldb, stride_b, beta,
+                  c_full + first * stride_c, ldc, stride_c, count);
+    if (rc != SUSHI_CUDA_OK || !do_gather) return rc;
+    if ((rc = ensure_events(ctx, 1)) != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[0], d->stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->slab_events[0], 0));
+    const int64_t block = (batch + nranks - 1) / nranks;
+    if ((rc = gather_slab(ctx, c_full, batch, m * n, 0, block)) != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->comm_done, 0));
+    return SUSHI_CUDA_OK;
+}
+
+// ======================================================================== harness helper
+extern "C" int sushi_cuda_fill_uniform(sushi_cuda_ctx* ctx, int dev, float* dst, int64_t count, uint64_t seed,
+                                       int64_t first_index)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || count < 0 || (count > 0 && !dst))
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "fill_uniform: bad argument");
+    if (count == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    int64_t blocks = (count + 255) / 256;
+    if (blocks > (int64_t)d->sm_count * 32) blocks = (int64_t)d->sm_count * 32;
+    fill_uniform_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(dst, count, splitmix64_host(seed), first_index);
+    ctx->launches++;
+    SC_CUDA(ctx, cudaGetLastError());
+    return SUSHI_CUDA_OK;
+}

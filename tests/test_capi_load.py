@@ -1,0 +1,71 @@
+"""The C-ABI library loads and exports every symbol include/sushiblas_cuda.h declares;
+host-only entry points behave; compute entry points fail loudly without a device.  No GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "sushiblas_cuda.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"SUSHI_CUDA_API\s+[\w\s\*]+?\b(sushi_cuda_\w+)\s*\(", text)
+
+
+def test_header_symbols_are_all_exported(lib_path):
+    names = declared_symbols()
+    assert len(names) >= 25
+    lib = ctypes.CDLL(lib_path)
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_binding_covers_the_header(lib_path):
+    from sushiblas_b200 import capi
+    assert sorted(capi.SIGNATURES) == sorted(declared_symbols())
+    capi.load_library()
+
+
+def test_partition_rule(lib_path):
+    from sushiblas_b200.capi import partition, SushiCudaError
+    assert partition(32768, 8, 3) == (12288, 4096)
+    assert partition(256, 8, 7) == (224, 32)
+    # uneven: block = ceil(10/4) = 3 -> 3,3,3,1
+    assert [partition(10, 4, r) for r in range(4)] == [(0, 3), (3, 3), (6, 3), (9, 1)]
+    # more ranks than units: trailing ranks own nothing
+    assert [partition(2, 4, r)[1] for r in range(4)] == [1, 1, 0, 0]
+    for total in (0, 1, 7, 100, 65536):
+        for nr in (1, 2, 3, 8):
+            blocks = [partition(total, nr, r) for r in range(nr)]
+            assert sum(c for _, c in blocks) == total
+            pos = 0
+            for first, count in blocks:
+                assert first == pos or count == 0
+                pos += count
+    with pytest.raises(SushiCudaError):
+        partition(10, 0, 0)
+    with pytest.raises(SushiCudaError):
+        partition(10, 2, 2)
+
+
+def test_workspace_bytes(lib_path):
+    from sushiblas_b200.capi import workspace_bytes
+    # planes: 2 (hi/lo) * ceil(k/16) * rows_pad(256) * 16 * 4 bytes per operand
+    assert workspace_bytes(4096, 4096, 4096) == 2 * (2 * 256 * 4096 * 16 * 4)
+    assert workspace_bytes(1, 1, 1) == 2 * (2 * 1 * 256 * 16 * 4)
+    assert workspace_bytes(512, 512, 512, 256) == 256 * 2 * (2 * 32 * 512 * 16 * 4)
+
+
+def test_no_device_fails_loudly(lib_path):
+    """Without a CUDA device there is no fallback: context creation reports an error."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    from sushiblas_b200 import SushiCuda, SushiCudaError
+    with pytest.raises(SushiCudaError) as e:
+        SushiCuda([0])
+    assert e.value.code in (-2, -3)

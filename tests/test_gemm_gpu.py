@@ -1,0 +1,333 @@
+"""GPU parity tests: the CUDA path through the C ABI against the fp64 oracle.
+
+Tolerance (floating point): the bound of the specification,
+    |dC_ij| <= 8*K*2^-24*(|A||B|)_ij + 2^-24*|beta*C_ij| ,
+tested against the fp64 oracle with the K term at HALF budget, so that, by the triangle
+inequality, the result is within the full K term of any conforming reference sgemm (the
+beta term is a single fp32 rounding of the output and is kept whole).  Integer-valued golden
+vectors must match bit for bit.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import ref_gemm as og
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "gemm_integer_kat.npz")
+AUTO, SIMT, TC3X = 0, 1, 2
+BUDGET = 0.5
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def run_gemm(ctx, variant, ta, tb, m, n, k, alpha, a, lda, sa, b, ldb, sb, beta, c, ldc, sc, batch):
+    """a, b, c: flat float32 numpy buffers.  Returns the flat C buffer after the call."""
+    ctx.set_gemm_variant(variant)
+    da, db, dc = dev(a), dev(b), dev(c)
+    if batch == 1 and sa == 0 and sb == 0 and sc == 0:
+        ctx.sgemm(ta, tb, m, n, k, alpha, da, lda, db, ldb, beta, dc, ldc)
+    else:
+        ctx.sgemm_strided_batched(ta, tb, m, n, k, alpha, da, lda, sa, db, ldb, sb, beta, dc, ldc, sc, batch)
+    ctx.sync()
+    ctx.set_gemm_variant(AUTO)
+    return dc.cpu().numpy()
+
+
+def make_case(seed, ta, tb, m, n, k, batch=1, pad=(0, 0, 0), dist="uniform"):
+    ar, ac = (k, m) if ta else (m, k)
+    br, bc = (n, k) if tb else (k, n)
+    lda, ldb, ldc = ac + pad[0], bc + pad[1], n + pad[2]
+    sa, sb, sc = ar * lda, br * ldb, m * ldc
+    gen = og.uniform_pm1 if dist == "uniform" else (lambda s, cnt: og.normal(s, cnt, 1.0))
+    a = gen(seed, max(1, batch * sa))
+    b = gen(seed + 1, max(1, batch * sb))
+    c = og.uniform_pm1(seed + 2, max(1, batch * sc))
+    return dict(a=a, b=b, c=c, lda=lda, ldb=ldb, ldc=ldc, sa=sa, sb=sb, sc=sc)
+
+
+def check(ctx, variant, ta, tb, m, n, k, alpha, beta, batch=1, pad=(0, 0, 0), seed=100, dist="uniform",
+          poison_c=False):
+    cs = make_case(seed, ta, tb, m, n, k, batch, pad, dist)
+    c_in = cs["c"].copy()
+    if poison_c:
+        assert beta == 0.0
+        c_in[:] = np.nan
+    out = run_gemm(ctx, variant, ta, tb, m, n, k, alpha, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"],
+                   beta, c_in, cs["ldc"], cs["sc"], batch)
+    ref, absab = og.gemm_f64_np(ta, tb, m, n, k, alpha, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"],
+                                beta, cs["c"], cs["ldc"], cs["sc"], batch)
+    got = og._view(out, m, n, cs["ldc"], cs["sc"], batch)
+    cin_v = og._view(cs["c"], m, n, cs["ldc"], cs["sc"], batch)
+    r, q = og.tolerance_ratio(got, ref, absab, k, beta=beta, c_in=cin_v, budget=BUDGET)
+    assert r <= 1.0, f"variant={variant} ta={ta} tb={tb} m={m} n={n} k={k} batch={batch}: ratio {r:.3g} (noK {q:.3g})"
+    # padding between rows / batches of C must be untouched
+    if pad[2] and not poison_c:
+        mask = np.ones(out.shape, dtype=bool)
+        idx = (np.arange(batch)[:, None, None] * cs["sc"] + np.arange(m)[None, :, None] * cs["ldc"]
+               + np.arange(n)[None, None, :]).ravel()
+        mask[idx] = False
+        assert np.array_equal(out[mask], cs["c"][mask]), "C padding was overwritten"
+    return r, q
+
+
+# ------------------------------------------------------------------ known answers
+def test_reference_kat_3x3(ctx):
+    g = np.load(GOLDEN)
+    out = run_gemm(ctx, AUTO, 0, 0, 3, 3, 3, 1.0, g["ref_simple3x3.a"], 3, 0, g["ref_simple3x3.b"], 3, 0, 0.0,
+                   g["ref_simple3x3.c_in"], 3, 0, 1)
+    assert np.array_equal(out, g["ref_simple3x3.c_out"])
+
+
+def test_reference_kat_column_major_via_operand_swap(ctx):
+    # column-major C = A*B is the row-major product C^T = B^T * A^T on the same memory images
+    g = np.load(GOLDEN)
+    out = run_gemm(ctx, AUTO, 0, 0, 2, 2, 2, 1.0, g["ref_colmajor2x2.b"], 2, 0, g["ref_colmajor2x2.a"], 2, 0, 0.0,
+                   np.zeros(4, np.float32), 2, 0, 1)
+    assert np.array_equal(out, g["ref_colmajor2x2.c_out"])
+
+
+@pytest.mark.parametrize("variant", [SIMT, TC3X])
+def test_integer_golden_bit_exact(ctx, variant):
+    g = np.load(GOLDEN)
+    for name in g["names"]:
+        ta, tb, m, n, k, alpha, beta, batch, lda, ldb, ldc, sa, sb, sc = [int(v) for v in g[f"{name}.meta"]]
+        out = run_gemm(ctx, variant, ta, tb, m, n, k, float(alpha), g[f"{name}.a"], lda, sa, g[f"{name}.b"], ldb, sb,
+                       float(beta), g[f"{name}.c_in"], ldc, sc, batch)
+        exp = g[f"{name}.c_out"]
+        bad = np.flatnonzero(out != exp)
+        assert bad.size == 0, f"{name} variant={variant}: {bad.size} mismatches, first at {bad[:5]}, " \
+                              f"got {out[bad[:5]]} want {exp[bad[:5]]}"
+
+
+# ------------------------------------------------------------------ SIMT kernel
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_simt_small_shape_sweep(ctx, ta, tb):
+    sizes = [1, 2, 3, 8, 17, 32, 33, 64, 65, 127, 129]
+    rng = np.random.default_rng(5 + 2 * ta + tb)
+    for _ in range(24):
+        m, n, k = (int(rng.choice(sizes)) for _ in range(3))
+        alpha, beta = float(rng.choice([1.0, 1.5, -0.5])), float(rng.choice([0.0, 0.5, 1.0, -1.0]))
+        pad = tuple(int(v) for v in rng.choice([0, 1, 3, 4], 3))
+        check(ctx, SIMT, ta, tb, m, n, k, alpha, beta, batch=int(rng.choice([1, 2, 5])), pad=pad,
+              seed=int(rng.integers(1, 1 << 30)))
+
+
+def test_simt_beta_zero_ignores_nan_c(ctx):
+    check(ctx, SIMT, 0, 0, 70, 50, 33, 1.0, 0.0, poison_c=True)
+    check(ctx, SIMT, 1, 1, 128, 128, 64, 2.0, 0.0, batch=2, poison_c=True)
+
+
+def test_simt_mid_sizes(ctx):
+    check(ctx, SIMT, 0, 0, 512, 384, 256, 1.0, 0.0)
+    check(ctx, SIMT, 0, 1, 1000, 300, 200, 1.5, 0.5, pad=(0, 0, 4))
+    check(ctx, SIMT, 1, 0, 256, 1024, 96, 1.0, 1.0, batch=3)
+
+
+def test_degenerate_sizes(ctx):
+    # k == 0: C <- beta*C ; alpha == 0 likewise; m or n == 0: no-op
+    c = og.uniform_pm1(9, 12)
+    out = run_gemm(ctx, AUTO, 0, 0, 3, 4, 0, 1.0, np.zeros(1, np.float32), 1, 0, np.zeros(4, np.float32), 4, 0, 0.5,
+                   c.copy(), 4, 0, 1)
+    assert np.array_equal(out, np.float32(0.5) * c)
+    out = run_gemm(ctx, AUTO, 0, 0, 3, 4, 0, 1.0, np.zeros(1, np.float32), 1, 0, np.zeros(4, np.float32), 4, 0, 0.0,
+                   np.full(12, np.nan, np.float32), 4, 0, 1)
+    assert np.array_equal(out, np.zeros(12, np.float32))
+    out = run_gemm(ctx, AUTO, 0, 0, 0, 4, 5, 1.0, np.zeros(1, np.float32), 5, 0, np.zeros(20, np.float32), 4, 0, 0.0,
+                   c.copy(), 4, 0, 1)
+    assert np.array_equal(out, c)
+
+
+def test_invalid_arguments_are_rejected(ctx):
+    from sushiblas_b200 import SushiCudaError
+    x = torch.zeros(64, device="cuda")
+    with pytest.raises(SushiCudaError) as e:
+        ctx.sgemm(0, 0, 4, 4, 4, 1.0, x, 3, x, 4, 0.0, x, 4)      # lda < k
+    assert e.value.code == -1
+    with pytest.raises(SushiCudaError):
+        ctx.sgemm(0, 0, 4, 4, 4, 1.0, x, 4, x, 4, 0.0, x, 2)      # ldc < n
+    with pytest.raises(SushiCudaError):
+        ctx.sgemm(0, 0, -1, 4, 4, 1.0, x, 4, x, 4, 0.0, x, 4)
+    with pytest.raises(SushiCudaError):
+        ctx.sgemm(0, 0, 4, 4, 4, 1.0, None, 4, x, 4, 0.0, x, 4)
+    with pytest.raises(SushiCudaError):
+        ctx.sgemm(0, 0, 4, 4, 4, 1.0, x, 4, x, 4, 0.0, x, 4, dev=3)
+
+
+# ------------------------------------------------------------------ tcgen05 3xTF32 kernel
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_tc3x_transposes_alpha_beta(ctx, ta, tb):
+    check(ctx, TC3X, ta, tb, 256, 256, 64, 1.0, 0.0)
+    check(ctx, TC3X, ta, tb, 512, 768, 320, 1.5, 0.5)
+    r, q = check(ctx, TC3X, ta, tb, 1024, 1024, 1024, 1.5, 0.5)
+    assert q < 64.0, q      # 3xTF32 keeps the error at the fp32 level, independent of K's bound
+
+
+def test_tc3x_ragged_and_padded(ctx):
+    check(ctx, TC3X, 0, 0, 300, 260, 100, 1.0, 0.0)
+    check(ctx, TC3X, 1, 0, 257, 255, 77, 2.0, -1.0, pad=(4, 0, 4))
+    check(ctx, TC3X, 0, 1, 129, 513, 130, 1.0, 1.0, pad=(1, 3, 5))      # unaligned leading dims: scalar epilogue
+    check(ctx, TC3X, 1, 1, 640, 130, 1, 1.0, 0.5)                        # k = 1
+    check(ctx, TC3X, 0, 0, 1, 1, 4096, 1.0, 0.0)                         # one element of C
+
+
+def test_tc3x_beta_zero_ignores_nan_c(ctx):
+    check(ctx, TC3X, 0, 0, 512, 512, 128, 1.0, 0.0, poison_c=True)
+
+
+def test_tc3x_batched(ctx):
+    check(ctx, TC3X, 0, 0, 512, 512, 512, 1.0, 0.0, batch=8, dist="normal")
+    check(ctx, TC3X, 1, 0, 200, 300, 150, 0.5, 2.0, batch=5)
+    check(ctx, TC3X, 0, 1, 256, 256, 256, 1.0, 1.0, batch=3, pad=(4, 4, 4))
+
+
+def test_tc3x_many_tiles_persistent(ctx):
+    # more tiles than SMs: exercises the persistent loop, the ring phases and TMEM hand-over
+    check(ctx, TC3X, 0, 0, 4096, 3072, 96, 1.0, 0.5)
+    check(ctx, TC3X, 0, 0, 256, 256, 48, 1.0, 0.0, batch=400)
+
+
+def test_auto_matches_explicit_variants(ctx):
+    # AUTO picks SIMT for small problems and TC3X for large ones; both are within tolerance
+    check(ctx, AUTO, 0, 0, 96, 80, 40, 1.0, 0.0)
+    check(ctx, AUTO, 0, 0, 2048, 2048, 512, 1.0, 0.0)
+
+
+# ------------------------------------------------------------------ benchmark configurations
+def test_config1_1024_cubed(ctx):
+    # M=N=K=1024, NN, alpha=1, beta=0, A,B ~ U[-1,1), C zero-initialised
+    for variant in (SIMT, TC3X, AUTO):
+        check(ctx, variant, 0, 0, 1024, 1024, 1024, 1.0, 0.0, seed=20240601)
+
+
+def _sampled_check(ctx, ta, tb, m, n, k, alpha, beta, a_t, b_t, c_in_t, c_out_t, rows, ldc=None):
+    """fp64 check of selected rows of a large result (device tensors, row-major dense)."""
+    rows_t = torch.as_tensor(rows, device="cuda")
+    a_rows = (a_t[:, rows_t].T if ta else a_t[rows_t, :]).double().cpu().numpy()     # len(rows) x k
+    opb = (b_t.T if tb else b_t).double().cpu().numpy()                               # k x n
+    ref = float(np.float32(alpha)) * (a_rows @ opb)
+    absab = np.abs(a_rows) @ np.abs(opb)
+    cin = None
+    if beta != 0.0:
+        cin = c_in_t[rows_t, :].double().cpu().numpy()
+        ref = ref + float(np.float32(beta)) * cin
+    got = c_out_t[rows_t, :].cpu().numpy()
+    return og.tolerance_ratio(got, ref, absab, k, beta=beta, c_in=cin, budget=BUDGET)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_config2_4096_cubed(ctx, ta, tb):
+    # M=N=K=4096, alpha=1.5, beta=0.5, A,B,C ~ U[-1,1); 256 sampled rows checked in fp64
+    n = 4096
+    a = torch.empty(n, n, device="cuda"); b = torch.empty_like(a); c = torch.empty_like(a)
+    ctx.fill_uniform(a, n * n, 20240601); ctx.fill_uniform(b, n * n, 20240602); ctx.fill_uniform(c, n * n, 20240603)
+    ctx.sync()
+    # the device generator is bit-identical to the host one
+    assert np.array_equal(a[0, :1000].cpu().numpy(), og.uniform_pm1(20240601, 1000))
+    c_in = c.clone()
+    ctx.sgemm(ta, tb, n, n, n, 1.5, a, n, b, n, 0.5, c, n)
+    ctx.sync()
+    rows = np.random.default_rng(7).choice(n, 256, replace=False)
+    r, q = _sampled_check(ctx, ta, tb, n, n, n, 1.5, 0.5, a, b, c_in, c, rows)
+    assert r <= 1.0 and q < 128.0, (r, q)
+    # linearity property over the full matrix: GEMM(2A, B, beta=0) == 2 * GEMM(A, B, beta=0) exactly
+    c1 = torch.empty_like(a); c2 = torch.empty_like(a)
+    ctx.sgemm(ta, tb, n, n, n, 1.0, a, n, b, n, 0.0, c1, n)
+    a2 = a * 2
+    ctx.sgemm(ta, tb, n, n, n, 1.0, a2, n, b, n, 0.0, c2, n)
+    ctx.sync()
+    assert torch.equal(c2, c1 * 2)
+
+
+def test_config3_batched_512(ctx):
+    # batch of 512^3 NN, alpha=1, beta=0, A,B ~ N(0,1): 32 batches checked fully in fp64, and the
+    # full 256-batch call must equal per-batch calls bit for bit (batch entries are independent)
+    m = 512; batch = 256
+    g = torch.Generator(device="cuda"); g.manual_seed(20240601)
+    a = torch.randn(batch, m, m, device="cuda", generator=g)
+    b = torch.randn(batch, m, m, device="cuda", generator=g)
+    c = torch.full((batch, m, m), float("nan"), device="cuda")
+    ctx.sgemm_strided_batched(0, 0, m, m, m, 1.0, a, m, m * m, b, m, m * m, 0.0, c, m, m * m, batch)
+    ctx.sync()
+    idx = list(range(0, batch, 8))
+    a64 = a[idx].double().cpu().numpy(); b64 = b[idx].double().cpu().numpy()
+    ref = a64 @ b64; absab = np.abs(a64) @ np.abs(b64)
+    r, q = og.tolerance_ratio(c[idx].cpu().numpy(), ref, absab, m, budget=BUDGET)
+    assert r <= 1.0 and q < 64.0, (r, q)
+    single = torch.empty(m, m, device="cuda")
+    ctx.set_gemm_variant(TC3X)
+    for i in (0, 37, 255):
+        ctx.sgemm(0, 0, m, m, m, 1.0, a[i], m, b[i], m, 0.0, single, m)
+        ctx.sync()
+        assert torch.equal(single, c[i])
+    ctx.set_gemm_variant(AUTO)
+
+
+def test_config4_tall_skinny(ctx):
+    # M=65536, N=256, K=4096, NN, A ~ U[-1,1), B ~ N(0, 0.02); 512 sampled rows in fp64
+    m, n, k = 65536, 256, 4096
+    a = torch.empty(m, k, device="cuda")
+    ctx.fill_uniform(a, m * k, 20240601); ctx.sync()
+    b = dev(og.normal(20240602, k * n, std=0.02).reshape(k, n))
+    c = torch.full((m, n), float("nan"), device="cuda")
+    ctx.sgemm(0, 0, m, n, k, 1.0, a, k, b, n, 0.0, c, n)
+    ctx.sync()
+    rows = np.random.default_rng(8).choice(m, 512, replace=False)
+    r, q = _sampled_check(ctx, 0, 0, m, n, k, 1.0, 0.0, a, b, None, c, rows)
+    assert r <= 1.0 and q < 128.0, (r, q)
+    assert bool(torch.isfinite(c).all())
+
+
+# ------------------------------------------------------------------ host-buffer entry point and storage calls
+def test_host_entry_point_matches_device_path(ctx):
+    m, n, k, batch = 300, 200, 150, 2
+    cs = make_case(55, 0, 1, m, n, k, batch, pad=(0, 0, 4))
+    c_host = cs["c"].copy()
+    ctx.sgemm_strided_batched_host(0, 1, m, n, k, 1.5, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"],
+                                   0.5, c_host, cs["ldc"], cs["sc"], batch)
+    ctx.sync()
+    out = run_gemm(ctx, AUTO, 0, 1, m, n, k, 1.5, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"], 0.5,
+                   cs["c"].copy(), cs["ldc"], cs["sc"], batch)
+    assert np.array_equal(c_host, out)
+    # beta == 0 with a padded C: the gaps between rows survive the copy back
+    c_host = cs["c"].copy()
+    ctx.sgemm_strided_batched_host(0, 1, m, n, k, 1.0, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"],
+                                   0.0, c_host, cs["ldc"], cs["sc"], batch)
+    ctx.sync()
+    v = og._view(c_host, m, cs["ldc"], cs["ldc"], cs["sc"], batch)
+    assert np.array_equal(v[:, :, n:], og._view(cs["c"], m, cs["ldc"], cs["ldc"], cs["sc"], batch)[:, :, n:])
+
+
+def test_storage_calls_round_trip(ctx):
+    nbytes = 1 << 20
+    d = ctx.malloc(nbytes)
+    h = ctx.host_alloc(nbytes)
+    import ctypes
+    src = (ctypes.c_uint8 * nbytes).from_address(h)
+    pattern = np.arange(nbytes, dtype=np.uint8)
+    np.frombuffer(src, dtype=np.uint8)[:] = pattern
+    ctx.memcpy_h2d(d, h, nbytes)
+    d2 = ctx.malloc(nbytes)
+    ctx.memcpy_d2d(d2, d, nbytes)
+    ctx.memset(d, 0, nbytes)
+    back = np.empty(nbytes, dtype=np.uint8)
+    ctx.memcpy_d2h(back, d2, nbytes)
+    zero = np.ones(nbytes, dtype=np.uint8)
+    ctx.memcpy_d2h(zero, d, nbytes)
+    ctx.sync()
+    assert np.array_equal(back, pattern) and not zero.any()
+    ctx.free(d); ctx.free(d2); ctx.host_free(h)
+
+
+def test_launch_counter_counts_kernels(ctx):
+    before = ctx.launch_count()
+    check(ctx, SIMT, 0, 0, 64, 64, 64, 1.0, 0.0)
+    mid = ctx.launch_count()
+    check(ctx, TC3X, 0, 0, 256, 256, 64, 1.0, 0.0)
+    after = ctx.launch_count()
+    assert mid - before == 1 and after - mid == 3     # split A, split B, GEMM
