@@ -28,7 +28,11 @@ def ctx(lib_path):
         pytest.skip("no CUDA device")
     torch.cuda.set_device(0)
     c = SushiCuda([0])
-    c.set_stream(torch.cuda.current_stream().cuda_stream)
+    # torch work and library kernels share one explicit stream (handle 0 of torch's default
+    # stream would select the context's own stream instead)
+    s = torch.cuda.Stream()
+    torch.cuda.set_stream(s)
+    c.set_stream(s.cuda_stream)
     yield c
     torch.cuda.synchronize()
     c.close()
