@@ -34,8 +34,8 @@ UNIT = "TFLOP/s"
 SEED = 20240601
 
 # DRAM bytes per launch of the dominant kernel from the committed ncu capture
-# (profiles/sgemm_tc3x_4096.md); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"sgemm_4096_nn_nt_tn_tt": None}
+# (profiles/sgemm_tc3x_4096_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum); None where no capture exists.
+NCU_TRAFFIC_BYTES = {"sgemm_4096_nn_nt_tn_tt": 592.1e6}
 
 
 def log(*a):
