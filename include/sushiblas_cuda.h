@@ -142,6 +142,36 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched_host(sushi_cuda_ctx* ctx, in
 SUSHI_CUDA_API int sushi_cuda_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, size_t* bytes);
 SUSHI_CUDA_API int sushi_cuda_reserve_workspace(sushi_cuda_ctx* ctx, int dev, size_t bytes);
 
+/* Allocation-free variant of sushi_cuda_sgemm (no counterpart in the reference).
+ *
+ * Some hosts cannot let a library allocate device memory at call time: an application whose own
+ * pool already owns the whole GPU, a thread running while another one is capturing a CUDA graph
+ * (cudaMalloc is refused during a global-mode capture), or a latency-critical loop that cannot
+ * afford the device-wide synchronisation an allocation implies.  This entry point needs no
+ * context and calls no cudaMalloc / cudaFree / allocating routine: the hi/lo operand planes of
+ * the 3xTF32 kernel live in a fixed SUSHI_CUDA_STATIC_SCRATCH_BYTES array that is part of the
+ * library image (every GPU that loads the library holds it until the process exits).
+ *
+ *  - Runs on the CURRENT device, on `cuda_stream` (a cudaStream_t as void*; NULL = default
+ *    stream), asynchronously; always the tensor-core 3xTF32 kernel.
+ *  - Limit: 8 * (pad256(m) + pad256(n)) * pad16(k) bytes must fit the scratch (pad = round up);
+ *    e.g. 1024 x 1024 x 2048 fits, 2048^3 does not.  Larger problems return
+ *    SUSHI_CUDA_ERR_UNSUPPORTED with the sizes in sushi_cuda_last_error(NULL).
+ *  - The first call on each device resolves the scratch address (one-time set-up); make that
+ *    call before any stream capture begins.
+ *  - All calls on a device share the one scratch array: calls that may overlap on the GPU
+ *    (different streams, no ordering between them) race and give wrong results; order them.
+ *    Nothing is assumed about the array's previous contents.
+ *  - `status_dev` (optional, device memory, 4 bytes): set to 0 by the call and to a non-zero
+ *    code by the kernel if one of its bounded waits expired (C is then incomplete).          */
+#define SUSHI_CUDA_STATIC_SCRATCH_BYTES (32u << 20)
+SUSHI_CUDA_API int sushi_cuda_sgemm_static_scratch(void* cuda_stream, int trans_a, int trans_b,
+                                                   int64_t m, int64_t n, int64_t k, float alpha,
+                                                   const float* a, int64_t lda,
+                                                   const float* b, int64_t ldb,
+                                                   float beta, float* c, int64_t ldc,
+                                                   int* status_dev);
+
 /* ---- multi-GPU layer (one process per GPU) --------------------------------------------
  * No counterpart in the reference (it has no collective call site); the partitioning
  * follows the independence of C's row blocks / batch entries in the calls above.

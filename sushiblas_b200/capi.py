@@ -58,6 +58,8 @@ SIGNATURES = {
                                             _f32, _vp, _i64, _int]),
     "sushi_cuda_sgemm_batch_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                               _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
+    "sushi_cuda_sgemm_static_scratch": (_int, [_vp, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
+                                               _f32, _vp, _i64, _vp]),
     "sushi_cuda_fill_uniform": (_int, [_vp, _int, _vp, _i64, ctypes.c_uint64, _i64]),
 }
 
@@ -106,6 +108,19 @@ def workspace_bytes(m: int, n: int, k: int, batch: int = 1) -> int:
     if rc != 0:
         raise SushiCudaError(rc, lib.sushi_cuda_last_error(None).decode())
     return out.value
+
+
+STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def sgemm_static_scratch(stream_ptr, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc, status_dev=None):
+    """Allocation-free GEMM on the current device (no context): operand planes live in the
+    library's fixed scratch array.  See include/sushiblas_cuda.h for the limits."""
+    lib = load_library()
+    rc = lib.sushi_cuda_sgemm_static_scratch(stream_ptr, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda,
+                                             _addr(b), ldb, beta, _addr(c), ldc, _addr(status_dev))
+    if rc != 0:
+        raise SushiCudaError(rc, lib.sushi_cuda_last_error(None).decode())
 
 
 def _addr(x) -> Optional[int]:

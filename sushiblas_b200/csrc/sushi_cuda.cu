@@ -828,3 +828,84 @@ extern "C" int sushi_cuda_fill_uniform(sushi_cuda_ctx* ctx, int dev, float* dst,
     SC_CUDA(ctx, cudaGetLastError());
     return SUSHI_CUDA_OK;
 }
+
+// ======================================================================== allocation-free variant
+// Scratch for sushi_cuda_sgemm_static_scratch.  In host code these names are host-side stand-ins
+// for the device symbols, never device addresses: the addresses handed to kernels come from
+// cudaGetSymbolAddress, resolved once per device with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[SUSHI_CUDA_STATIC_SCRATCH_BYTES];
+static __device__ int g_static_status;
+
+namespace {
+struct StaticScratchDevice
+{
+    bool ready = false;
+    float* scratch = nullptr;
+    int* status = nullptr;
+    int sm_count = 0;
+};
+constexpr int STATIC_MAX_DEVICES = 64;
+StaticScratchDevice g_static_dev[STATIC_MAX_DEVICES];
+std::mutex g_static_mutex;
+} // namespace
+
+extern "C" int sushi_cuda_sgemm_static_scratch(void* cuda_stream, int trans_a, int trans_b,
+                                               int64_t m, int64_t n, int64_t k, float alpha,
+                                               const float* a, int64_t lda, const float* b, int64_t ldb,
+                                               float beta, float* c, int64_t ldc, int* status_dev)
+{
+    int rc = validate_gemm(nullptr, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, 0, 0, 0, 1);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    int device = -1;
+    SC_CUDA(nullptr, cudaGetDevice(&device));
+    if (device < 0 || device >= STATIC_MAX_DEVICES)
+        return set_error(nullptr, SUSHI_CUDA_ERR_UNSUPPORTED, "sgemm_static_scratch: device index out of range");
+    StaticScratchDevice& sd = g_static_dev[device];
+    {
+        // one-time set-up for this device: resolve the device addresses of the static symbols
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!sd.ready)
+        {
+            void* p = nullptr;
+            SC_CUDA(nullptr, cudaGetSymbolAddress(&p, g_static_scratch));
+            sd.scratch = static_cast<float*>(p);
+            SC_CUDA(nullptr, cudaGetSymbolAddress(&p, g_static_status));
+            sd.status = static_cast<int*>(p);
+            SC_CUDA(nullptr, cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, device));
+            sd.ready = true;
+        }
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    int* status = status_dev ? status_dev : sd.status;
+    if (m == 0 || n == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(nullptr, cudaMemsetAsync(status, 0, sizeof(int), st));       // must start at zero
+    if (k == 0 || alpha == 0.0f)
+    {
+        if (beta == 1.0f) return SUSHI_CUDA_OK;
+        int64_t blocks = (m * n + 255) / 256;
+        if (blocks > (int64_t)sd.sm_count * 16) blocks = (int64_t)sd.sm_count * 16;
+        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, st>>>(c, m, n, ldc, 0, 1, beta);
+        SC_CUDA(nullptr, cudaGetLastError());
+        return SUSHI_CUDA_OK;
+    }
+    const size_t bytes_a = sushi::split_plane_bytes(m, k, 1);
+    const size_t bytes_b = sushi::split_plane_bytes(n, k, 1);
+    if (bytes_a + bytes_b > (size_t)SUSHI_CUDA_STATIC_SCRATCH_BYTES)
+    {
+        char msg[256];
+        snprintf(msg, sizeof msg,
+                 "sgemm_static_scratch: m=%lld n=%lld k=%lld needs %zu bytes of operand planes, the static scratch "
+                 "holds %u; use sushi_cuda_sgemm (context-owned scratch) for this size",
+                 (long long)m, (long long)n, (long long)k, bytes_a + bytes_b, (unsigned)SUSHI_CUDA_STATIC_SCRATCH_BYTES);
+        return set_error(nullptr, SUSHI_CUDA_ERR_UNSUPPORTED, msg);
+    }
+    // The pre-pass writes every byte of the planes it hands to the GEMM (padding included), so
+    // whatever an earlier call left in the array is never read.
+    float* planes_a = sd.scratch;
+    float* planes_b = reinterpret_cast<float*>(reinterpret_cast<char*>(sd.scratch) + bytes_a);
+    SC_CUDA(nullptr, sushi::launch_split_tf32(a, planes_a, m, k, lda, 0, 1, /*k_contig=*/!trans_a, sd.sm_count, st));
+    SC_CUDA(nullptr, sushi::launch_split_tf32(b, planes_b, n, k, ldb, 0, 1, /*k_contig=*/trans_b != 0, sd.sm_count, st));
+    SC_CUDA(nullptr, sushi::tc3x::launch_sgemm_tc3x(planes_a, planes_b, c, m, n, k, ldc, 0, 1, alpha, beta, status,
+                                                   sd.sm_count, st));
+    return SUSHI_CUDA_OK;
+}
