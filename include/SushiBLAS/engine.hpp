@@ -1,0 +1,156 @@
+// engine.hpp -- entry object of the library (reference: include/SushiBLAS/engine.hpp:61-194,
+// src/engine.cpp:35-69): holds the runtime context, the deferred task graph, the default
+// layout and the RNG seed; hands out tensors and the BLAS facade.  Only blas() is provided:
+// the other op families of the reference are outside the fp32 GEMM path.
+#pragma once
+
+#include <atomic>
+#include <cstdint>
+#include <initializer_list>
+#include <vector>
+
+#include <SushiBLAS/core/common.hpp>
+#include <SushiBLAS/core/logger.hpp>
+#include <SushiBLAS/ops/blas.hpp>
+#include <SushiBLAS/storage.hpp>
+#include <SushiBLAS/tensor.hpp>
+#include <SushiRuntime/SushiRuntime.h>
+
+namespace SushiBLAS
+{
+    class Engine
+    {
+        public:
+            Engine(SushiRuntime::Execution::RuntimeContext& ctx, Core::Layout layout = Core::Layout::ROW_MAJOR)
+                : context_(ctx), graph_(ctx), default_layout_(layout)
+            {
+                SB_LOG_INFO("SushiBLAS Engine initialized with {} layout.",
+                            layout == Core::Layout::ROW_MAJOR ? "Row-Major" : "Column-Major");
+            }
+
+            Core::Layout get_layout() const { return default_layout_; }
+
+            BLASOps blas() { return BLASOps(*this); }
+
+            SushiRuntime::Execution::RuntimeContext& get_context() { return context_; }
+            SushiRuntime::Graph::TaskGraph& get_graph() { return graph_; }
+
+            /// Enqueues every recorded task on the device stream.  wait() on the result blocks
+            /// until they have run and throws std::runtime_error if any failed.
+            SushiRuntime::Execution::Event execute() { return graph_.execute(); }
+
+            /// New FLOAT32 tensor; memory is not initialised (engine.cpp:42-46).
+            Tensor create_tensor(std::initializer_list<int64_t> dims,
+                                 SushiRuntime::Memory::AllocStrategy strat = SushiRuntime::Memory::AllocStrategy::SHARED)
+            {
+                return create_tensor(dims, Core::DataType::FLOAT32, strat);
+            }
+
+            /// New tensor of `dtype`: one Storage of prod(dims) * bytes-per-element, contiguous in
+            /// the engine's default layout (engine.cpp:48-69).
+            Tensor create_tensor(std::initializer_list<int64_t> dims, Core::DataType dtype,
+                                 SushiRuntime::Memory::AllocStrategy strat = SushiRuntime::Memory::AllocStrategy::SHARED)
+            {
+                std::size_t elements = 1;
+                for (int64_t d : dims) elements *= static_cast<std::size_t>(d);
+                std::size_t bytes_per_element = 4;
+                if (dtype == Core::DataType::FLOAT64 || dtype == Core::DataType::COMPLEX32) bytes_per_element = 8;
+                else if (dtype == Core::DataType::COMPLEX64) bytes_per_element = 16;
+                else if (dtype == Core::DataType::HALF) bytes_per_element = 2;
+                auto storage = SushiRuntime::make_sushi<Storage>(context_.get_allocator(), elements * bytes_per_element, strat);
+                Tensor t(storage, dims, 0, default_layout_);
+                t.dtype = dtype;
+                return t;
+            }
+
+            void set_seed(uint64_t s) { seed_ = s; }
+            uint64_t get_seed() const { return seed_; }
+            uint64_t get_and_increment_rng_offset() { return rng_offset_++; }
+
+        private:
+            SushiRuntime::Execution::RuntimeContext& context_;
+            SushiRuntime::Graph::TaskGraph graph_;
+            Core::Layout default_layout_;
+            uint64_t seed_ = 0;
+            std::atomic<uint64_t> rng_offset_{0};
+    };
+
+    // ---------------------------------------------------------------- Level3::gemm
+    inline SushiRuntime::Execution::Event Level3::gemm(const Tensor& A, const Tensor& B, Tensor& C, bool transA,
+                                                       bool transB, float alpha, float beta)
+    {
+        using namespace SushiRuntime::Graph::Literals;
+        const detail::GemmCall user = detail::derive_gemm_call(A, B, C, transA, transB, alpha, beta);
+        SB_THROW_IF(A.dtype != Core::DataType::FLOAT32,
+                    "Unsupported data type for GEMM operation (the CUDA backend serves FLOAT32 only).");
+
+        bool swapped = false;
+        const detail::GemmCall g = detail::row_major_equivalent(user, &swapped);
+        const Tensor& first = swapped ? B : A;       // operand in the "A" position of the row-major call
+        const Tensor& second = swapped ? A : B;
+
+        struct Operand
+        {
+            SushiRuntime::sushi_ptr<Storage> storage;   // keeps the block alive until the task has run
+            float* ptr;                                 // tensor.data(): host (SHARED/HOST) or device (DEVICE)
+            int64_t extent;                             // elements the call may touch from ptr
+            bool host;
+        };
+        auto describe = [](const Tensor& t, int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t batch) {
+            Operand o{t.storage, t.data_as<float>(), detail::operand_extent(rows, cols, ld, stride, batch), false};
+            o.host = t.storage->host_resident();
+            const std::size_t need = (static_cast<std::size_t>(t.storage_offset) + static_cast<std::size_t>(o.extent)) * sizeof(float);
+            SB_THROW_IF(need > t.storage->size_bytes,
+                        "GEMM operand does not fit its storage (needs {} bytes, has {}).", need, t.storage->size_bytes);
+            return o;
+        };
+        Operand oa = describe(first, g.trans_a ? g.k : g.m, g.trans_a ? g.m : g.k, g.lda, g.stride_a, g.batch);
+        Operand ob = describe(second, g.trans_b ? g.n : g.k, g.trans_b ? g.k : g.n, g.ldb, g.stride_b, g.batch);
+        Operand oc = describe(C, g.m, g.n, g.ldc, g.stride_c, g.batch);
+
+        // dependency sets name the storage base pointers, as in gemm.cpp:112-120
+        std::vector<void*> reads = {A.storage->data_ptr, B.storage->data_ptr};
+        std::vector<void*> writes = {C.storage->data_ptr};
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = "blas.lvl3.gemm";
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = "blas.lvl3.gemm"_op;
+        meta.set_param(0, alpha);
+        meta.set_param(1, beta);
+        meta.set_param(2, transA);
+        meta.set_param(3, transB);
+
+        engine_.get_graph().add_task(meta, reads, writes,
+            [g, oa, ob, oc](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            {
+                sushi_cuda_ctx* ctx = rt.native_handle();
+                // device address of an operand; host-resident operands are staged through their mirror
+                auto on_device = [ctx](const Operand& o, bool upload, float** out) -> int
+                {
+                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
+                    if (!base) return SUSHI_CUDA_ERR_OOM;
+                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) -
+                                                            static_cast<char*>(o.storage->data_ptr)));
+                    if (o.host && upload && o.extent > 0)
+                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
+                    return SUSHI_CUDA_OK;
+                };
+                float *da = nullptr, *db = nullptr, *dc = nullptr;
+                int rc = on_device(oa, true, &da);
+                if (rc == SUSHI_CUDA_OK) rc = on_device(ob, true, &db);
+                // C goes up when it is read (beta != 0) or when the call leaves gaps in it
+                const bool dense_c = (g.ldc == g.n) && (g.batch == 1 || g.stride_c == g.m * g.n);
+                if (rc == SUSHI_CUDA_OK) rc = on_device(oc, g.beta != 0.0f || !dense_c, &dc);
+                if (rc != SUSHI_CUDA_OK) return rc;
+                SB_LOG_INFO("CUDA GEMM [Row-Major]: {}x[{}x{}x{}]", g.batch, g.m, g.n, g.k);
+                rc = sushi_cuda_sgemm_strided_batched(ctx, 0, g.trans_a, g.trans_b, g.m, g.n, g.k, g.alpha, da, g.lda,
+                                                      g.stride_a, db, g.ldb, g.stride_b, g.beta, dc, g.ldc, g.stride_c,
+                                                      g.batch);
+                if (rc == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
+                    rc = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
+                return rc;
+            });
+        return SushiRuntime::Execution::Event();
+    }
+} // namespace SushiBLAS

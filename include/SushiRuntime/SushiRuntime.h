@@ -1,0 +1,413 @@
+// SushiRuntime.h -- the small public surface of the runtime that SushiBLAS callers touch,
+// rewritten for the CUDA backend (no SYCL).  One header, header-only.
+//
+// What is kept, with the reference's spellings so that caller code compiles unchanged:
+//   sr::Core::RefCounted, sr::sushi_ptr<T>, sr::make_sushi<T>     (include/SushiRuntime/core/ref_counted.hpp:38-80,
+//                                                                  core/sushi_ptr.hpp:38-143)
+//   sr::Core::DEFAULT_ALIGNMENT, MAX_SUPPORTED_XPU                (core/common.hpp:40-53)
+//   sr::Memory::AllocStrategy, sr::Memory::USMAllocator           (memory/usm_allocator.hpp:33-71)
+//   sr::Graph::TaskType / OpID / "_op" / TaskMetadata / TaskGraph (graph/task_types.hpp:35-129,
+//                                                                  graph/task_graph.hpp:55-125)
+//   sr::Execution::RuntimeContext                                 (execution/runtime_context.hpp:42-96)
+// What changes: sycl::queue / sycl::event are gone.  A RuntimeContext owns one sushi_cuda_ctx
+// (C ABI, include/sushiblas_cuda.h) with one in-order stream; TaskGraph is a deferred list of
+// closures replayed in submission order on that stream, which satisfies every read/write
+// dependency the reference infers from pointer sets; execute() returns an Event whose wait()
+// synchronises the stream and raises std::runtime_error on any recorded failure.
+// The work-stealing scheduler, the dependency tracker, the memory pool and the NUMA/topology
+// layers of the reference are not rebuilt.
+#pragma once
+
+#include <atomic>
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+#include <unordered_map>
+#include <utility>
+#include <vector>
+
+#include "../sushiblas_cuda.h"
+
+namespace SushiRuntime
+{
+    namespace Core
+    {
+        inline constexpr std::size_t DEFAULT_ALIGNMENT = 128;
+        inline constexpr std::size_t MAX_SUPPORTED_XPU = 16;
+
+        /// Intrusive reference count; objects are deleted when the count drops to zero.
+        class RefCounted
+        {
+            public:
+                RefCounted() = default;
+                RefCounted(const RefCounted&) = delete;
+                RefCounted& operator=(const RefCounted&) = delete;
+
+                void add_ref() const noexcept { refs_.fetch_add(1, std::memory_order_relaxed); }
+                void release() const noexcept
+                {
+                    if (refs_.fetch_sub(1, std::memory_order_acq_rel) == 1) delete this;
+                }
+                std::uint32_t ref_count() const noexcept { return refs_.load(std::memory_order_acquire); }
+
+            protected:
+                virtual ~RefCounted() = default;
+
+            private:
+                mutable std::atomic<std::uint32_t> refs_{0};
+        };
+    } // namespace Core
+
+    /// Smart pointer for RefCounted objects.
+    template <typename T>
+    class sushi_ptr
+    {
+        public:
+            sushi_ptr() noexcept = default;
+            sushi_ptr(std::nullptr_t) noexcept {}
+            explicit sushi_ptr(T* p) noexcept : p_(p) { acquire(); }
+            sushi_ptr(const sushi_ptr& o) noexcept : p_(o.p_) { acquire(); }
+            sushi_ptr(sushi_ptr&& o) noexcept : p_(o.p_) { o.p_ = nullptr; }
+            template <typename U, typename = std::enable_if_t<std::is_convertible_v<U*, T*>>>
+            sushi_ptr(const sushi_ptr<U>& o) noexcept : p_(o.get()) { acquire(); }
+            ~sushi_ptr() { drop(); }
+
+            sushi_ptr& operator=(const sushi_ptr& o) noexcept
+            {
+                if (p_ != o.p_) { drop(); p_ = o.p_; acquire(); }
+                return *this;
+            }
+            sushi_ptr& operator=(sushi_ptr&& o) noexcept
+            {
+                if (this != &o) { drop(); p_ = o.p_; o.p_ = nullptr; }
+                return *this;
+            }
+            sushi_ptr& operator=(std::nullptr_t) noexcept { drop(); p_ = nullptr; return *this; }
+
+            T* get() const noexcept { return p_; }
+            T* operator->() const noexcept { return p_; }
+            T& operator*() const noexcept { return *p_; }
+            explicit operator bool() const noexcept { return p_ != nullptr; }
+            void reset() noexcept { drop(); p_ = nullptr; }
+
+            friend bool operator==(const sushi_ptr& a, const sushi_ptr& b) noexcept { return a.p_ == b.p_; }
+            friend bool operator!=(const sushi_ptr& a, const sushi_ptr& b) noexcept { return a.p_ != b.p_; }
+            friend bool operator==(const sushi_ptr& a, std::nullptr_t) noexcept { return a.p_ == nullptr; }
+            friend bool operator!=(const sushi_ptr& a, std::nullptr_t) noexcept { return a.p_ != nullptr; }
+
+        private:
+            void acquire() const noexcept { if (p_) p_->add_ref(); }
+            void drop() const noexcept { if (p_) p_->release(); }
+            T* p_ = nullptr;
+    };
+
+    template <typename T, typename... Args>
+    sushi_ptr<T> make_sushi(Args&&... args)
+    {
+        return sushi_ptr<T>(new T(std::forward<Args>(args)...));
+    }
+
+    namespace Memory
+    {
+        /// Where a tensor's bytes live.  With cudaMalloc storage and explicit staging:
+        ///  DEVICE: device memory only; data() is a device pointer.
+        ///  SHARED: pinned host image the caller reads/writes, mirrored by a device buffer that
+        ///          operations stage through (upload before use, download after a write).
+        ///  HOST:   pinned host image, staged the same way.
+        enum class AllocStrategy
+        {
+            DEVICE,
+            SHARED,
+            HOST
+        };
+
+        /// Allocation interface handed to Storage.  allocate()/deallocate() keep the reference's
+        /// meaning; the three staging queries replace "which sycl::device owns this pointer".
+        class USMAllocator : public Core::RefCounted
+        {
+            public:
+                virtual void* allocate(std::size_t bytes, AllocStrategy strategy = AllocStrategy::SHARED,
+                                       std::size_t alignment = Core::DEFAULT_ALIGNMENT) = 0;
+                virtual void deallocate(void* ptr) = 0;
+
+                /// True when `ptr` (an allocation base) is dereferenceable on the host.
+                virtual bool is_host_resident(void* ptr) = 0;
+                /// Device buffer backing `ptr`: the pointer itself for DEVICE allocations, a lazily
+                /// created device mirror of equal size for SHARED / HOST ones; nullptr if unknown.
+                virtual void* device_view(void* ptr) = 0;
+                /// Native context the allocation belongs to (nullptr for host-only test allocators).
+                virtual sushi_cuda_ctx* native_context() { return nullptr; }
+
+            protected:
+                ~USMAllocator() override = default;
+        };
+    } // namespace Memory
+
+    namespace Graph
+    {
+        enum class TaskType : std::uint8_t
+        {
+            NONE = 0,
+            MATH_OP,
+            MEMORY_COPY,
+            CUSTOM_HOST,
+            CONTROL_FLOW
+        };
+
+        /// Operation identifier: 32-bit FNV-1a hash of the operation's dotted name.
+        struct OpID
+        {
+            std::uint32_t value;
+
+            constexpr OpID() : value(0) {}
+            constexpr explicit OpID(std::uint32_t v) : value(v) {}
+
+            static constexpr std::uint32_t hash_str(const char* s, std::size_t n)
+            {
+                std::uint32_t h = 0x811C9DC5u;           // FNV offset basis
+                for (std::size_t i = 0; i < n; ++i)
+                {
+                    h ^= static_cast<std::uint8_t>(s[i]);
+                    h *= 0x01000193u;                    // FNV prime
+                }
+                return h;
+            }
+
+            constexpr bool operator==(const OpID& o) const { return value == o.value; }
+            constexpr bool operator!=(const OpID& o) const { return value != o.value; }
+            constexpr bool operator<(const OpID& o) const { return value < o.value; }
+        };
+
+        namespace Literals
+        {
+            constexpr OpID operator""_op(const char* s, std::size_t n) { return OpID(OpID::hash_str(s, n)); }
+        }
+
+        /// Name, category, id and up to eight 64-bit scalar parameters of a task.
+        struct TaskMetadata
+        {
+            const char* name = "unnamed_task";
+            TaskType task_type = TaskType::NONE;
+            OpID op_id = OpID(0);
+
+            static constexpr std::size_t K_MAX_PARAMS = 8;
+            std::uint64_t params[K_MAX_PARAMS] = {0};
+
+            template <typename T>
+            void set_param(int index, T value)
+            {
+                static_assert(std::is_trivially_copyable_v<T> && sizeof(T) <= sizeof(std::uint64_t));
+                if (index < 0 || index >= static_cast<int>(K_MAX_PARAMS)) return;
+                params[index] = 0;
+                std::memcpy(&params[index], &value, sizeof(T));
+            }
+
+            template <typename T>
+            T get_param(int index) const
+            {
+                static_assert(std::is_trivially_copyable_v<T> && sizeof(T) <= sizeof(std::uint64_t));
+                T value{};
+                if (index >= 0 && index < static_cast<int>(K_MAX_PARAMS)) std::memcpy(&value, &params[index], sizeof(T));
+                return value;
+            }
+        };
+    } // namespace Graph
+
+    namespace Execution
+    {
+        class RuntimeContext;
+
+        /// Completion handle returned by TaskGraph::execute() / Engine::execute().
+        /// A default-constructed Event is already complete (what the reference's op calls return).
+        class Event
+        {
+            public:
+                Event() = default;
+                explicit Event(RuntimeContext* ctx) : ctx_(ctx) {}
+                /// Blocks until the context's stream has drained; throws std::runtime_error on failure.
+                inline void wait();
+
+            private:
+                RuntimeContext* ctx_ = nullptr;
+        };
+
+        namespace detail
+        {
+            /// cudaMalloc / pinned-host allocator bound to one sushi_cuda_ctx.
+            class CudaAllocator final : public Memory::USMAllocator
+            {
+                public:
+                    explicit CudaAllocator(sushi_cuda_ctx* ctx) : ctx_(ctx) {}
+
+                    void* allocate(std::size_t bytes, Memory::AllocStrategy strategy, std::size_t) override
+                    {
+                        void* p = nullptr;
+                        const int rc = (strategy == Memory::AllocStrategy::DEVICE)
+                                           ? sushi_cuda_malloc(ctx_, 0, bytes, &p)
+                                           : sushi_cuda_host_alloc(ctx_, bytes, &p);
+                        if (rc != SUSHI_CUDA_OK) return nullptr;
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        blocks_[p] = Block{bytes, strategy, nullptr};
+                        return p;
+                    }
+
+                    void deallocate(void* ptr) override
+                    {
+                        Block b;
+                        {
+                            std::lock_guard<std::mutex> lock(mutex_);
+                            auto it = blocks_.find(ptr);
+                            if (it == blocks_.end()) return;
+                            b = it->second;
+                            blocks_.erase(it);
+                        }
+                        // queued work may still reference the block
+                        sushi_cuda_sync(ctx_, 0);
+                        if (b.strategy == Memory::AllocStrategy::DEVICE) sushi_cuda_free(ctx_, 0, ptr);
+                        else
+                        {
+                            if (b.mirror) sushi_cuda_free(ctx_, 0, b.mirror);
+                            sushi_cuda_host_free(ctx_, ptr);
+                        }
+                    }
+
+                    bool is_host_resident(void* ptr) override
+                    {
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        auto it = blocks_.find(ptr);
+                        return it != blocks_.end() && it->second.strategy != Memory::AllocStrategy::DEVICE;
+                    }
+
+                    void* device_view(void* ptr) override
+                    {
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        auto it = blocks_.find(ptr);
+                        if (it == blocks_.end()) return nullptr;
+                        Block& b = it->second;
+                        if (b.strategy == Memory::AllocStrategy::DEVICE) return ptr;
+                        if (!b.mirror && sushi_cuda_malloc(ctx_, 0, b.bytes, &b.mirror) != SUSHI_CUDA_OK) return nullptr;
+                        return b.mirror;
+                    }
+
+                    sushi_cuda_ctx* native_context() override { return ctx_; }
+
+                private:
+                    struct Block { std::size_t bytes; Memory::AllocStrategy strategy; void* mirror; };
+                    sushi_cuda_ctx* ctx_;
+                    std::mutex mutex_;
+                    std::unordered_map<void*, Block> blocks_;
+            };
+        } // namespace detail
+
+        /// Owns the device context.  Construction needs a CUDA device (sm_100a): there is no CPU
+        /// fallback, so it throws std::runtime_error otherwise.  The device is device 0 or the
+        /// one named by $SUSHI_CUDA_DEVICE.
+        class RuntimeContext
+        {
+            public:
+                RuntimeContext()
+                {
+                    const int rc = sushi_cuda_init(nullptr, 0, &ctx_);
+                    if (rc != SUSHI_CUDA_OK)
+                        throw std::runtime_error(std::string("RuntimeContext: cannot create the CUDA context: ") +
+                                                 sushi_cuda_last_error(nullptr));
+                    allocator_ = make_sushi<detail::CudaAllocator>(ctx_);
+                }
+
+                ~RuntimeContext()
+                {
+                    allocator_.reset();
+                    if (ctx_) sushi_cuda_destroy(ctx_);
+                }
+
+                RuntimeContext(const RuntimeContext&) = delete;
+                RuntimeContext& operator=(const RuntimeContext&) = delete;
+
+                /// Kept for source compatibility; the single device is found at construction.
+                void probe_hardware() {}
+
+                sushi_ptr<Memory::USMAllocator> get_allocator() { return allocator_; }
+                sushi_ptr<Memory::USMAllocator> get_allocator(int /*numa_id*/) { return allocator_; }
+
+                /// Global synchronisation; throws std::runtime_error if anything queued has failed.
+                void wait_all()
+                {
+                    const int rc = sushi_cuda_sync(ctx_, 0);
+                    if (rc != SUSHI_CUDA_OK)
+                        throw std::runtime_error(std::string("wait_all: ") + sushi_cuda_last_error(ctx_));
+                }
+
+                /// The C-ABI handle (for the op front-ends).
+                sushi_cuda_ctx* native_handle() const { return ctx_; }
+
+            private:
+                sushi_cuda_ctx* ctx_ = nullptr;
+                sushi_ptr<Memory::USMAllocator> allocator_;
+        };
+
+        inline void Event::wait()
+        {
+            if (ctx_) ctx_->wait_all();
+        }
+    } // namespace Execution
+
+    namespace Graph
+    {
+        /// Work item of a task: enqueue onto the context's stream, return a sushi_cuda status.
+        using HostWork = std::function<int(Execution::RuntimeContext&)>;
+
+        /// Deferred task list.  add_task() records; execute() replays in order on the stream.
+        class TaskGraph
+        {
+            public:
+                explicit TaskGraph(Execution::RuntimeContext& ctx) : ctx_(ctx) {}
+                TaskGraph(const TaskGraph&) = delete;
+                TaskGraph& operator=(const TaskGraph&) = delete;
+
+                void add_task(const TaskMetadata& meta, const std::vector<void*>& read_access,
+                              const std::vector<void*>& write_access, HostWork work)
+                {
+                    tasks_.push_back(Task{meta, read_access, write_access, std::move(work)});
+                }
+
+                /// Number of tasks recorded and not yet executed.
+                std::size_t pending() const { return tasks_.size(); }
+                /// Metadata of a pending task (profilers / tests).
+                const TaskMetadata& metadata(std::size_t i) const { return tasks_.at(i).meta; }
+                const std::vector<void*>& reads(std::size_t i) const { return tasks_.at(i).reads; }
+                const std::vector<void*>& writes(std::size_t i) const { return tasks_.at(i).writes; }
+
+                /// Enqueues every pending task; the returned Event completes when the stream drains.
+                Execution::Event execute()
+                {
+                    std::vector<Task> run;
+                    run.swap(tasks_);
+                    for (Task& t : run)
+                    {
+                        const int rc = t.work(ctx_);
+                        if (rc != SUSHI_CUDA_OK)
+                            throw std::runtime_error(std::string(t.meta.name) + ": " +
+                                                     sushi_cuda_last_error(ctx_.native_handle()));
+                    }
+                    return Execution::Event(&ctx_);
+                }
+
+            private:
+                struct Task
+                {
+                    TaskMetadata meta;
+                    std::vector<void*> reads, writes;
+                    HostWork work;
+                };
+                Execution::RuntimeContext& ctx_;
+                std::vector<Task> tasks_;
+        };
+    } // namespace Graph
+} // namespace SushiRuntime
+
+namespace sr = SushiRuntime;

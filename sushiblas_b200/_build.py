@@ -49,3 +49,28 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         "-o", LIB_PATH, os.path.join(CSRC, "sushi_cuda.cu"), "-ldl"]
     subprocess.check_call(cmd, cwd=ROOT)
     return LIB_PATH
+
+
+CPP_TESTS = ("test_host_logic", "test_engine_gemm")
+CPP_BIN_DIR = os.path.join(ROOT, "tests", "cpp", "bin")
+
+
+def build_cpp_tests(force: bool = False) -> dict:
+    """Compile the C++ API tests (g++ -std=c++20) against the in-tree headers and library."""
+    build_library()
+    os.makedirs(CPP_BIN_DIR, exist_ok=True)
+    gxx = shutil.which("g++") or "g++"
+    out = {}
+    headers = []
+    for base, _, files in os.walk(os.path.join(ROOT, "include")):
+        headers += [os.path.join(base, f) for f in files]
+    for name in CPP_TESTS:
+        src = os.path.join(ROOT, "tests", "cpp", name + ".cpp")
+        exe = os.path.join(CPP_BIN_DIR, name)
+        deps = [src, os.path.join(ROOT, "tests", "cpp", "check.hpp"), LIB_PATH] + headers
+        if force or not os.path.exists(exe) or any(os.path.getmtime(d) > os.path.getmtime(exe) for d in deps):
+            subprocess.check_call([gxx, "-std=c++20", "-O2", "-Wall", "-Wextra", "-I", os.path.join(ROOT, "include"),
+                                   src, "-L", HERE, "-lsushiblas_cuda", "-Wl,-rpath,$ORIGIN/../../../sushiblas_b200",
+                                   "-o", exe], cwd=ROOT)
+        out[name] = exe
+    return out

@@ -1,0 +1,249 @@
+// GPU tests of the C++ Engine/Tensor API: the reference's own GEMM tests
+// (tests/blas/level3/test_gemm.cpp:39-88) with their fixture helpers
+// (tests/test_common.hpp:36-58: fill through data_as<T>() on the host, verify with an absolute
+// tolerance of 1e-4), the caller shapes of tests/runtime/test_framework_sim.cpp:18-58,81-111 and
+// tests/runtime/test_dependency_stress.cpp:17-45,67-83, examples/example.cpp:34-56, plus the
+// cases the reference never tests (transposes, alpha/beta, rank-3 batches, DEVICE storage).
+#include <chrono>
+#include <memory>
+#include <random>
+#include <vector>
+#include <SushiBLAS/SushiBLAS.h>
+#include "check.hpp"
+
+static sr::Execution::RuntimeContext& runtime() { static sr::Execution::RuntimeContext ctx; return ctx; }
+
+template <typename T = float>
+static void fill_tensor(sb::Tensor& t, const std::vector<T>& data)
+{
+    SB_THROW_IF(static_cast<int64_t>(data.size()) != t.num_elements, "Data size mismatch. Vector: {}, Tensor: {}",
+                data.size(), t.num_elements);
+    std::copy(data.begin(), data.end(), t.data_as<T>());
+}
+
+template <typename T = float>
+static void verify_tensor(const sb::Tensor& t, const std::vector<T>& expected, float abs_error = 1e-4f)
+{
+    EXPECT_EQ(static_cast<int64_t>(expected.size()), t.num_elements);
+    const T* p = t.data_as<T>();
+    for (size_t i = 0; i < expected.size(); ++i) EXPECT_NEAR(p[i], expected[i], abs_error);
+}
+
+// fp64 reference on host vectors (row-major)
+static std::vector<float> host_gemm(bool ta, bool tb, int m, int n, int k, float alpha, const std::vector<float>& a,
+                                    const std::vector<float>& b, float beta, const std::vector<float>& c)
+{
+    std::vector<float> out(size_t(m) * n);
+    for (int i = 0; i < m; ++i)
+        for (int j = 0; j < n; ++j)
+        {
+            double s = 0;
+            for (int p = 0; p < k; ++p)
+                s += double(ta ? a[size_t(p) * m + i] : a[size_t(i) * k + p]) * double(tb ? b[size_t(j) * k + p] : b[size_t(p) * n + j]);
+            out[size_t(i) * n + j] = float(alpha * s + (beta != 0 ? beta * double(c[size_t(i) * n + j]) : 0.0));
+        }
+    return out;
+}
+
+static std::vector<float> random_vec(size_t n, unsigned seed)
+{
+    std::mt19937 g(seed);
+    std::uniform_real_distribution<float> d(-1.0f, 1.0f);
+    std::vector<float> v(n);
+    for (auto& x : v) x = d(g);
+    return v;
+}
+
+TEST_CASE(SimpleGEMM3x3)
+{
+    sb::Engine engine(runtime(), sb::Core::Layout::ROW_MAJOR);
+    const int N = 3;
+    auto A = engine.create_tensor({N, N});
+    auto B = engine.create_tensor({N, N});
+    auto C = engine.create_tensor({N, N});
+    fill_tensor(A, {1, 2, 3, 4, 5, 6, 7, 8, 9});
+    fill_tensor(B, {2, 0, 0, 0, 2, 0, 0, 0, 2});
+    fill_tensor(C, std::vector<float>(N * N, 0.0f));
+    engine.blas().gemm(A, B, C);
+    engine.execute().wait();
+    verify_tensor(C, {2, 4, 6, 8, 10, 12, 14, 16, 18});
+}
+
+TEST_CASE(SimpleGEMMColumnMajor)
+{
+    sb::Engine engine(runtime(), sb::Core::Layout::COLUMN_MAJOR);
+    const int M = 2, N = 2, K = 2;
+    auto A = engine.create_tensor({M, K});
+    auto B = engine.create_tensor({K, N});
+    auto C = engine.create_tensor({M, N});
+    fill_tensor(A, {1, 3, 2, 4});
+    fill_tensor(B, {5, 7, 6, 8});
+    engine.blas().gemm(A, B, C);
+    engine.execute().wait();
+    verify_tensor(C, {19, 43, 22, 50});
+}
+
+TEST_CASE(TransposesAlphaBeta)
+{
+    sb::Engine engine(runtime());
+    const int m = 37, n = 29, k = 53;
+    for (int ta = 0; ta < 2; ++ta)
+        for (int tb = 0; tb < 2; ++tb)
+        {
+            auto A = ta ? engine.create_tensor({k, m}) : engine.create_tensor({m, k});
+            auto B = tb ? engine.create_tensor({n, k}) : engine.create_tensor({k, n});
+            auto C = engine.create_tensor({m, n});
+            auto a = random_vec(size_t(m) * k, 1 + ta), b = random_vec(size_t(k) * n, 3 + tb), c = random_vec(size_t(m) * n, 5);
+            fill_tensor(A, a); fill_tensor(B, b); fill_tensor(C, c);
+            engine.blas().gemm(A, B, C, ta, tb, 1.5f, 0.5f);
+            engine.execute().wait();
+            verify_tensor(C, host_gemm(ta, tb, m, n, k, 1.5f, a, b, 0.5f, c), 1e-4f);
+        }
+}
+
+TEST_CASE(BetaZeroNeverReadsC)
+{
+    sb::Engine engine(runtime());
+    auto A = engine.create_tensor({8, 8}), B = engine.create_tensor({8, 8}), C = engine.create_tensor({8, 8});
+    auto a = random_vec(64, 7), b = random_vec(64, 8);
+    fill_tensor(A, a); fill_tensor(B, b);
+    fill_tensor(C, std::vector<float>(64, std::numeric_limits<float>::quiet_NaN()));
+    engine.blas().gemm(A, B, C);
+    engine.execute().wait();
+    verify_tensor(C, host_gemm(false, false, 8, 8, 8, 1.0f, a, b, 0.0f, a));
+}
+
+TEST_CASE(BatchedRank3AndLargeTensorCorePath)
+{
+    sb::Engine engine(runtime());
+    const int batch = 3, m = 320, n = 272, k = 200;      // large enough for the tcgen05 path, ragged tiles
+    auto A = engine.create_tensor({batch, m, k}), B = engine.create_tensor({batch, k, n}), C = engine.create_tensor({batch, m, n});
+    auto a = random_vec(size_t(batch) * m * k, 11), b = random_vec(size_t(batch) * k * n, 12);
+    fill_tensor(A, a); fill_tensor(B, b);
+    engine.blas().gemm(A, B, C);
+    engine.execute().wait();
+    for (int bi = 0; bi < batch; ++bi)
+    {
+        std::vector<float> ab(a.begin() + size_t(bi) * m * k, a.begin() + size_t(bi + 1) * m * k);
+        std::vector<float> bb(b.begin() + size_t(bi) * k * n, b.begin() + size_t(bi + 1) * k * n);
+        auto ref = host_gemm(false, false, m, n, k, 1.0f, ab, bb, 0.0f, ab);
+        const float* got = C.data_as<float>() + size_t(bi) * m * n;
+        for (size_t i = 0; i < ref.size(); ++i) EXPECT_NEAR(got[i], ref[i], 2e-4);
+    }
+}
+
+TEST_CASE(DeviceStorageWithExplicitStaging)
+{
+    sb::Engine engine(runtime());
+    const int m = 300, n = 260, k = 256;
+    auto dev = sr::Memory::AllocStrategy::DEVICE;
+    auto A = engine.create_tensor({m, k}, dev), B = engine.create_tensor({k, n}, dev), C = engine.create_tensor({m, n}, dev);
+    EXPECT_TRUE(!A.storage->host_resident());
+    auto a = random_vec(size_t(m) * k, 21), b = random_vec(size_t(k) * n, 22), c = random_vec(size_t(m) * n, 23);
+    A.from_host(a.data()); B.from_host(b.data()); C.from_host(c.data());
+    engine.blas().gemm(A, B, C, false, false, 2.0f, -1.0f);
+    engine.execute().wait();
+    std::vector<float> out(size_t(m) * n);
+    C.to_host(out.data());
+    auto ref = host_gemm(false, false, m, n, k, 2.0f, a, b, -1.0f, c);
+    for (size_t i = 0; i < ref.size(); ++i) EXPECT_NEAR(out[i], ref[i], 3e-4);
+    // slices of the leading dimension are views into the same storage
+    auto top = C.slice(0, 0, 100);
+    std::vector<float> part(size_t(100) * n);
+    top.to_host(part.data());
+    EXPECT_EQ(part[5], out[5]);
+}
+
+TEST_CASE(ChainedGemmsKeepOrder)
+{
+    // x <- x * W repeated: each GEMM reads what the previous one wrote
+    // (shape of DeepForwardPass, tests/runtime/test_framework_sim.cpp:18-58, scaled down)
+    sb::Engine engine(runtime());
+    const int batch = 64, hidden = 128, layers = 6;
+    auto x0 = engine.create_tensor({batch, hidden}), x1 = engine.create_tensor({batch, hidden});
+    auto W = engine.create_tensor({hidden, hidden});
+    auto w = random_vec(size_t(hidden) * hidden, 31);
+    for (auto& v : w) v *= 0.1f;
+    auto x = random_vec(size_t(batch) * hidden, 32);
+    fill_tensor(W, w); fill_tensor(x0, x);
+    sb::Tensor* cur = &x0; sb::Tensor* nxt = &x1;
+    for (int l = 0; l < layers; ++l) { engine.blas().gemm(*cur, W, *nxt); std::swap(cur, nxt); }
+    EXPECT_EQ(engine.get_graph().pending(), size_t(layers));
+    engine.execute().wait();
+    std::vector<float> ref = x;
+    for (int l = 0; l < layers; ++l) ref = host_gemm(false, false, batch, hidden, hidden, 1.0f, ref, w, 0.0f, ref);
+    verify_tensor(*cur, ref, 1e-4f);
+}
+
+TEST_CASE(FrameworkSimShapesAndStress)
+{
+    // DeepForwardPass: 10 x (512x1024 * 1024x1024); ParallelBatchedInference: 24 x (256x256 * 256x512);
+    // dependency stress: 5000 reader GEMMs of 32x32 after one writer, then 3000 independent 8x8 GEMMs.
+    // Like the reference, only shapes and a positive duration are asserted; timings are printed.
+    sb::Engine engine(runtime());
+    auto dev = sr::Memory::AllocStrategy::DEVICE;
+    {
+        std::vector<sb::Tensor> act, wts;
+        for (int l = 0; l <= 10; ++l) act.push_back(engine.create_tensor({512, 1024}, dev));
+        for (int l = 0; l < 10; ++l) wts.push_back(engine.create_tensor({1024, 1024}, dev));
+        std::vector<float> ones(size_t(1024) * 1024, 0.001f);
+        for (auto& w : wts) w.from_host(ones.data());
+        act[0].from_host(ones.data());
+        auto t0 = std::chrono::steady_clock::now();
+        for (int l = 0; l < 10; ++l) engine.blas().gemm(act[l], wts[l], act[l + 1]);
+        engine.execute().wait();
+        double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        std::printf("       DeepForwardPass 10 x (512x1024x1024): %.3f ms\n", ms);
+        EXPECT_EQ(act[10].shape[0], 512); EXPECT_EQ(act[10].shape[1], 1024); EXPECT_TRUE(ms > 0);
+    }
+    {
+        auto src = engine.create_tensor({32, 32}, dev), w = engine.create_tensor({32, 32}, dev);
+        std::vector<sb::Tensor> outs;
+        for (int i = 0; i < 5000; ++i) outs.push_back(engine.create_tensor({32, 32}, dev));
+        std::vector<float> v(1024, 0.5f);
+        src.from_host(v.data()); w.from_host(v.data());
+        auto t0 = std::chrono::steady_clock::now();
+        engine.blas().gemm(w, w, src);
+        for (auto& o : outs) engine.blas().gemm(src, w, o);
+        engine.execute().wait();
+        double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        std::printf("       1 writer + 5000 reader GEMMs (32^3): %.3f ms\n", ms);
+        std::vector<float> got(1024);
+        outs[4999].to_host(got.data());
+        EXPECT_NEAR(got[0], 32 * (32 * 0.25f) * 0.5f, 1e-3);
+        EXPECT_TRUE(ms > 0);
+    }
+}
+
+TEST_CASE(ExampleFlowWithWaitAll)
+{
+    // examples/example.cpp:34-56: column-major engine, 1024^2 tensors, execute() then ctx.wait_all()
+    sb::Engine sbe(runtime(), sb::Core::Layout::COLUMN_MAJOR);
+    auto A = sbe.create_tensor({1024, 1024}, sr::Memory::AllocStrategy::SHARED);
+    auto B = sbe.create_tensor({1024, 1024}, sr::Memory::AllocStrategy::SHARED);
+    auto C = sbe.create_tensor({1024, 1024}, sr::Memory::AllocStrategy::SHARED);
+    std::fill_n(A.data_as<float>(), A.num_elements, 1.0f);
+    std::fill_n(B.data_as<float>(), B.num_elements, 0.5f);
+    sbe.blas().gemm(A, B, C);
+    sbe.execute();
+    runtime().wait_all();
+    EXPECT_NEAR(C.data_as<float>()[12345], 512.0f, 1e-3);
+}
+
+TEST_CASE(ErrorsAreRuntimeErrors)
+{
+    sb::Engine engine(runtime());
+    auto A = engine.create_tensor({4, 4}), B = engine.create_tensor({4, 4});
+    auto D = engine.create_tensor({4, 4}, sb::Core::DataType::FLOAT64);
+    auto v = engine.create_tensor({4});
+    sb::Tensor none;
+    EXPECT_THROWS(engine.blas().gemm(v, B, A), "at least 2D");
+    EXPECT_THROWS(engine.blas().gemm(A, B, D), "Data type mismatch");
+    EXPECT_THROWS(engine.blas().gemm(D, D, D), "FLOAT32 only");
+    auto big = engine.create_tensor({64, 64});
+    auto small = engine.create_tensor({2, 2});
+    EXPECT_THROWS(engine.blas().gemm(small, B, big), "does not fit its storage");
+    EXPECT_EQ(engine.get_graph().pending(), size_t(0));
+}
+
+int main() { return check::run_all(); }

@@ -1,0 +1,156 @@
+// Host-side logic of the C++ API, no GPU needed: Tensor metadata and views
+// (reference include/SushiBLAS/tensor.hpp:92-300), Storage rounding (storage.hpp:78-95),
+// GEMM parameter derivation and validation (src/ops/blas/level3/gemm.cpp:87-105), task
+// metadata (task_types.hpp:35-129), the smart pointer, and the loud failure of
+// RuntimeContext without a device.
+#include <cstdlib>
+#include <cstring>
+#include <SushiBLAS/SushiBLAS.h>
+#include "check.hpp"
+
+namespace {
+// host-only allocator for tests: plain malloc, everything host-resident, no device view
+struct MallocAllocator final : sr::Memory::USMAllocator
+{
+    int live = 0;
+    std::size_t last_bytes = 0;
+    void* allocate(std::size_t bytes, sr::Memory::AllocStrategy, std::size_t) override
+    { ++live; last_bytes = bytes; return std::aligned_alloc(128, bytes); }
+    void deallocate(void* p) override { --live; std::free(p); }
+    bool is_host_resident(void*) override { return true; }
+    void* device_view(void*) override { return nullptr; }
+};
+
+sb::Tensor make(sr::sushi_ptr<MallocAllocator> al, std::initializer_list<int64_t> dims,
+                sb::Core::Layout l = sb::Core::Layout::ROW_MAJOR)
+{
+    std::size_t n = 1; for (auto d : dims) n *= d;
+    auto st = sr::make_sushi<sb::Storage>(al, n * 4);
+    return sb::Tensor(st, dims, 0, l);
+}
+}
+
+TEST_CASE(storage_rounds_to_128_and_frees)
+{
+    auto al = sr::make_sushi<MallocAllocator>();
+    {
+        auto st = sr::make_sushi<sb::Storage>(al, 36);       // 3x3 floats
+        EXPECT_EQ(st->requested_bytes, 36u);
+        EXPECT_EQ(st->size_bytes, 128u);
+        EXPECT_EQ(al->last_bytes, 128u);
+        EXPECT_EQ(al->live, 1);
+        auto copy = st;
+        EXPECT_EQ(st->ref_count(), 2u);
+    }
+    EXPECT_EQ(al->live, 0);
+    EXPECT_THROWS(sr::make_sushi<sb::Storage>(al, 0), "cannot be zero");
+    EXPECT_THROWS(sr::make_sushi<sb::Storage>(sr::sushi_ptr<MallocAllocator>(), 16), "cannot be null");
+}
+
+TEST_CASE(tensor_strides_row_and_column_major)
+{
+    auto al = sr::make_sushi<MallocAllocator>();
+    auto t = make(al, {4, 5, 6});
+    EXPECT_EQ(t.rank, 3); EXPECT_EQ(t.num_elements, 120);
+    EXPECT_EQ(t.strides[0], 30); EXPECT_EQ(t.strides[1], 6); EXPECT_EQ(t.strides[2], 1);
+    auto c = make(al, {4, 5, 6}, sb::Core::Layout::COLUMN_MAJOR);
+    EXPECT_EQ(c.strides[0], 1); EXPECT_EQ(c.strides[1], 4); EXPECT_EQ(c.strides[2], 20);
+    EXPECT_TRUE(t.is_contiguous() && c.is_contiguous() && t.is_aligned());
+    EXPECT_THROWS(make(al, {1, 1, 1, 1, 1, 1, 1}), "exceeds limit");
+    // capacity check
+    auto st = sr::make_sushi<sb::Storage>(al, 64);
+    EXPECT_THROWS(sb::Tensor(st, {8, 8}), "capacity exceeded");
+    EXPECT_THROWS(sb::Tensor(st, {2, 2}, -1), "negative");
+    sb::Tensor empty;
+    EXPECT_THROWS(empty.data(), "no storage");
+}
+
+TEST_CASE(tensor_views)
+{
+    auto al = sr::make_sushi<MallocAllocator>();
+    auto t = make(al, {4, 6});
+    float* p = t.data_as<float>();
+    for (int i = 0; i < 24; ++i) p[i] = float(i);
+    auto tr = t.transpose(0, 1);
+    EXPECT_EQ(tr.shape[0], 6); EXPECT_EQ(tr.strides[0], 1); EXPECT_EQ(tr.strides[1], 6);
+    EXPECT_TRUE(!tr.is_contiguous());
+    EXPECT_THROWS(t.transpose(0, 2), "Invalid dimensions");
+    auto r = t.reshape({2, 12});
+    EXPECT_EQ(r.strides[0], 12); EXPECT_EQ(r.data(), t.data());
+    EXPECT_THROWS(t.reshape({5, 5}), "Element count mismatch");
+    EXPECT_THROWS(tr.reshape({24}), "must be contiguous");
+    auto s = t.slice(0, 1, 3);                    // rows 1..2
+    EXPECT_EQ(s.shape[0], 2); EXPECT_EQ(s.storage_offset, 6); EXPECT_EQ(s.data_as<float>()[0], 6.0f);
+    auto neg = t.slice(0, -1, 100);               // last row, end clamped
+    EXPECT_EQ(neg.shape[0], 1); EXPECT_EQ(neg.storage_offset, 18);
+    EXPECT_THROWS(t.slice(2, 0, 1), "Invalid dimension");
+    // host staging helpers on a host-resident tensor are plain copies
+    std::vector<float> out(24);
+    t.to_host(out.data());
+    EXPECT_EQ(out[23], 23.0f);
+}
+
+TEST_CASE(gemm_parameter_derivation)
+{
+    auto al = sr::make_sushi<MallocAllocator>();
+    auto A = make(al, {256, 512, 512}), B = make(al, {256, 512, 512}), C = make(al, {256, 512, 512});
+    auto g = sb::detail::derive_gemm_call(A, B, C, false, false, 1.0f, 0.0f);
+    EXPECT_EQ(g.m, 512); EXPECT_EQ(g.n, 512); EXPECT_EQ(g.k, 512); EXPECT_EQ(g.batch, 256);
+    EXPECT_EQ(g.lda, 512); EXPECT_EQ(g.stride_a, 262144); EXPECT_EQ(g.stride_c, 262144);
+    // k comes from A's second-to-last dim under transA
+    auto At = make(al, {7, 3}), B2 = make(al, {7, 5}), C2 = make(al, {3, 5});
+    g = sb::detail::derive_gemm_call(At, B2, C2, true, false, 2.0f, 0.5f);
+    EXPECT_EQ(g.m, 3); EXPECT_EQ(g.n, 5); EXPECT_EQ(g.k, 7); EXPECT_EQ(g.lda, 3); EXPECT_EQ(g.batch, 1);
+    EXPECT_EQ(g.stride_a, 0);
+    // rank-4 batch = product of leading dims
+    auto A4 = make(al, {2, 3, 8, 4}), B4 = make(al, {2, 3, 4, 6}), C4 = make(al, {2, 3, 8, 6});
+    g = sb::detail::derive_gemm_call(A4, B4, C4, false, false, 1.0f, 0.0f);
+    EXPECT_EQ(g.batch, 6); EXPECT_EQ(g.stride_a, 32); EXPECT_EQ(g.stride_b, 24); EXPECT_EQ(g.stride_c, 48);
+    // validation
+    auto v = make(al, {4});
+    EXPECT_THROWS(sb::detail::derive_gemm_call(v, B2, C2, false, false, 1, 0), "at least 2D");
+    auto D = make(al, {3, 5}); D.dtype = sb::Core::DataType::FLOAT64;
+    EXPECT_THROWS(sb::detail::derive_gemm_call(At, B2, D, true, false, 1, 0), "Data type mismatch");
+    EXPECT_THROWS(sb::detail::derive_gemm_call(At, B2, C, true, false, 1, 0), "rank >= 3");
+}
+
+TEST_CASE(column_major_maps_to_swapped_row_major)
+{
+    auto al = sr::make_sushi<MallocAllocator>();
+    auto L = sb::Core::Layout::COLUMN_MAJOR;
+    auto A = make(al, {5, 7}, L), B = make(al, {7, 3}, L), C = make(al, {5, 3}, L);
+    auto g = sb::detail::derive_gemm_call(A, B, C, false, false, 1.0f, 0.0f);
+    EXPECT_EQ(g.lda, 5); EXPECT_EQ(g.ldb, 7); EXPECT_EQ(g.ldc, 5); EXPECT_EQ(g.k, 7);
+    bool swapped = false;
+    auto r = sb::detail::row_major_equivalent(g, &swapped);
+    EXPECT_TRUE(swapped);
+    EXPECT_EQ(r.m, 3); EXPECT_EQ(r.n, 5); EXPECT_EQ(r.k, 7); EXPECT_EQ(r.lda, 7); EXPECT_EQ(r.ldb, 5); EXPECT_EQ(r.ldc, 5);
+    auto rm = sb::detail::row_major_equivalent(sb::detail::derive_gemm_call(make(al, {5, 7}), make(al, {7, 3}),
+                                                                            C = make(al, {5, 3}), false, true, 1, 0), &swapped);
+    EXPECT_TRUE(!swapped && rm.trans_b);
+    EXPECT_EQ(sb::detail::operand_extent(4, 3, 5, 100, 3), 2 * 100 + 3 * 5 + 3);
+    EXPECT_EQ(sb::detail::operand_extent(0, 3, 5, 100, 3), 0);
+}
+
+TEST_CASE(task_metadata_and_op_id)
+{
+    using namespace sr::Graph::Literals;
+    constexpr auto id = "blas.lvl3.gemm"_op;
+    // FNV-1a 32-bit of the operation name
+    std::uint32_t h = 2166136261u;
+    for (const char* s = "blas.lvl3.gemm"; *s; ++s) { h ^= std::uint8_t(*s); h *= 16777619u; }
+    EXPECT_EQ(id.value, h);
+    EXPECT_TRUE("a"_op != "b"_op);
+    sr::Graph::TaskMetadata m;
+    m.set_param(0, 1.5f); m.set_param(2, true); m.set_param(9, 3);       // out-of-range index ignored
+    EXPECT_EQ(m.get_param<float>(0), 1.5f); EXPECT_EQ(m.get_param<bool>(2), true); EXPECT_EQ(m.get_param<int>(9), 0);
+}
+
+TEST_CASE(runtime_context_fails_loudly_without_a_device)
+{
+    int count = 0;
+    if (sushi_cuda_device_count(&count) == SUSHI_CUDA_OK && count > 0) return;     // a GPU is present
+    EXPECT_THROWS(sr::Execution::RuntimeContext ctx, "cannot create the CUDA context");
+}
+
+int main() { return check::run_all(); }
