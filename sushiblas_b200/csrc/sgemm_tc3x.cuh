@@ -21,6 +21,17 @@
 // 8*(BM+BN) bytes per 3*BM*BN tensor-core MACs; 256 x 256 keeps that at ~43 B/clk/SM of L2
 // bandwidth at full tensor rate, where 128 x 256 would need 64 B/clk/SM.
 //
+// Work distribution: whole tiles are dealt round-robin to the CTAs (data-parallel rounds).  The
+// tiles of a last, partial round -- or all tiles when there are fewer tiles than SMs -- are cut
+// along K into S equal slices ("split-K tail"), and the (slice, tile) items are dealt round-robin
+// slice-major, so that the CTAs running at the same time work on the same K range of neighbouring
+// tiles and keep sharing A/B panels in L2.  Slices 0 .. S-2 write their raw 256 x 256 fp32
+// accumulators to a slot in global scratch and publish an epoch flag (release); the CTA holding
+// the last slice owns the tile: it acquires the flags, adds the slots and applies alpha/beta.
+// Publishing never waits, an owner only waits for items dealt before its own, and the grid never
+// exceeds the SM count, so the exchange cannot deadlock; the flag wait is bounded like every
+// other wait.
+//
 // Every wait in this kernel is bounded: on expiry the waiter records a code in *status,
 // raises a CTA-wide abort flag, every role leaves its loop, in-flight copies and MMAs are
 // drained with bounded waits, TMEM is freed and the kernel returns.
@@ -49,7 +60,12 @@ constexpr unsigned long long DRAIN_LIMIT_NS = 2000000ull;    // 2 ms per drain w
 
 // status codes written to *status (first writer wins)
 enum : int { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA_FULL = 2, ST_TIMEOUT_MMA_ACC = 3,
-             ST_TIMEOUT_EPILOGUE = 4 };
+             ST_TIMEOUT_EPILOGUE = 4, ST_TIMEOUT_PARTIAL_FLAG = 5, ST_TIMEOUT_PARTIAL_PUBLISH = 6 };
+
+constexpr int SK_SLOT_FLOATS = BM * BN;               // one raw accumulator tile per published slice
+constexpr int SK_MAX_SPLIT = 4;                       // at most this many K slices per tile
+constexpr size_t SK_FLAG_BYTES = 16384;              // flag region at the head of the exchange area
+constexpr int SK_MIN_KB = 8;                          // and each slice is at least this many k-blocks
 
 struct Params
 {
@@ -61,7 +77,53 @@ struct Params
     int64_t total_tiles;           // tiles_m * tiles_n * batch
     float alpha, beta;
     int* status;
+    // work distribution
+    int64_t dp_tiles;              // tiles [0, dp_tiles) are dealt whole, round-robin over the grid
+    int32_t sk_tiles;              // tiles [dp_tiles, dp_tiles + sk_tiles) are cut along K (0: none)
+    int32_t sk_split;              // number of K slices per cut tile (>= 2 when sk_tiles > 0)
+    float* sk_partials;            // [sk_tiles * (sk_split-1)][256*256] raw accumulators of slices 0 .. S-2
+    unsigned int* sk_flags;        // [sk_tiles * (sk_split-1)] epoch of the slot's last publication
+    unsigned int sk_epoch;         // this launch's epoch (never 0)
 };
+
+// One unit of work of a CTA: k-blocks [kb0, kb1) of one tile.
+struct WorkItem
+{
+    int64_t tile;
+    int32_t kb0, kb1;
+    int32_t kind;                  // 0 whole tile; 1 slice that publishes a partial; 2 last slice: owner of a cut tile
+    int32_t slot;                  // kind 1: slot to publish; kind 2: slot of slice 0 (slice q at slot + q*sk_tiles)
+};
+
+// idx-th work item of CTA `cta` (identical enumeration in every role); false when exhausted.
+// Items are numbered: whole tiles first, then (slice q, cut tile t) at dp_tiles + q*sk_tiles + t;
+// item g belongs to CTA g % grid.
+__device__ __forceinline__ bool get_work_item(const Params& p, int32_t cta, int32_t grid, int32_t idx, WorkItem& w)
+{
+    const int64_t g = cta + (int64_t)idx * grid;
+    w.slot = 0;
+    if (g < p.dp_tiles) { w.tile = g; w.kb0 = 0; w.kb1 = p.num_kb; w.kind = 0; return true; }
+    const int64_t i = g - p.dp_tiles;
+    if (i >= (int64_t)p.sk_tiles * p.sk_split) return false;
+    const int32_t q = (int32_t)(i / p.sk_tiles), t = (int32_t)(i % p.sk_tiles);
+    w.tile = p.dp_tiles + t;
+    w.kb0 = (int32_t)((int64_t)q * p.num_kb / p.sk_split);
+    w.kb1 = (int32_t)((int64_t)(q + 1) * p.num_kb / p.sk_split);
+    if (q == p.sk_split - 1) { w.kind = 2; w.slot = t; }
+    else { w.kind = 1; w.slot = q * p.sk_tiles + t; }
+    return true;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* ptr)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* ptr, unsigned int v)
+{
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -209,16 +271,16 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint8_t* stage_base = smem;
     uint8_t* epi_base = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(epi_base + EPI_WARPS * EPI_STAGE_BYTES);
-    // bars[0..2] full, [3..5] empty, [6] acc_full, [7..8] acc_empty, [9] drain
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 11);
+    // bars[0..2] full, [3..5] empty, [6] acc_full, [7..8] acc_empty, [9] drain, [10] partial written
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 12);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     const uint32_t full0 = smem_u32(bars + 0), empty0 = smem_u32(bars + 3);
     const uint32_t acc_full = smem_u32(bars + 6), acc_empty0 = smem_u32(bars + 7);
-    const uint32_t drain = smem_u32(bars + 9);
+    const uint32_t drain = smem_u32(bars + 9), partial_done = smem_u32(bars + 10);
 
     if (threadIdx.x == 0)
     {
@@ -227,6 +289,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         mbar_init(acc_empty0, EPI_WARPS / 2);
         mbar_init(acc_empty0 + 8, EPI_WARPS / 2);
         mbar_init(drain, 1);
+        mbar_init(partial_done, EPI_WARPS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -242,18 +305,18 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t first_tile = blockIdx.x;
-    const int64_t tile_step = gridDim.x;
+    const int32_t cta = (int32_t)blockIdx.x, grid = (int32_t)gridDim.x;
 
     if (warp == 0)
     {
         // ------------------------------------------------------------ TMA producer
         uint32_t it = 0;
         bool ok = true;
-        for (int64_t t = first_tile; t < p.total_tiles && ok; t += tile_step)
+        WorkItem w;
+        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
-            const TileCoord tc = decode_tile(t, p.tiles_m, p.tiles_n);
-            for (int32_t kb = 0; kb < p.num_kb && ok; ++kb, ++it)
+            const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+            for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
             {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                 int okl = 1;
@@ -290,16 +353,17 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ------------------------------------------------------------ MMA issuer
         uint32_t it = 0, tl = 0;
         bool ok = true;
-        for (int64_t t = first_tile; t < p.total_tiles && ok; t += tile_step, ++tl)
+        WorkItem w;
+        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx, ++tl)
         {
-            for (int32_t kb = 0; kb < p.num_kb && ok; ++kb, ++it)
+            for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
             {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                 int okl = 1;
                 if (lane == 0)
                 {
                     okl = mbar_wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, WAIT_LIMIT_NS);
-                    if (okl && kb == 0)
+                    if (okl && kb == w.kb0)
                     {
                         // both accumulator halves must have been drained by the previous tile's epilogue
                         okl = mbar_wait_bounded(acc_empty0, (tl & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS) &&
@@ -322,7 +386,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             for (int ks = 0; ks < BK / 8; ++ks)
                             {
                                 const uint64_t koff = (uint64_t)((ks * 8 * 4) >> 4);   // +32 bytes per k-step
-                                const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
+                                const uint32_t acc = (kb > w.kb0 || ks > 0) ? 1u : 0u;   // a run starts from zero
                                 // small terms first, then the leading product
                                 tcgen05_mma_tf32(d, a_lo + koff, b_hi + koff, IDESC_TF32_M128_N256, acc);
                                 tcgen05_mma_tf32(d, a_hi + koff, b_lo + koff, IDESC_TF32_M128_N256, 1u);
@@ -330,7 +394,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             }
                         }
                         tcgen05_commit(empty0 + 8 * s);               // stage reusable once these MMAs retire
-                        if (kb == p.num_kb - 1) tcgen05_commit(acc_full);  // accumulators complete
+                        if (kb == w.kb1 - 1) tcgen05_commit(acc_full);     // accumulators of this run complete
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
@@ -353,12 +417,38 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int q = warp & 3;                  // TMEM lane quarter this warp may access
         float4* stg = reinterpret_cast<float4*>(epi_base + ew * EPI_STAGE_BYTES);   // [32 rows][8 float4]
         const bool has_beta = (p.beta != 0.0f);
-        uint32_t tl = 0;
+        const int rsub = lane >> 3, c4 = lane & 7;
+        uint32_t tl = 0, published = 0;
         bool ok = true;
-        for (int64_t t = first_tile; t < p.total_tiles && ok; t += tile_step, ++tl)
+        WorkItem w;
+        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx, ++tl)
         {
-            const TileCoord tc = decode_tile(t, p.tiles_m, p.tiles_n);
+            const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
             int okl = mbar_wait_bounded(acc_full, tl & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
+            if (okl && w.kind == 2)
+            {
+                // owner of a cut tile: the earlier slices must have been published
+                for (int32_t c = 0; c < p.sk_split - 1 && okl; ++c)
+                {
+                    const unsigned int* flag = p.sk_flags + (w.slot + c * p.sk_tiles);
+                    const unsigned long long t0 = globaltimer_ns();
+                    uint32_t spins = 0;
+                    while (ld_acquire_gpu(flag) != p.sk_epoch)
+                    {
+                        if (((++spins) & 0x3F) == 0)
+                        {
+                            if (*abort_flag) { okl = 0; break; }
+                            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS)
+                            {
+                                *abort_flag = 1;
+                                atomicCAS(p.status, 0, (int)ST_TIMEOUT_PARTIAL_FLAG);
+                                okl = 0;
+                                break;
+                            }
+                        }
+                    }
+                }
+            }
             ok = __all_sync(0xffffffffu, okl) != 0;
             if (!ok) break;
             tcgen05_fence_after();
@@ -368,14 +458,17 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int64_t col_base = (int64_t)tc.tn * BN;
             const bool vec_ok = ((p.ldc & 3) == 0) && ((p.stride_c & 3) == 0) &&
                                 ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
-            const int rsub = lane >> 3, c4 = lane & 7;
+            const bool partial = (w.kind == 1);
+            // slot element of (tile row, tile col): row-major 256 x 256
+            float* my_slot = partial ? p.sk_partials + (size_t)w.slot * SK_SLOT_FLOATS : nullptr;
+            const int slot_row0 = h * 128 + q * 32;
 
-            if (row_base < p.m)
+            if (partial || row_base < p.m)
             {
                 for (int chunk = 0; chunk < BN / 32; ++chunk)
                 {
                     const int64_t col0 = col_base + chunk * 32;
-                    if (col0 >= p.n) break;
+                    if (!partial && col0 >= p.n) break;
                     uint32_t v[32];
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256 + chunk * 32);
                     tcgen05_ld_32x32b_x32(taddr, v);
@@ -383,7 +476,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     // old C values for the beta term, fetched while the TMEM load is in flight
                     float4 old[8];
                     const int64_t gcol = col0 + c4 * 4;
-                    if (has_beta && vec_ok)
+                    if (!partial && has_beta && vec_ok)
                     {
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
@@ -400,42 +493,75 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                     {
-                        float4 w;
-                        w.x = __uint_as_float(v[4 * j + 0]); w.y = __uint_as_float(v[4 * j + 1]);
-                        w.z = __uint_as_float(v[4 * j + 2]); w.w = __uint_as_float(v[4 * j + 3]);
-                        stg[lane * 8 + (j ^ (lane & 7))] = w;
+                        float4 x;
+                        x.x = __uint_as_float(v[4 * j + 0]); x.y = __uint_as_float(v[4 * j + 1]);
+                        x.z = __uint_as_float(v[4 * j + 2]); x.w = __uint_as_float(v[4 * j + 3]);
+                        stg[lane * 8 + (j ^ (lane & 7))] = x;
                     }
                     __syncwarp();
+                    float4 acc4[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                     {
                         const int r = i * 4 + rsub;
-                        const float4 a = stg[r * 8 + (c4 ^ (r & 7))];
-                        const int64_t grow = row_base + r;
-                        if (grow >= p.m || gcol >= p.n) continue;
-                        float* dst = cb + grow * p.ldc + gcol;
-                        if (vec_ok && gcol + 3 < p.n)
-                        {
-                            float4 o;
-                            o.x = p.alpha * a.x; o.y = p.alpha * a.y; o.z = p.alpha * a.z; o.w = p.alpha * a.w;
-                            if (has_beta)
-                            {
-                                o.x = fmaf(p.beta, old[i].x, o.x); o.y = fmaf(p.beta, old[i].y, o.y);
-                                o.z = fmaf(p.beta, old[i].z, o.z); o.w = fmaf(p.beta, old[i].w, o.w);
-                            }
-                            *reinterpret_cast<float4*>(dst) = o;
-                        }
-                        else
-                        {
-                            const float av[4] = {a.x, a.y, a.z, a.w};
+                        acc4[i] = stg[r * 8 + (c4 ^ (r & 7))];
+                    }
+                    const size_t slot_off0 = (size_t)(slot_row0 + rsub) * BN + chunk * 32 + c4 * 4;   // row r = i*4 + rsub
+                    if (partial)
+                    {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
+                        for (int i = 0; i < 8; ++i)
+                            __stcg(reinterpret_cast<float4*>(my_slot + slot_off0 + (size_t)i * 4 * BN), acc4[i]);
+                    }
+                    else
+                    {
+                        if (w.kind == 2)
+                        {
+                            // add the published slices; eight independent 128-bit loads in flight per slice
+                            for (int32_t c = 0; c < p.sk_split - 1; ++c)
                             {
-                                if (gcol + j < p.n)
+                                const float* src = p.sk_partials + (size_t)(w.slot + c * p.sk_tiles) * SK_SLOT_FLOATS + slot_off0;
+                                float4 t4[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    t4[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * 4 * BN));
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
                                 {
-                                    float o = p.alpha * av[j];
-                                    if (has_beta) o = fmaf(p.beta, dst[j], o);
-                                    dst[j] = o;
+                                    acc4[i].x += t4[i].x; acc4[i].y += t4[i].y; acc4[i].z += t4[i].z; acc4[i].w += t4[i].w;
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                        {
+                            const float4 a = acc4[i];
+                            const int64_t grow = row_base + i * 4 + rsub;
+                            if (grow >= p.m || gcol >= p.n) continue;
+                            float* dst = cb + grow * p.ldc + gcol;
+                            if (vec_ok && gcol + 3 < p.n)
+                            {
+                                float4 o;
+                                o.x = p.alpha * a.x; o.y = p.alpha * a.y; o.z = p.alpha * a.z; o.w = p.alpha * a.w;
+                                if (has_beta)
+                                {
+                                    o.x = fmaf(p.beta, old[i].x, o.x); o.y = fmaf(p.beta, old[i].y, o.y);
+                                    o.z = fmaf(p.beta, old[i].z, o.z); o.w = fmaf(p.beta, old[i].w, o.w);
+                                }
+                                *reinterpret_cast<float4*>(dst) = o;
+                            }
+                            else
+                            {
+                                const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                {
+                                    if (gcol + j < p.n)
+                                    {
+                                        float o = p.alpha * av[j];
+                                        if (has_beta) o = fmaf(p.beta, dst[j], o);
+                                        dst[j] = o;
+                                    }
                                 }
                             }
                         }
@@ -443,10 +569,29 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     __syncwarp();
                 }
             }
-            // this warp is done reading accumulator half h of this tile
+            // this warp is done reading accumulator half h of this run
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * h);
+
+            if (partial)
+            {
+                // publish the slot: every warp fences its stores and arrives; one thread waits
+                // (bounded) for all eight and releases the flag
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(partial_done);
+                if (ew == 0 && lane == 0)
+                {
+                    if (mbar_wait_bounded(partial_done, published & 1, abort_flag, p.status, ST_TIMEOUT_PARTIAL_PUBLISH,
+                                          WAIT_LIMIT_NS))
+                    {
+                        __threadfence();
+                        st_release_gpu(p.sk_flags + w.slot, p.sk_epoch);
+                    }
+                }
+                ++published;
+            }
         }
     }
 
@@ -494,10 +639,53 @@ inline bool make_plane_map(CUtensorMap* map, const float* planes, int64_t rows_p
     return r == CUDA_SUCCESS;
 }
 
+// Split-K tail plan for `tiles` tiles on `sm_count` SMs (see the header comment).
+struct TailPlan { int64_t dp_tiles; int32_t sk_tiles, sk_split; int64_t grid; };
+
+inline TailPlan plan_tail(int64_t tiles, int64_t num_kb, int sm_count, bool allow_split)
+{
+    TailPlan t{tiles, 0, 1, tiles < sm_count ? tiles : sm_count};
+    // With at least one tile per SM the tail is not cut: measured on B200 (power-capped clocks,
+    // fix-up traffic) the gain of a balanced last round does not cover the exchange.
+    if (!allow_split || tiles <= 0 || tiles >= sm_count) return t;
+    // Cost in units of one whole-tile main loop: rounds/S plus the fix-up, which is a fixed
+    // time per published slice (slot write + owner's read) and so weighs 7/num_kb of a tile.
+    int best_s = 1;
+    double best = 1.0;
+    for (int s = 2; s <= SK_MAX_SPLIT; ++s)
+    {
+        if (num_kb / s < SK_MIN_KB) break;
+        const double cost = (double)((tiles * s + sm_count - 1) / sm_count) / s + (s - 1) * 7.0 / (double)num_kb;
+        if (cost < best - 0.02) { best = cost; best_s = s; }
+    }
+    if (best_s == 1) return t;
+    t.dp_tiles = 0; t.sk_tiles = (int32_t)tiles; t.sk_split = best_s;
+    t.grid = tiles * best_s < sm_count ? tiles * best_s : sm_count;
+    return t;
+}
+
+// Exchange area layout: SK_FLAG_BYTES of epoch flags (one per published slice, at fixed offsets so
+// that a flag never aliases old slot data), then one 256 x 256 fp32 slot per published slice.
+// The flag region must be zero-filled when the area is allocated.
+inline size_t sk_area_bytes(const TailPlan& t)
+{
+    const size_t slots = (size_t)t.sk_tiles * (size_t)(t.sk_split - 1);
+    return slots ? SK_FLAG_BYTES + slots * (SK_SLOT_FLOATS * sizeof(float)) : 0;
+}
+
+inline void tile_counts(int64_t m, int64_t n, int64_t k, int64_t batch, int64_t* tiles, int64_t* num_kb)
+{
+    *tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * batch;
+    *num_kb = (k + BK - 1) / BK;
+}
+
 // planes_a / planes_b as written by launch_split_tf32 for op(A) (rows = m) and op(B)^T (rows = n).
+// sk_area: zero-initialised exchange area of at least sk_area_bytes(plan) bytes, or nullptr to
+// deal whole tiles only; sk_epoch: a value never used before with this area (and never 0).
 inline cudaError_t launch_sgemm_tc3x(const float* planes_a, const float* planes_b, float* c,
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
-                                     float alpha, float beta, int* status, int sm_count, cudaStream_t st)
+                                     float alpha, float beta, int* status, int sm_count, cudaStream_t st,
+                                     void* sk_area = nullptr, unsigned int sk_epoch = 0)
 {
     // per-device attribute; cheap enough to set on every launch
     cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -513,9 +701,13 @@ inline cudaError_t launch_sgemm_tc3x(const float* planes_a, const float* planes_
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
     p.alpha = alpha; p.beta = beta; p.status = status;
-    const int64_t grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
-    if (grid <= 0) return cudaSuccess;
-    sgemm_tc3x_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
+    p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split;
+    p.sk_flags = static_cast<unsigned int*>(sk_area);
+    p.sk_partials = sk_area ? reinterpret_cast<float*>(static_cast<char*>(sk_area) + SK_FLAG_BYTES) : nullptr;
+    p.sk_epoch = sk_epoch;
+    if (plan.grid <= 0) return cudaSuccess;
+    sgemm_tc3x_kernel<<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
 

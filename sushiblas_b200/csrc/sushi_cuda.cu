@@ -36,6 +36,9 @@ struct DeviceState
     size_t stage_bytes[3] = {0, 0, 0};
     int* status = nullptr;                // device word written by bounded in-kernel waits
     int* status_host = nullptr;           // pinned mirror
+    void* sk_area = nullptr;              // split-K exchange area (epoch flags + slots), flags zeroed at allocation
+    size_t sk_area_bytes = 0;
+    unsigned int sk_epoch = 0;            // last epoch handed to a launch
     // kernel timing (off by default): event triples {before pre-pass, before GEMM, after GEMM}
     std::vector<cudaEvent_t> timing_events;
     size_t timing_used = 0;
@@ -72,6 +75,7 @@ struct sushi_cuda_ctx
     int variant = SUSHI_GEMM_AUTO;
     std::atomic<int64_t> launches{0};
     bool timing = false;
+    bool stream_k = true;                 // cut the tiles of a partial round along K (SUSHI_SPLIT_K=0 disables)
     // multi-GPU (one process per GPU: a single communicator bound to one device index)
     ncclComm_t comm = nullptr;
     int comm_dev = -1, nranks = 1, rank = 0;
@@ -189,9 +193,18 @@ int timing_mark(sushi_cuda_ctx* ctx, DeviceState& d, int which, int prepass_laun
     return SUSHI_CUDA_OK;
 }
 
+// Lets a caller that multiplies several row slabs of A by the same B (the sharded path) keep
+// one kernel family for all slabs and split B into planes only once.
+struct SlabReuse
+{
+    int variant = -1;          // -1: choose per call
+    bool b_planes_ready = false;
+    int64_t max_rows = 0;      // largest slab (sizes the A planes once)
+};
+
 int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int64_t n, int64_t k, float alpha,
              const float* a, int64_t lda, int64_t sa, const float* b, int64_t ldb, int64_t sb,
-             float beta, float* c, int64_t ldc, int64_t sc, int64_t batch)
+             float beta, float* c, int64_t ldc, int64_t sc, int64_t batch, SlabReuse* reuse = nullptr)
 {
     if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
     SC_CUDA(ctx, cudaSetDevice(d.device));
@@ -206,26 +219,57 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         SC_CUDA(ctx, cudaGetLastError());
         return SUSHI_CUDA_OK;
     }
-    int variant = ctx->variant;
+    int variant = (reuse && reuse->variant >= 0) ? reuse->variant : ctx->variant;
     if (variant == SUSHI_GEMM_AUTO)
         variant = prefer_tc3x(m, n, k, batch, d.sm_count) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+    if (reuse) reuse->variant = variant;
 
     if (variant == SUSHI_GEMM_TC3X)
     {
-        const size_t bytes_a = sushi::split_plane_bytes(m, k, batch);
+        // workspace: [planes of op(B)^T][planes of op(A)] -- B first so that slabs of A of any
+        // size can follow without moving it
+        const int64_t a_rows = (reuse && reuse->max_rows > m) ? reuse->max_rows : m;
+        const size_t bytes_a = sushi::split_plane_bytes(a_rows, k, batch);
         const size_t bytes_b = sushi::split_plane_bytes(n, k, batch);
         int rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_a + bytes_b);
         if (rc != SUSHI_CUDA_OK) return rc;
-        float* planes_a = static_cast<float*>(d.workspace);
-        float* planes_b = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_a);
-        if ((rc = timing_mark(ctx, d, 0, 2)) != SUSHI_CUDA_OK) return rc;
+        float* planes_b = static_cast<float*>(d.workspace);
+        float* planes_a = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b);
+        const bool split_b = !(reuse && reuse->b_planes_ready);
+        if ((rc = timing_mark(ctx, d, 0, split_b ? 2 : 1)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::launch_split_tf32(a, planes_a, m, k, lda, sa, batch, /*k_contig=*/!ta, d.sm_count, d.stream));
-        SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b, n, k, ldb, sb, batch, /*k_contig=*/tb != 0, d.sm_count, d.stream));
+        if (split_b)
+            SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b, n, k, ldb, sb, batch, /*k_contig=*/tb != 0, d.sm_count, d.stream));
+        if (reuse) reuse->b_planes_ready = true;
+        void* sk_area = nullptr;
+        if (ctx->stream_k)
+        {
+            int64_t tiles = 0, num_kb = 0;
+            sushi::tc3x::tile_counts(m, n, k, batch, &tiles, &num_kb);
+            const size_t need = sushi::tc3x::sk_area_bytes(sushi::tc3x::plan_tail(tiles, num_kb, d.sm_count, true));
+            if (need > d.sk_area_bytes)
+            {
+                // grown on demand (outside the kernel-timing marks); flags start at zero
+                if ((rc = grow(ctx, d, &d.sk_area, &d.sk_area_bytes, need)) != SUSHI_CUDA_OK) return rc;
+                SC_CUDA(ctx, cudaMemsetAsync(d.sk_area, 0, sushi::tc3x::SK_FLAG_BYTES, d.stream));
+            }
+            if (need > 0)
+            {
+                sk_area = d.sk_area;
+                if (++d.sk_epoch == 0)
+                {
+                    // 2^32 launches later: start the epochs over on clean flags
+                    SC_CUDA(ctx, cudaMemsetAsync(d.sk_area, 0, sushi::tc3x::SK_FLAG_BYTES, d.stream));
+                    d.sk_epoch = 1;
+                }
+            }
+        }
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(planes_a, planes_b, c, m, n, k, ldc, sc, batch, alpha, beta,
-                                                   d.status, d.sm_count, d.stream));
+                                                   d.status, d.sm_count, d.stream,
+                                                   sk_area, d.sk_epoch));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
-        ctx->launches += 3;
+        ctx->launches += split_b ? 3 : 2;
         return SUSHI_CUDA_OK;
     }
 
@@ -335,6 +379,7 @@ extern "C" int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx
     }
     sushi_cuda_ctx* ctx = new sushi_cuda_ctx();
     ctx->variant = check_variant_env(SUSHI_GEMM_AUTO);
+    if (const char* e = getenv("SUSHI_SPLIT_K")) ctx->stream_k = atoi(e) != 0;
     for (int id : ids)
     {
         if (id < 0 || id >= count)
@@ -381,6 +426,7 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         cudaSetDevice(d.device);
         if (d.own_stream) cudaStreamSynchronize(d.own_stream);
         if (d.workspace) cudaFree(d.workspace);
+        if (d.sk_area) cudaFree(d.sk_area);
         for (void* s : d.stage) if (s) cudaFree(s);
         if (d.status) cudaFree(d.status);
         if (d.status_host) cudaFreeHost(d.status_host);
@@ -757,6 +803,11 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     slabs = (block + slab_rows - 1) / slab_rows;
     if ((rc = ensure_events(ctx, (size_t)slabs)) != SUSHI_CUDA_OK) return rc;
     SC_CUDA(ctx, cudaSetDevice(d->device));
+    // one kernel family for the whole block, B split into planes once, A planes sized for a slab
+    SlabReuse reuse;
+    if (ctx->variant == SUSHI_GEMM_AUTO)
+        reuse.variant = (count > 0 && prefer_tc3x(count, n, k, 1, d->sm_count)) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+    reuse.max_rows = slab_rows < count ? slab_rows : count;
     for (int64_t s = 0; s < slabs; ++s)
     {
         const int64_t u0 = s * slab_rows, u1 = (u0 + slab_rows < block) ? u0 + slab_rows : block;
@@ -765,7 +816,7 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
         {
             const float* a_slab = trans_a ? a_local + lo : a_local + lo * lda;
             rc = run_gemm(ctx, *d, trans_a, trans_b, hi - lo, n, k, alpha, a_slab, lda, 0, b, ldb, 0, beta,
-                          c_block + lo * ldc, ldc, 0, 1);
+                          c_block + lo * ldc, ldc, 0, 1, &reuse);
             if (rc != SUSHI_CUDA_OK) return rc;
         }
         SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[s], d->stream));

@@ -49,6 +49,8 @@ def main():
         a_local = (a[:, first:first + count] if ta else a[first:first + count]).contiguous()
         c_shard = c_in.clone()
         torch.cuda.synchronize()
+        # same kernel family on both sides (the automatic choice depends on the block size)
+        ctx.set_gemm_variant(2 if m >= 1024 else 1)
         ctx.sgemm_row_sharded(ta, 0, m, n, k, alpha, a_local, count if ta else k, b, n, beta, c_shard, n, gather=True)
         c_one = c_in.clone()
         ctx.sgemm(ta, 0, m, n, k, alpha, a, m if ta else k, b, n, beta, c_one, n)
@@ -64,6 +66,7 @@ def main():
         b = full(22, batch * k, n).view(batch, k, n)
         first, count = partition(batch, world, rank)
         c_shard = torch.full((batch, m, n), float("nan"), device=dev)
+        ctx.set_gemm_variant(2 if m >= 256 else 1)
         ctx.sgemm_batch_sharded(0, 0, m, n, k, 1.0, a[first:first + count].contiguous() if count else a, k, m * k,
                                 b[first:first + count].contiguous() if count else b, n, k * n, 0.0, c_shard, n, m * n,
                                 batch, gather=True)

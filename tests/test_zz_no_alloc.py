@@ -38,12 +38,17 @@ def _case(ctx, stream, ta, tb, m, n, k, alpha, beta, seed):
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     got, want = c_new.cpu().numpy(), c_old.cpu().numpy()
-    # same kernels, same order of operations: identical bits ...
-    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from sushi_cuda_sgemm"
-    # ... and inside the tolerance the parity tests use against the fp64 oracle
+    # Same pre-pass and the same tensor-core kernel; only the work distribution may differ (the
+    # regular entry point can cut few-tile problems along K through its context-owned exchange
+    # area, which reorders the fp32 summation).  So: both inside the tolerance the parity tests use
+    # against the fp64 oracle, and within a few fp32 roundings of each other.
     ref, absab = og.gemm_f64_np(ta, tb, m, n, k, alpha, ha, ac, 0, hb, bc, 0, beta, hc, n, 0, 1)
-    r, _ = og.tolerance_ratio(got[None], ref, absab, k, beta=beta, c_in=hc[None], budget=0.5)
-    assert r <= 1.0, r
+    for name, out in (("static_scratch", got), ("regular", want)):
+        r, _ = og.tolerance_ratio(out[None], ref, absab, k, beta=beta, c_in=hc[None], budget=0.5)
+        assert r <= 1.0, (name, r)
+    scale = 2.0 ** -24 * (np.abs(alpha) * absab[0] + np.abs(beta * hc))
+    assert np.all(np.abs(got.astype(np.float64) - want) <= 64.0 * scale + 1e-30), \
+        f"max difference {np.abs(got - want).max()} between the two entry points"
 
 
 def test_static_scratch_matches_regular_entry_point_twice_in_a_row(ctx):
