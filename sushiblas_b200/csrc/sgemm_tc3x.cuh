@@ -17,6 +17,15 @@
 //   warps 2..9  epilogue: tcgen05.ld (32 lanes x 32 columns), transpose through swizzled
 //               shared memory, then alpha*acc + beta*C with 128-bit stores that are
 //               contiguous along each row of C (8 lanes cover one 128-byte row segment)
+// In-kernel split: an operand whose k index is contiguous in memory (A not transposed, B
+// transposed) and whose leading dimension / base are 16-byte aligned can skip the pre-pass: TMA
+// loads its raw fp32 tile (3-D map over the user's matrix, zero fill outside M/N/K) into the hi
+// slot of the stage, and the eight epilogue warps -- idle during the main loop -- rewrite it in
+// place as hi = rna_tf32(x) and store lo = rna_tf32(x - hi) into the lo slot (element-wise, so the
+// TMA swizzle is preserved), fence the generic-proxy writes towards the async proxy and arrive on
+// a per-stage "converted" barrier that the MMA warp then waits on instead of the TMA barrier.
+// This removes 12 B/element of pre-pass traffic and halves that operand's read traffic.
+//
 // Why 256 x 256: with both planes of both operands streamed per k-block, a CTA moves
 // 8*(BM+BN) bytes per 3*BM*BN tensor-core MACs; 256 x 256 keeps that at ~43 B/clk/SM of L2
 // bandwidth at full tensor rate, where 128 x 256 would need 64 B/clk/SM.
@@ -60,7 +69,7 @@ constexpr unsigned long long DRAIN_LIMIT_NS = 2000000ull;    // 2 ms per drain w
 
 // status codes written to *status (first writer wins)
 enum : int { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA_FULL = 2, ST_TIMEOUT_MMA_ACC = 3,
-             ST_TIMEOUT_EPILOGUE = 4, ST_TIMEOUT_PARTIAL_FLAG = 5, ST_TIMEOUT_PARTIAL_PUBLISH = 6 };
+             ST_TIMEOUT_EPILOGUE = 4, ST_TIMEOUT_PARTIAL_FLAG = 5, ST_TIMEOUT_PARTIAL_PUBLISH = 6, ST_TIMEOUT_CONVERT = 7 };
 
 constexpr int SK_SLOT_FLOATS = BM * BN;               // one raw accumulator tile per published slice
 constexpr int SK_MAX_SPLIT = 4;                       // at most this many K slices per tile
@@ -81,6 +90,7 @@ struct Params
     int64_t dp_tiles;              // tiles [0, dp_tiles) are dealt whole, round-robin over the grid
     int32_t sk_tiles;              // tiles [dp_tiles, dp_tiles + sk_tiles) are cut along K (0: none)
     int32_t sk_split;              // number of K slices per cut tile (>= 2 when sk_tiles > 0)
+    int32_t raw_mask;              // bit 0: A arrives raw (split in kernel); bit 1: B arrives raw
     float* sk_partials;            // [sk_tiles * (sk_split-1)][256*256] raw accumulators of slices 0 .. S-2
     unsigned int* sk_flags;        // [sk_tiles * (sk_split-1)] epoch of the slot's last publication
     unsigned int sk_epoch;         // this launch's epoch (never 0)
@@ -191,6 +201,27 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// hi = rna_tf32(x), lo = rna_tf32(x - hi); inf / nan stay in hi only.
+__device__ __forceinline__ void split_tf32_1(float x, float& hi, float& lo)
+{
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    const float r = x - hi;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
+    lo = (fabsf(hi) <= 3.402823466e+38f) ? __uint_as_float(l) : 0.0f;
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -263,6 +294,7 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t t, int32_t tiles_m, int
 
 __global__ void __launch_bounds__(THREADS, 1)
 sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap raw_a, const __grid_constant__ CUtensorMap raw_b,
                   const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -271,20 +303,25 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint8_t* stage_base = smem;
     uint8_t* epi_base = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(epi_base + EPI_WARPS * EPI_STAGE_BYTES);
-    // bars[0..2] full, [3..5] empty, [6] acc_full, [7..8] acc_empty, [9] drain, [10] partial written
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 12);
+    // bars[0..2] full, [3..5] empty, [6] acc_full, [7..8] acc_empty, [9] drain, [10] partial written,
+    // [11..13] converted (raw operands split in place)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 15);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     const uint32_t full0 = smem_u32(bars + 0), empty0 = smem_u32(bars + 3);
     const uint32_t acc_full = smem_u32(bars + 6), acc_empty0 = smem_u32(bars + 7);
-    const uint32_t drain = smem_u32(bars + 9), partial_done = smem_u32(bars + 10);
+    const uint32_t drain = smem_u32(bars + 9), partial_done = smem_u32(bars + 10), conv0 = smem_u32(bars + 11);
+    const bool a_raw = (p.raw_mask & 1) != 0, b_raw = (p.raw_mask & 2) != 0;
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < STAGES; ++s)
+        {
+            mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); mbar_init(conv0 + 8 * s, EPI_WARPS);
+        }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty0, EPI_WARPS / 2);
         mbar_init(acc_empty0 + 8, EPI_WARPS / 2);
@@ -327,9 +364,11 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     {
                         const uint32_t dst = smem_u32(stage_base + s * STAGE_BYTES);
                         const uint32_t bar = full0 + 8 * s;
-                        mbar_arrive_expect_tx(bar, STAGE_BYTES);
-                        tma_load_4d(dst, &map_a, bar, 0, tc.tm * BM, kb, (int32_t)(tc.bi * 2));
-                        tma_load_4d(dst + OPERAND_BYTES, &map_b, bar, 0, tc.tn * BN, kb, (int32_t)(tc.bi * 2));
+                        mbar_arrive_expect_tx(bar, (a_raw ? PLANE_BYTES : OPERAND_BYTES) + (b_raw ? PLANE_BYTES : OPERAND_BYTES));
+                        if (a_raw) tma_load_3d(dst, &raw_a, bar, kb * BK, tc.tm * BM, (int32_t)tc.bi);
+                        else tma_load_4d(dst, &map_a, bar, 0, tc.tm * BM, kb, (int32_t)(tc.bi * 2));
+                        if (b_raw) tma_load_3d(dst + OPERAND_BYTES, &raw_b, bar, kb * BK, tc.tn * BN, (int32_t)tc.bi);
+                        else tma_load_4d(dst + OPERAND_BYTES, &map_b, bar, 0, tc.tn * BN, kb, (int32_t)(tc.bi * 2));
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
@@ -362,7 +401,9 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 int okl = 1;
                 if (lane == 0)
                 {
-                    okl = mbar_wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, WAIT_LIMIT_NS);
+                    // raw operands: wait for the converter warps (which waited for the TMA data)
+                    okl = mbar_wait_bounded((p.raw_mask ? conv0 : full0) + 8 * s, ph, abort_flag, p.status,
+                                            ST_TIMEOUT_MMA_FULL, WAIT_LIMIT_NS);
                     if (okl && kb == w.kb0)
                     {
                         // both accumulator halves must have been drained by the previous tile's epilogue
@@ -418,12 +459,48 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         float4* stg = reinterpret_cast<float4*>(epi_base + ew * EPI_STAGE_BYTES);   // [32 rows][8 float4]
         const bool has_beta = (p.beta != 0.0f);
         const int rsub = lane >> 3, c4 = lane & 7;
-        uint32_t tl = 0, published = 0;
+        uint32_t tl = 0, published = 0, it = 0;
         bool ok = true;
         WorkItem w;
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx, ++tl)
         {
             const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+            if (p.raw_mask)
+            {
+                // converter duty: split the raw operand tiles of every stage of this run in place
+                const int te = ew * 32 + lane;                       // 0..255
+                for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
+                {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    const int okc = mbar_wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_CONVERT, WAIT_LIMIT_NS);
+                    ok = __all_sync(0xffffffffu, okc) != 0;
+                    if (!ok) break;
+                    uint8_t* stage = stage_base + s * STAGE_BYTES;
+#pragma unroll
+                    for (int op = 0; op < 2; ++op)
+                    {
+                        if (!((p.raw_mask >> op) & 1)) continue;
+                        float4* hi = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES);
+                        float4* lo = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES + PLANE_BYTES);
+#pragma unroll
+                        for (int j = 0; j < PLANE_BYTES / 16 / (EPI_WARPS * 32); ++j)
+                        {
+                            const int e = te + j * (EPI_WARPS * 32);
+                            const float4 x = hi[e];
+                            float4 h4, l4;
+                            split_tf32_1(x.x, h4.x, l4.x); split_tf32_1(x.y, h4.y, l4.y);
+                            split_tf32_1(x.z, h4.z, l4.z); split_tf32_1(x.w, h4.w, l4.w);
+                            hi[e] = h4;
+                            lo[e] = l4;
+                        }
+                    }
+                    // generic-proxy writes must be visible to the tensor core's async-proxy reads
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(conv0 + 8 * s);
+                }
+                if (!ok) break;
+            }
             int okl = mbar_wait_bounded(acc_full, tl & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
             if (okl && w.kind == 2)
             {
@@ -680,9 +757,46 @@ inline void tile_counts(int64_t m, int64_t n, int64_t k, int64_t batch, int64_t*
 }
 
 // planes_a / planes_b as written by launch_split_tf32 for op(A) (rows = m) and op(B)^T (rows = n).
+// Tensor map over a user operand whose k index is contiguous: element (row, kk) at
+// base[bi*stride + row*ld + kk]; box = {16 k, 256 rows, 1}; outside rows/k reads as zero.
+inline bool make_raw_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int64_t stride,
+                         int64_t batch)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t gdim[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t gstr[2] = {(cuuint64_t)ld * 4, (cuuint64_t)(batch > 1 ? stride : rows * ld) * 4};
+    cuuint32_t box[3] = {(cuuint32_t)BK, 256u, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// True when a k-contiguous operand can be fetched raw by TMA: 16-byte aligned base, leading
+// dimension and batch stride multiples of 4 floats, extents within the tensor-map limits.
+inline bool raw_eligible(const float* base, int64_t rows, int64_t k, int64_t ld, int64_t stride, int64_t batch)
+{
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld & 3) != 0) return false;
+    if (batch > 1 && ((stride & 3) != 0 || stride <= 0)) return false;
+    if (ld * 4 >= (1ll << 40) || (batch > 1 ? stride : rows * ld) * 4 >= (1ll << 40)) return false;
+    return rows > 0 && k > 0 && rows < (1ll << 32) && k < (1ll << 32);
+}
+
+// One operand of the GEMM kernel: either pre-split planes (split_tf32.cuh) or the raw
+// k-contiguous user matrix.
+struct OperandSource
+{
+    const float* planes = nullptr;     // pre-split hi/lo planes, or
+    const float* raw = nullptr;        // raw operand: element (row, kk) at raw[bi*stride + row*ld + kk]
+    int64_t ld = 0, stride = 0;
+};
+
+// a / b: op(A) (rows = m) and op(B)^T (rows = n).
 // sk_area: zero-initialised exchange area of at least sk_area_bytes(plan) bytes, or nullptr to
 // deal whole tiles only; sk_epoch: a value never used before with this area (and never 0).
-inline cudaError_t launch_sgemm_tc3x(const float* planes_a, const float* planes_b, float* c,
+inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource& b, float* c,
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
                                      float alpha, float beta, int* status, int sm_count, cudaStream_t st,
                                      void* sk_area = nullptr, unsigned int sk_epoch = 0)
@@ -692,10 +806,13 @@ inline cudaError_t launch_sgemm_tc3x(const float* planes_a, const float* planes_
     if (e != cudaSuccess) return e;
     const int64_t m_pad = (m + 255) / 256 * 256, n_pad = (n + 255) / 256 * 256;
     const int64_t num_kb = (k + BK - 1) / BK;
-    CUtensorMap map_a, map_b;
-    if (!make_plane_map(&map_a, planes_a, m_pad, num_kb, batch)) return cudaErrorInvalidValue;
-    if (!make_plane_map(&map_b, planes_b, n_pad, num_kb, batch)) return cudaErrorInvalidValue;
+    CUtensorMap map_a, map_b, raw_a, raw_b;
     Params p;
+    p.raw_mask = (a.raw ? 1 : 0) | (b.raw ? 2 : 0);
+    if (a.raw) { if (!make_raw_map(&raw_a, a.raw, m, k, a.ld, a.stride, batch)) return cudaErrorInvalidValue; map_a = raw_a; }
+    else { if (!make_plane_map(&map_a, a.planes, m_pad, num_kb, batch)) return cudaErrorInvalidValue; raw_a = map_a; }
+    if (b.raw) { if (!make_raw_map(&raw_b, b.raw, n, k, b.ld, b.stride, batch)) return cudaErrorInvalidValue; map_b = raw_b; }
+    else { if (!make_plane_map(&map_b, b.planes, n_pad, num_kb, batch)) return cudaErrorInvalidValue; raw_b = map_b; }
     p.c = c; p.m = m; p.n = n; p.ldc = ldc; p.stride_c = stride_c;
     p.num_kb = (int32_t)num_kb;
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
@@ -707,7 +824,7 @@ inline cudaError_t launch_sgemm_tc3x(const float* planes_a, const float* planes_
     p.sk_partials = sk_area ? reinterpret_cast<float*>(static_cast<char*>(sk_area) + SK_FLAG_BYTES) : nullptr;
     p.sk_epoch = sk_epoch;
     if (plan.grid <= 0) return cudaSuccess;
-    sgemm_tc3x_kernel<<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    sgemm_tc3x_kernel<<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
     return cudaGetLastError();
 }
 

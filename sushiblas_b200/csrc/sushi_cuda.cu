@@ -75,6 +75,7 @@ struct sushi_cuda_ctx
     int variant = SUSHI_GEMM_AUTO;
     std::atomic<int64_t> launches{0};
     bool timing = false;
+    int fuse_split = 1;                   // in-kernel split of k-contiguous operands: 0 never, 1 by shape, 2 always
     bool stream_k = true;                 // cut the tiles of a partial round along K (SUSHI_SPLIT_K=0 disables)
     // multi-GPU (one process per GPU: a single communicator bound to one device index)
     ncclComm_t comm = nullptr;
@@ -226,18 +227,31 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
 
     if (variant == SUSHI_GEMM_TC3X)
     {
+        // An operand whose k index is contiguous can be split inside the GEMM kernel instead of
+        // by the pre-pass.  The pre-pass costs 12 B per operand element once; the in-kernel split
+        // costs ~10 % of the kernel's tensor rate (shared-memory bandwidth) for every tile that
+        // uses the operand.  Measured break-even on B200: the operand is reused by about eleven
+        // 256-wide tiles, so A is split in-kernel when n <= 2048 and B when m <= 2048
+        // (SUSHI_FUSE_SPLIT=0: never, =2: whenever eligible).
+        const bool want_a = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && n <= 2048);
+        const bool want_b = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && m <= 2048);
+        const bool fuse_a = want_a && !ta && sushi::tc3x::raw_eligible(a, m, k, lda, sa, batch);
+        const bool fuse_b = want_b && tb && sushi::tc3x::raw_eligible(b, n, k, ldb, sb, batch);
         // workspace: [planes of op(B)^T][planes of op(A)] -- B first so that slabs of A of any
         // size can follow without moving it
         const int64_t a_rows = (reuse && reuse->max_rows > m) ? reuse->max_rows : m;
-        const size_t bytes_a = sushi::split_plane_bytes(a_rows, k, batch);
-        const size_t bytes_b = sushi::split_plane_bytes(n, k, batch);
-        int rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_a + bytes_b);
-        if (rc != SUSHI_CUDA_OK) return rc;
+        const size_t bytes_a = fuse_a ? 0 : sushi::split_plane_bytes(a_rows, k, batch);
+        const size_t bytes_b = fuse_b ? 0 : sushi::split_plane_bytes(n, k, batch);
+        int rc = SUSHI_CUDA_OK;
+        if (bytes_a + bytes_b > 0 && (rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_a + bytes_b)) != SUSHI_CUDA_OK)
+            return rc;
         float* planes_b = static_cast<float*>(d.workspace);
         float* planes_a = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b);
-        const bool split_b = !(reuse && reuse->b_planes_ready);
-        if ((rc = timing_mark(ctx, d, 0, split_b ? 2 : 1)) != SUSHI_CUDA_OK) return rc;
-        SC_CUDA(ctx, sushi::launch_split_tf32(a, planes_a, m, k, lda, sa, batch, /*k_contig=*/!ta, d.sm_count, d.stream));
+        const bool split_b = !fuse_b && !(reuse && reuse->b_planes_ready);
+        const int prepass_launches = (fuse_a ? 0 : 1) + (split_b ? 1 : 0);
+        if ((rc = timing_mark(ctx, d, 0, prepass_launches)) != SUSHI_CUDA_OK) return rc;
+        if (!fuse_a)
+            SC_CUDA(ctx, sushi::launch_split_tf32(a, planes_a, m, k, lda, sa, batch, /*k_contig=*/!ta, d.sm_count, d.stream));
         if (split_b)
             SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b, n, k, ldb, sb, batch, /*k_contig=*/tb != 0, d.sm_count, d.stream));
         if (reuse) reuse->b_planes_ready = true;
@@ -249,7 +263,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
             const size_t need = sushi::tc3x::sk_area_bytes(sushi::tc3x::plan_tail(tiles, num_kb, d.sm_count, true));
             if (need > d.sk_area_bytes)
             {
-                // grown on demand (outside the kernel-timing marks); flags start at zero
+                // grown on demand; flags start at zero
                 if ((rc = grow(ctx, d, &d.sk_area, &d.sk_area_bytes, need)) != SUSHI_CUDA_OK) return rc;
                 SC_CUDA(ctx, cudaMemsetAsync(d.sk_area, 0, sushi::tc3x::SK_FLAG_BYTES, d.stream));
             }
@@ -264,12 +278,14 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
                 }
             }
         }
+        sushi::tc3x::OperandSource src_a, src_b;
+        if (fuse_a) { src_a.raw = a; src_a.ld = lda; src_a.stride = sa; } else src_a.planes = planes_a;
+        if (fuse_b) { src_b.raw = b; src_b.ld = ldb; src_b.stride = sb; } else src_b.planes = planes_b;
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
-        SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(planes_a, planes_b, c, m, n, k, ldc, sc, batch, alpha, beta,
-                                                   d.status, d.sm_count, d.stream,
-                                                   sk_area, d.sk_epoch));
+        SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,
+                                                   d.status, d.sm_count, d.stream, sk_area, d.sk_epoch));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
-        ctx->launches += split_b ? 3 : 2;
+        ctx->launches += 1 + prepass_launches;
         return SUSHI_CUDA_OK;
     }
 
@@ -380,6 +396,7 @@ extern "C" int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx
     sushi_cuda_ctx* ctx = new sushi_cuda_ctx();
     ctx->variant = check_variant_env(SUSHI_GEMM_AUTO);
     if (const char* e = getenv("SUSHI_SPLIT_K")) ctx->stream_k = atoi(e) != 0;
+    if (const char* e = getenv("SUSHI_FUSE_SPLIT")) ctx->fuse_split = atoi(e);
     for (int id : ids)
     {
         if (id < 0 || id >= count)
@@ -956,7 +973,10 @@ extern "C" int sushi_cuda_sgemm_static_scratch(void* cuda_stream, int trans_a, i
     float* planes_b = reinterpret_cast<float*>(reinterpret_cast<char*>(sd.scratch) + bytes_a);
     SC_CUDA(nullptr, sushi::launch_split_tf32(a, planes_a, m, k, lda, 0, 1, /*k_contig=*/!trans_a, sd.sm_count, st));
     SC_CUDA(nullptr, sushi::launch_split_tf32(b, planes_b, n, k, ldb, 0, 1, /*k_contig=*/trans_b != 0, sd.sm_count, st));
-    SC_CUDA(nullptr, sushi::tc3x::launch_sgemm_tc3x(planes_a, planes_b, c, m, n, k, ldc, 0, 1, alpha, beta, status,
+    sushi::tc3x::OperandSource src_a, src_b;
+    src_a.planes = planes_a;
+    src_b.planes = planes_b;
+    SC_CUDA(nullptr, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, 0, 1, alpha, beta, status,
                                                    sd.sm_count, st));
     return SUSHI_CUDA_OK;
 }

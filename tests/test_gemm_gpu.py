@@ -220,6 +220,25 @@ def test_tc3x_split_k_tail_integer_exact(ctx):
         check(ctx, TC3X, 0, 0, 1024, 1024, 640, 1.5, 0.5)
 
 
+def test_tc3x_in_kernel_split_paths(ctx):
+    """Operands whose k index is contiguous are fetched raw by TMA and split inside the kernel
+    (NT: both operands, NN: A, TT: B); unaligned leading dimensions fall back to the pre-pass.
+    Ragged M, N, K rely on TMA zero fill."""
+    for (ta, tb) in [(0, 1), (0, 0), (1, 1)]:
+        check(ctx, TC3X, ta, tb, 300, 260, 100, 1.5, 0.5)                 # ragged everything, aligned ld
+        check(ctx, TC3X, ta, tb, 1024, 512, 1000, 1.0, 0.0, pad=(4, 8, 0))  # padded but aligned ld
+        check(ctx, TC3X, ta, tb, 257, 129, 77, 1.0, 1.0, pad=(1, 3, 0))     # ld % 4 != 0: pre-pass fallback
+        check(ctx, TC3X, ta, tb, 512, 256, 333, 1.0, 0.0, batch=5)
+    # integer-exact on the fully in-kernel path (NT) with split-K on top
+    rng = np.random.default_rng(5)
+    m, n, k = 1024, 768, 520
+    a = rng.integers(-3, 4, size=(m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(n, k)).astype(np.float32)
+    got = run_gemm(ctx, TC3X, 0, 1, m, n, k, 1.0, a.ravel(), k, 0, b.ravel(), k, 0, 0.0, np.zeros(m * n, np.float32),
+                   n, 0, 1).reshape(m, n)
+    assert np.array_equal(got, (a.astype(np.int64) @ b.astype(np.int64).T).astype(np.float32))
+
+
 def test_auto_matches_explicit_variants(ctx):
     # AUTO picks SIMT for small problems and TC3X for large ones; both are within tolerance
     check(ctx, AUTO, 0, 0, 96, 80, 40, 1.0, 0.0)
@@ -361,6 +380,10 @@ def test_launch_counter_counts_kernels(ctx):
     before = ctx.launch_count()
     check(ctx, SIMT, 0, 0, 64, 64, 64, 1.0, 0.0)
     mid = ctx.launch_count()
-    check(ctx, TC3X, 0, 0, 256, 256, 64, 1.0, 0.0)
-    after = ctx.launch_count()
-    assert mid - before == 1 and after - mid == 3     # split A, split B, GEMM
+    assert mid - before == 1
+    # tensor-core path: one pre-pass launch per operand that is not split inside the GEMM kernel
+    # (k-contiguous operands of small problems are): TN = 2 pre-passes, NN = 1 (B), NT = none
+    for (ta, tb, launches) in [(1, 0, 3), (0, 0, 2), (0, 1, 1)]:
+        start = ctx.launch_count()
+        check(ctx, TC3X, ta, tb, 256, 256, 64, 1.0, 0.0)
+        assert ctx.launch_count() - start == launches, (ta, tb)
