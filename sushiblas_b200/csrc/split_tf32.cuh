@@ -93,38 +93,74 @@ split_tf32_kcontig_kernel(const SplitArgs p)
 }
 
 // The row index is the contiguous one: element (row, kk) = x[kk*ld + row].
-// One CTA per (64 rows, one k-block): reads 16 runs of 64 floats, transposes through shared
-// memory and writes one contiguous 4 KB run per plane.
+// One CTA per (64 rows, 4 k-blocks = 64 k): reads 64 runs of 64 floats (128-bit loads when the
+// operand is 16-byte aligned), transposes through shared memory and writes four contiguous
+// 4 KB runs per plane.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 split_tf32_rcontig_kernel(const SplitArgs p)
 {
-    __shared__ float tile[SPLIT_KB][64 + 1];
+    constexpr int KT = 4 * SPLIT_KB;                 // 64 k per CTA
+    __shared__ float tile[KT][64 + 1];
     const int t = threadIdx.x;
     const int64_t row_tiles = p.rows_pad / 64;
+    const int64_t k_tiles = (p.num_kb + 3) / 4;
     int64_t blk = blockIdx.x;
     const int64_t rt = blk % row_tiles; blk /= row_tiles;
-    const int64_t kb = blk % p.num_kb;
-    const int64_t bi = blk / p.num_kb;
-    const int64_t r0 = rt * 64, k0 = kb * SPLIT_KB;
+    const int64_t kt = blk % k_tiles;
+    const int64_t bi = blk / k_tiles;
+    const int64_t r0 = rt * 64, k0 = kt * KT;
     const float* __restrict__ src = p.x + bi * p.stride_x;
 
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
+    if (VEC)
     {
-        const int r = t % 64, kk = t / 64 + 4 * j;
-        float v = 0.0f;
-        if (r0 + r < p.rows && k0 + kk < p.k) v = __ldg(src + (k0 + kk) * p.ld + r0 + r);
-        tile[kk][r] = v;
+        // 16 threads cover one 64-float run; 16 runs per pass
+        const int r4 = (t % 16) * 4, kk0 = t / 16;
+#pragma unroll
+        for (int j = 0; j < KT / 16; ++j)
+        {
+            const int kk = kk0 + 16 * j;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + kk < p.k)
+            {
+                const float* q = src + (k0 + kk) * p.ld + r0 + r4;
+                if (r0 + r4 + 3 < p.rows) v = __ldg(reinterpret_cast<const float4*>(q));
+                else
+                {
+                    if (r0 + r4 + 0 < p.rows) v.x = __ldg(q + 0);
+                    if (r0 + r4 + 1 < p.rows) v.y = __ldg(q + 1);
+                    if (r0 + r4 + 2 < p.rows) v.z = __ldg(q + 2);
+                }
+            }
+            tile[kk][r4 + 0] = v.x; tile[kk][r4 + 1] = v.y; tile[kk][r4 + 2] = v.z; tile[kk][r4 + 3] = v.w;
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < KT / 4; ++j)
+        {
+            const int r = t % 64, kk = t / 64 + 4 * j;
+            float v = 0.0f;
+            if (r0 + r < p.rows && k0 + kk < p.k) v = __ldg(src + (k0 + kk) * p.ld + r0 + r);
+            tile[kk][r] = v;
+        }
     }
     __syncthreads();
     const int row = t / 4, q = t % 4;
-    float4 hi, lo;
-    split_one(tile[q * 4 + 0][row], hi.x, lo.x);
-    split_one(tile[q * 4 + 1][row], hi.y, lo.y);
-    split_one(tile[q * 4 + 2][row], hi.z, lo.z);
-    split_one(tile[q * 4 + 3][row], hi.w, lo.w);
-    *reinterpret_cast<float4*>(p.planes + plane_offset(p, bi, 0, kb, r0 + row) + q * 4) = hi;
-    *reinterpret_cast<float4*>(p.planes + plane_offset(p, bi, 1, kb, r0 + row) + q * 4) = lo;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+    {
+        const int64_t kb = kt * 4 + b;
+        if (kb >= p.num_kb) break;
+        float4 hi, lo;
+        split_one(tile[b * SPLIT_KB + q * 4 + 0][row], hi.x, lo.x);
+        split_one(tile[b * SPLIT_KB + q * 4 + 1][row], hi.y, lo.y);
+        split_one(tile[b * SPLIT_KB + q * 4 + 2][row], hi.z, lo.z);
+        split_one(tile[b * SPLIT_KB + q * 4 + 3][row], hi.w, lo.w);
+        *reinterpret_cast<float4*>(p.planes + plane_offset(p, bi, 0, kb, r0 + row) + q * 4) = hi;
+        *reinterpret_cast<float4*>(p.planes + plane_offset(p, bi, 1, kb, r0 + row) + q * 4) = lo;
+    }
 }
 
 inline size_t split_plane_bytes(int64_t rows, int64_t k, int64_t batch)
@@ -154,9 +190,11 @@ inline cudaError_t launch_split_tf32(const float* x, float* planes, int64_t rows
     }
     else
     {
-        const int64_t blocks = (p.rows_pad / 64) * p.num_kb * batch;
+        const int64_t blocks = (p.rows_pad / 64) * ((p.num_kb + 3) / 4) * batch;
         if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-        split_tf32_rcontig_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+        const bool vec = ((ld & 3) == 0) && ((stride_x & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+        if (vec) split_tf32_rcontig_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(p);
+        else split_tf32_rcontig_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(p);
     }
     return cudaGetLastError();
 }
