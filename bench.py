@@ -253,16 +253,29 @@ def run_ours(args):
     # ---- device-resident inputs (rows [first, first+count) of the global A, all of B)
     a = torch.empty(count, k, device=device) if w["sharded"] else torch.empty(m, k, device=device)
     b = torch.empty(k, n, device=device)
-    c = torch.empty(m, n, device=device)
+    gather_mode = 1
+    c_raw = None
+    if world > 1 and args.gather == "fused":
+        # C lives in a plain cudaMalloc block so that it can be mapped into the peers (CUDA IPC):
+        # the GEMM epilogue then stores finished tiles straight into every rank's C over NVLink
+        c_raw = ctx.malloc(m * n * 4)
+        handles = [None] * world
+        dist.all_gather_object(handles, ctx.ipc_export(c_raw))
+        opened = [ctx.ipc_open(handles[r]) if r != rank else None for r in range(world)]
+        ctx.comm_set_peer_buffers([c_raw if r == rank else opened[r] for r in range(world)], m * n * 4)
+        c = c_raw
+        gather_mode = 2
+    else:
+        c = torch.empty(m, n, device=device)
     ctx.fill_uniform(a, a.numel(), SEED, first_index=first * k if w["sharded"] else 0)
     ctx.fill_uniform(b, b.numel(), SEED + 1)
-    ctx.fill_uniform(c, c.numel(), SEED + 2)
+    ctx.fill_uniform(c, m * n, SEED + 2)
     ctx.reserve_workspace(workspace_bytes(count if w["sharded"] else m, n, k))
     ctx.sync()
 
     def step():
         if w["sharded"]:
-            ctx.sgemm_row_sharded(0, 0, m, n, k, alpha, a, k, b, n, beta, c, n, gather=True)
+            ctx.sgemm_row_sharded(0, 0, m, n, k, alpha, a, k, b, n, beta, c, n, gather=gather_mode)
         else:
             for (ta, tb) in w["cases"]:
                 ctx.sgemm(ta, tb, m, n, k, alpha, a, m if ta else k, b, k if tb else n, beta, c, n)
@@ -327,7 +340,8 @@ def run_ours(args):
     # ---- end to end through the C ABI with pinned HOST buffers (copies inside the timed region)
     e2e = None
     if not args.no_e2e:
-        e2e = measure_e2e(ctx, torch, np, w, world, rank, first, count, barrier, max_over_ranks, stream, a, b, c)
+        e2e = measure_e2e(ctx, torch, np, w, world, rank, first, count, barrier, max_over_ranks, stream, a, b, c,
+                          gather_mode)
 
     extras = {}
     if world == 1 and not args.no_extras and name == "sgemm_4096_nn_nt_tn_tt":
@@ -349,7 +363,9 @@ def run_ours(args):
             "config": {"workload": name, "m": m, "n": n, "k": k, "alpha": alpha, "beta": beta,
                        "transposes": ["NT"[ta] + "NT"[tb] for ta, tb in w["cases"]],
                        "arithmetic": "3xTF32 on tcgen05 (hi/lo split), fp32 accumulate in TMEM",
-                       "partition": f"row blocks of A over {world} GPU(s), B replicated, C all-gathered (NCCL)"
+                       "partition": (f"row blocks of A over {world} GPU(s), B replicated, C all-gathered "
+                                     + ("by peer stores fused into the GEMM epilogue (NVLink) + NCCL barrier"
+                                        if gather_mode == 2 else "with NCCL, slab-pipelined"))
                        if w["sharded"] else "single GPU",
                        "l2": "no flush needed: operands + split planes per GEMM exceed the 126 MB L2 "
                              f"({alg_bytes / 2**20:.0f} MiB operands, {workspace_bytes(count if w['sharded'] else m, n, k) / 2**20:.0f} MiB planes)"},
@@ -358,12 +374,22 @@ def run_ours(args):
         }
         line.update(extras)
         print(json.dumps(line), flush=True)
+    if gather_mode == 2:
+        # unmap the peers' buffers only after every rank has finished using them
+        ctx.sync()
+        barrier()
+        ctx.comm_set_peer_buffers([], 0)
+        for r in range(world):
+            if r != rank:
+                ctx.ipc_close(opened[r])
+        barrier()
+        ctx.free(c_raw)
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def measure_e2e(ctx, torch, np, w, world, rank, first, count, barrier, max_over_ranks, stream, a, b, c):
+def measure_e2e(ctx, torch, np, w, world, rank, first, count, barrier, max_over_ranks, stream, a, b, c, gather_mode=1):
     """Same metric through the C ABI with HOST buffers: every step copies its inputs from
     pinned host memory to the device and the step's result back."""
     m, n, k, alpha, beta = w["m"], w["n"], w["k"], w["alpha"], w["beta"]
@@ -379,7 +405,9 @@ def measure_e2e(ctx, torch, np, w, world, rank, first, count, barrier, max_over_
     pc, hc = pinned(rows * n)
     # host images of the same synthetic operands (device -> host once, outside the timed region)
     ctx.memcpy_d2h(ha, a, ha.nbytes); ctx.memcpy_d2h(hb, b, hb.nbytes)
-    ctx.memcpy_d2h(hc, c[first:first + rows] if w["sharded"] else c, hc.nbytes)
+    from sushiblas_b200.capi import _addr
+    c_block = _addr(c) + first * n * 4 if w["sharded"] else _addr(c)      # this rank's rows of C
+    ctx.memcpy_d2h(hc, c_block, hc.nbytes)
     ctx.sync()
     steps, warm = (3, 1) if w["sharded"] else (5, 2)
 
@@ -387,8 +415,8 @@ def measure_e2e(ctx, torch, np, w, world, rank, first, count, barrier, max_over_
         def step():
             ctx.memcpy_h2d(a, ha, ha.nbytes)
             ctx.memcpy_h2d(b, hb, hb.nbytes)
-            ctx.sgemm_row_sharded(0, 0, m, n, k, alpha, a, k, b, n, beta, c, n, gather=True)
-            ctx.memcpy_d2h(hc, c[first:first + rows], hc.nbytes)
+            ctx.sgemm_row_sharded(0, 0, m, n, k, alpha, a, k, b, n, beta, c, n, gather=gather_mode)
+            ctx.memcpy_d2h(hc, c_block, hc.nbytes)
         h2d, d2h = ha.nbytes + hb.nbytes, hc.nbytes
     else:
         def step():
@@ -462,6 +490,8 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-extras", action="store_true", help="skip the 32768^3 single-GPU base measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU exchange of C: peer stores fused into the GEMM epilogue, or slab-pipelined NCCL")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -185,6 +185,17 @@ SUSHI_CUDA_API int sushi_cuda_comm_unique_id(void* id128);
 SUSHI_CUDA_API int sushi_cuda_comm_init_rank(sushi_cuda_ctx* ctx, int dev, const void* id128, int nranks, int rank);
 SUSHI_CUDA_API int sushi_cuda_comm_destroy(sushi_cuda_ctx* ctx);
 
+/* Peer-memory exchange for the fused GEMM + all-gather (gather == 2 below).  Each rank exports
+ * the buffer that will hold the full C (it must be the base of a sushi_cuda_malloc allocation),
+ * the host program exchanges the 64-byte handles, every rank opens its peers' handles and
+ * registers the nranks addresses (its own entry = its local pointer) and their common size with
+ * the context; a fused call whose m*n*4 exceeds that size falls back to the NCCL exchange.     */
+SUSHI_CUDA_API int sushi_cuda_ipc_export(sushi_cuda_ctx* ctx, int dev, const void* base_ptr, void* handle64);
+SUSHI_CUDA_API int sushi_cuda_ipc_open(sushi_cuda_ctx* ctx, int dev, const void* handle64, void** peer_ptr);
+SUSHI_CUDA_API int sushi_cuda_ipc_close(sushi_cuda_ctx* ctx, int dev, void* peer_ptr);
+SUSHI_CUDA_API int sushi_cuda_comm_set_peer_buffers(sushi_cuda_ctx* ctx, int dev, void* const* buffers, int count,
+                                                    size_t bytes_each);
+
 /* Row-block sharded GEMM (A NN/TN..., B replicated).  Global problem m x n x k.  `a_local`
  * holds this rank's rows of op(A): for trans_a == 0 the rows [first, first+count) of A
  * (count x k, leading dimension lda); for trans_a != 0 the matching columns of the stored
@@ -192,7 +203,12 @@ SUSHI_CUDA_API int sushi_cuda_comm_destroy(sushi_cuda_ctx* ctx);
  * m x n result buffer on this rank: the rank computes its own row block in place and the
  * blocks are all-gathered (NCCL over NVLink) slab by slab so that the exchange of one slab
  * overlaps the multiplication of the next.  With beta != 0 only the rank's own block of
- * c_full needs valid input.  gather == 0 skips the exchange (C stays sharded).            */
+ * c_full needs valid input.  gather == 0 skips the exchange (C stays sharded).
+ * gather == 2: fused exchange -- one GEMM launch over the whole block whose epilogue warps copy
+ * every finished 256 x 256 tile of C into the peers' buffers with plain NVLink stores while the
+ * next tile is being multiplied, followed by a 4-byte NCCL all-reduce as the cross-rank barrier.
+ * Needs sushi_cuda_comm_set_peer_buffers with c_full as this rank's entry, ldc == n, n % 4 == 0;
+ * otherwise the call falls back to gather == 1.                                            */
 SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                                 int64_t m, int64_t n, int64_t k, float alpha,
                                                 const float* a_local, int64_t lda,

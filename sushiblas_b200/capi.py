@@ -54,6 +54,10 @@ SIGNATURES = {
     "sushi_cuda_comm_unique_id": (_int, [_vp]),
     "sushi_cuda_comm_init_rank": (_int, [_vp, _int, _vp, _int, _int]),
     "sushi_cuda_comm_destroy": (_int, [_vp]),
+    "sushi_cuda_ipc_export": (_int, [_vp, _int, _vp, _vp]),
+    "sushi_cuda_ipc_open": (_int, [_vp, _int, _vp, ctypes.POINTER(_vp)]),
+    "sushi_cuda_ipc_close": (_int, [_vp, _int, _vp]),
+    "sushi_cuda_comm_set_peer_buffers": (_int, [_vp, _int, ctypes.POINTER(_vp), _int, _sz]),
     "sushi_cuda_sgemm_row_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
                                             _f32, _vp, _i64, _int]),
     "sushi_cuda_sgemm_batch_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
@@ -259,8 +263,25 @@ class SushiCuda:
     def comm_destroy(self):
         self._check(self.lib.sushi_cuda_comm_destroy(self._ctx))
 
+    def ipc_export(self, base_ptr, dev: int = 0) -> bytes:
+        buf = ctypes.create_string_buffer(64)
+        self._check(self.lib.sushi_cuda_ipc_export(self._ctx, dev, _addr(base_ptr), buf))
+        return buf.raw
+
+    def ipc_open(self, handle: bytes, dev: int = 0) -> int:
+        out = _vp()
+        self._check(self.lib.sushi_cuda_ipc_open(self._ctx, dev, ctypes.create_string_buffer(handle, 64), ctypes.byref(out)))
+        return out.value
+
+    def ipc_close(self, peer_ptr: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_ipc_close(self._ctx, dev, peer_ptr))
+
+    def comm_set_peer_buffers(self, buffers: Sequence[int], bytes_each: int, dev: int = 0):
+        arr = (_vp * len(buffers))(*buffers)
+        self._check(self.lib.sushi_cuda_comm_set_peer_buffers(self._ctx, dev, arr, len(buffers), bytes_each))
+
     def sgemm_row_sharded(self, trans_a, trans_b, m, n, k, alpha, a_local, lda, b, ldb, beta, c_full, ldc,
-                          gather: bool = True, dev: int = 0):
+                          gather=True, dev: int = 0):
         self._check(self.lib.sushi_cuda_sgemm_row_sharded(
             self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a_local), lda, _addr(b), ldb,
             beta, _addr(c_full), ldc, int(gather)))

@@ -90,6 +90,8 @@ struct Params
     int64_t dp_tiles;              // tiles [0, dp_tiles) are dealt whole, round-robin over the grid
     int32_t sk_tiles;              // tiles [dp_tiles, dp_tiles + sk_tiles) are cut along K (0: none)
     int32_t sk_split;              // number of K slices per cut tile (>= 2 when sk_tiles > 0)
+    int32_t n_peers;               // fused all-gather: finished tiles are also stored to peer_c[0 .. n_peers)
+    float* peer_c[7];              // the address of `c` inside each peer GPU's buffer
     int32_t raw_mask;              // bit 0: A arrives raw (split in kernel); bit 1: B arrives raw
     float* sk_partials;            // [sk_tiles * (sk_split-1)][256*256] raw accumulators of slices 0 .. S-2
     unsigned int* sk_flags;        // [sk_tiles * (sk_split-1)] epoch of the slot's last publication
@@ -651,6 +653,37 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * h);
 
+            if (p.n_peers > 0 && !partial && vec_ok && row_base < p.m)
+            {
+                // Fused all-gather: with the accumulators released (the next run's MMAs proceed),
+                // copy this warp's 32 x 256 region of the finished tile to every peer.  Each
+                // thread re-reads exactly the elements it stored above, so no fence is needed
+                // before the loads; the loads hit L2.
+                for (int chunk = 0; chunk < BN / 32; ++chunk)
+                {
+                    const int64_t gcol = col_base + chunk * 32 + c4 * 4;
+                    if (col_base + chunk * 32 >= p.n) break;
+                    float4 vals[8];
+                    bool live[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                    {
+                        const int64_t grow = row_base + i * 4 + rsub;
+                        live[i] = grow < p.m && gcol + 3 < p.n;
+                        if (live[i]) vals[i] = *reinterpret_cast<const float4*>(cb + grow * p.ldc + gcol);
+                    }
+                    for (int32_t peer = 0; peer < p.n_peers; ++peer)
+                    {
+                        float* pb = p.peer_c[peer] + tc.bi * p.stride_c;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (live[i])
+                                *reinterpret_cast<float4*>(pb + (row_base + i * 4 + rsub) * p.ldc + gcol) = vals[i];
+                    }
+                }
+                __threadfence_system();
+            }
+
             if (partial)
             {
                 // publish the slot: every warp fences its stores and arrives; one thread waits
@@ -799,7 +832,8 @@ struct OperandSource
 inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource& b, float* c,
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
                                      float alpha, float beta, int* status, int sm_count, cudaStream_t st,
-                                     void* sk_area = nullptr, unsigned int sk_epoch = 0)
+                                     void* sk_area = nullptr, unsigned int sk_epoch = 0,
+                                     float* const* peer_c = nullptr, int n_peers = 0)
 {
     // per-device attribute; cheap enough to set on every launch
     cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -808,6 +842,9 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     const int64_t num_kb = (k + BK - 1) / BK;
     CUtensorMap map_a, map_b, raw_a, raw_b;
     Params p;
+    if (n_peers < 0 || n_peers > 7) return cudaErrorInvalidValue;
+    p.n_peers = n_peers;
+    for (int i = 0; i < 7; ++i) p.peer_c[i] = (i < n_peers) ? peer_c[i] : nullptr;
     p.raw_mask = (a.raw ? 1 : 0) | (b.raw ? 2 : 0);
     if (a.raw) { if (!make_raw_map(&raw_a, a.raw, m, k, a.ld, a.stride, batch)) return cudaErrorInvalidValue; map_a = raw_a; }
     else { if (!make_plane_map(&map_a, a.planes, m_pad, num_kb, batch)) return cudaErrorInvalidValue; raw_a = map_a; }

@@ -56,6 +56,7 @@ struct NcclApi
     int (*CommDestroy)(ncclComm_t) = nullptr;
     int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
     int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     int (*GroupStart)() = nullptr;
     int (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
@@ -83,6 +84,10 @@ struct sushi_cuda_ctx
     cudaStream_t comm_stream = nullptr;
     std::vector<cudaEvent_t> slab_events;
     cudaEvent_t comm_done = nullptr;
+    // fused all-gather: every rank's C buffer as addressable from this device (own entry local)
+    std::vector<void*> peer_buffers;
+    size_t peer_bytes = 0;
+    float* barrier_word = nullptr;        // 4-byte operand of the NCCL all-reduce used as a cross-rank barrier
 };
 
 namespace {
@@ -201,6 +206,8 @@ struct SlabReuse
     int variant = -1;          // -1: choose per call
     bool b_planes_ready = false;
     int64_t max_rows = 0;      // largest slab (sizes the A planes once)
+    float* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int n_peers = 0;           // fused all-gather: the GEMM epilogue also stores C to these addresses
 };
 
 int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int64_t n, int64_t k, float alpha,
@@ -283,7 +290,8 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         if (fuse_b) { src_b.raw = b; src_b.ld = ldb; src_b.stride = sb; } else src_b.planes = planes_b;
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,
-                                                   d.status, d.sm_count, d.stream, sk_area, d.sk_epoch));
+                                                   d.status, d.sm_count, d.stream, sk_area, d.sk_epoch,
+                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
         ctx->launches += 1 + prepass_launches;
         return SUSHI_CUDA_OK;
@@ -322,10 +330,11 @@ bool load_nccl(std::string* err)
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
     api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
     api.Broadcast = reinterpret_cast<decltype(api.Broadcast)>(dlsym(h, "ncclBroadcast"));
+    api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(h, "ncclAllReduce"));
     api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(dlsym(h, "ncclGroupStart"));
     api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(dlsym(h, "ncclGroupEnd"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-    if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.Broadcast ||
+    if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.Broadcast || !api.AllReduce ||
         !api.GroupStart || !api.GroupEnd || !api.GetErrorString)
     {
         *err = "libnccl is missing a required symbol";
@@ -725,6 +734,8 @@ extern "C" int sushi_cuda_comm_init_rank(sushi_cuda_ctx* ctx, int dev, const voi
     ctx->comm_dev = dev; ctx->nranks = nranks; ctx->rank = rank;
     SC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
     SC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
+    SC_CUDA(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->barrier_word), 256));
+    SC_CUDA(ctx, cudaMemset(ctx->barrier_word, 0, 256));
     return SUSHI_CUDA_OK;
 }
 
@@ -738,6 +749,9 @@ extern "C" int sushi_cuda_comm_destroy(sushi_cuda_ctx* ctx)
     ctx->slab_events.clear();
     if (ctx->comm_done) { cudaEventDestroy(ctx->comm_done); ctx->comm_done = nullptr; }
     if (ctx->comm_stream) { cudaStreamDestroy(ctx->comm_stream); ctx->comm_stream = nullptr; }
+    if (ctx->barrier_word) { cudaFree(ctx->barrier_word); ctx->barrier_word = nullptr; }
+    ctx->peer_buffers.clear();
+    ctx->peer_bytes = 0;
     ctx->comm_dev = -1; ctx->nranks = 1; ctx->rank = 0;
     return SUSHI_CUDA_OK;
 }
@@ -787,6 +801,57 @@ int ensure_events(sushi_cuda_ctx* ctx, size_t n)
 
 } // namespace
 
+extern "C" int sushi_cuda_ipc_export(sushi_cuda_ctx* ctx, int dev, const void* base_ptr, void* handle64)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !base_ptr || !handle64) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "ipc_export: bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    cudaIpcMemHandle_t h;
+    SC_CUDA(ctx, cudaIpcGetMemHandle(&h, const_cast<void*>(base_ptr)));
+    memcpy(handle64, &h, sizeof h);
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_ipc_open(sushi_cuda_ctx* ctx, int dev, const void* handle64, void** peer_ptr)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !handle64 || !peer_ptr) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "ipc_open: bad argument");
+    *peer_ptr = nullptr;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof h);
+    SC_CUDA(ctx, cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_ipc_close(sushi_cuda_ctx* ctx, int dev, void* peer_ptr)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "ipc_close: bad context or device index");
+    if (!peer_ptr) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaStreamSynchronize(d->stream));
+    SC_CUDA(ctx, cudaIpcCloseMemHandle(peer_ptr));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_comm_set_peer_buffers(sushi_cuda_ctx* ctx, int dev, void* const* buffers, int count,
+                                                size_t bytes_each)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "comm_set_peer_buffers: bad context or device index");
+    if (count == 0) { ctx->peer_buffers.clear(); ctx->peer_bytes = 0; return SUSHI_CUDA_OK; }
+    if (!ctx->comm || ctx->comm_dev != dev || !buffers || count != ctx->nranks || count > 8)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG,
+                         "comm_set_peer_buffers: needs a communicator on this device and one buffer per rank (at most 8)");
+    for (int i = 0; i < count; ++i)
+        if (!buffers[i]) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "comm_set_peer_buffers: null buffer");
+    ctx->peer_buffers.assign(buffers, buffers + count);
+    ctx->peer_bytes = bytes_each;
+    return SUSHI_CUDA_OK;
+}
+
 extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                             int64_t m, int64_t n, int64_t k, float alpha,
                                             const float* a_local, int64_t lda,
@@ -809,6 +874,29 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     float* c_block = c_full + first * ldc;
     if (!do_gather)
         return run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1);
+
+    // Fused exchange: one launch over the whole block; the epilogue stores C tiles to the peers.
+    const bool tensor_path = ctx->variant == SUSHI_GEMM_TC3X ||
+                             (ctx->variant == SUSHI_GEMM_AUTO && count > 0 && prefer_tc3x(count, n, k, 1, d->sm_count));
+    bool all_tensor = tensor_path;
+    if (gather == 2 && (int)ctx->peer_buffers.size() == nranks && ctx->peer_buffers[rank] == c_full && (n & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(c_full) & 15) == 0 && all_tensor && count > 0 &&
+        (size_t)m * (size_t)n * sizeof(float) <= ctx->peer_bytes)
+    {
+        SC_CUDA(ctx, cudaSetDevice(d->device));
+        // barrier 1: every rank has reached this call, so nobody still reads the previous C
+        SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
+        SlabReuse fused;
+        fused.variant = SUSHI_GEMM_TC3X;
+        for (int r = 0; r < nranks; ++r)
+            if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * ldc;
+        rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
+                      &fused);
+        if (rc != SUSHI_CUDA_OK) return rc;
+        // barrier 2: every rank's kernel (and with it its stores into this rank's buffer) is complete
+        SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
+        return SUSHI_CUDA_OK;
+    }
 
     // Slab pipeline: multiply slab s on the compute stream, exchange it on the comm stream.
     const int64_t block = (m + nranks - 1) / nranks;

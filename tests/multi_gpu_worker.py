@@ -3,10 +3,12 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
         --master-port 29511 tests/multi_gpu_worker.py
 
-Each rank multiplies its row block (or batch block) through the sharded C-ABI entry points with
-the NCCL exchange, then compares the gathered result with the same problem computed by this
-rank alone through sushi_cuda_sgemm: the tiles are the same kernels in the same order, so the
-results must be bit-identical.  Exits non-zero on any mismatch.
+Each rank multiplies its row block (or batch block) through the sharded C-ABI entry points --
+NCCL slab exchange and the exchange fused into the GEMM epilogue (peer stores over NVLink) --
+then compares the gathered result with the same problem computed by this rank alone through
+sushi_cuda_sgemm.  Where both sides run the same tiles in the same order the results must be
+bit-identical; the fused case checks that all ranks hold identical bits and that they agree
+with the single-GPU result to fp32 summation order.  Exits non-zero on any mismatch.
 """
 import os
 import sys
@@ -59,6 +61,50 @@ def main():
         if not torch.equal(c_shard, c_one):
             bad = int((c_shard != c_one).sum())
             failures.append(f"row_sharded m={m} n={n} k={k} ta={ta}: {bad} elements differ on rank {rank}")
+
+    # ---- fused GEMM + all-gather: the epilogue stores finished tiles into the peers' buffers
+    import numpy as np
+    for (m, n, k, alpha, beta) in [(4096, 1024, 512, 1.0, 0.0), (2048 * world, 768, 640, 1.5, 0.5), (1000, 512, 256, 1.0, 0.0)]:
+        nbytes = m * n * 4
+        c_mine = ctx.malloc(nbytes)                      # base of a cudaMalloc block: exportable
+        handles = [None] * world
+        dist.all_gather_object(handles, ctx.ipc_export(c_mine))
+        opened = [ctx.ipc_open(handles[r]) if r != rank else None for r in range(world)]
+        ctx.comm_set_peer_buffers([c_mine if r == rank else opened[r] for r in range(world)], nbytes)
+        a = full(31, m, k); b = full(32, k, n); c_in = full(33, m, n)
+        first, count = partition(m, world, rank)
+        ctx.memcpy_d2d(c_mine, c_in, nbytes)
+        ctx.set_gemm_variant(2)
+        for _ in range(2):                               # twice: the second call overwrites the first's C
+            ctx.memcpy_d2d(c_mine, c_in, nbytes)
+            ctx.sync(); dist.barrier()
+            ctx.sgemm_row_sharded(0, 0, m, n, k, alpha, a[first:first + count].contiguous(), k, b, n, beta, c_mine, n,
+                                  gather=2)
+        c_one = c_in.clone()
+        ctx.sgemm(0, 0, m, n, k, alpha, a, k, b, n, beta, c_one, n)
+        got = np.empty((m, n), dtype=np.float32)
+        ctx.memcpy_d2h(got, c_mine, nbytes)
+        ctx.sync()
+        torch.cuda.synchronize()
+        want = c_one.cpu().numpy()
+        # (1) the exchange itself is exact: every rank ends up with the same bits everywhere
+        import zlib
+        sums = [None] * world
+        dist.all_gather_object(sums, zlib.crc32(got.tobytes()))
+        if len(set(sums)) != 1:
+            failures.append(f"fused gather m={m} n={n} k={k}: ranks hold different C ({sums})")
+        # (2) against one GPU computing everything: equal up to the fp32 summation order (a block
+        # with fewer tiles than SMs is cut along K, the full problem may not be)
+        err = float(np.abs(got.astype(np.float64) - want).max())
+        if not err <= 64 * 2.0 ** -24 * (abs(alpha) * k * 0.5 + abs(beta)):
+            failures.append(f"fused gather m={m} n={n} k={k}: max |diff| {err} vs single GPU on rank {rank}")
+        dist.barrier()
+        ctx.comm_set_peer_buffers([], 0)
+        for r in range(world):
+            if r != rank:
+                ctx.ipc_close(opened[r])
+        dist.barrier()
+        ctx.free(c_mine)
 
     # ---- batch-sharded strided-batched GEMM
     for (batch, m, n, k) in [(16, 256, 256, 192), (5, 64, 48, 32)]:
