@@ -1,7 +1,8 @@
 // engine.hpp -- entry object of the library (reference: include/SushiBLAS/engine.hpp:61-194,
 // src/engine.cpp:35-69): holds the runtime context, the deferred task graph, the default
-// layout and the RNG seed; hands out tensors and the BLAS facade.  Only blas() is provided:
-// the other op families of the reference are outside the fp32 GEMM path.
+// layout and the RNG seed; hands out tensors and the op facades.  Only blas() (GEMM) and
+// nonlinear() (ReLU, fusable into a GEMM) are provided: the other op families of the reference
+// are outside the fp32 GEMM path.
 #pragma once
 
 #include <atomic>
@@ -12,6 +13,7 @@
 #include <SushiBLAS/core/common.hpp>
 #include <SushiBLAS/core/logger.hpp>
 #include <SushiBLAS/ops/blas.hpp>
+#include <SushiBLAS/ops/math/nonlinear.hpp>
 #include <SushiBLAS/storage.hpp>
 #include <SushiBLAS/tensor.hpp>
 #include <SushiRuntime/SushiRuntime.h>
@@ -31,6 +33,7 @@ namespace SushiBLAS
             Core::Layout get_layout() const { return default_layout_; }
 
             BLASOps blas() { return BLASOps(*this); }
+            NonLinearOps nonlinear() { return NonLinearOps(*this); }
 
             SushiRuntime::Execution::RuntimeContext& get_context() { return context_; }
             SushiRuntime::Graph::TaskGraph& get_graph() { return graph_; }
@@ -121,8 +124,15 @@ namespace SushiBLAS
         meta.set_param(2, transA);
         meta.set_param(3, transB);
 
+        // a later relu(C) can be folded into this GEMM when C is written densely
+        const bool dense_out = (g.ldc == g.n) && (g.batch == 1 || g.stride_c == g.m * g.n);
+        SushiRuntime::Graph::FusionInfo producer;
+        producer.slot = std::make_shared<SushiRuntime::Graph::EpilogueSlot>();
+        if (dense_out) { producer.out_ptr = C.data(); producer.out_count = g.m * g.n * g.batch; }
+        auto slot = producer.slot;
+
         engine_.get_graph().add_task(meta, reads, writes,
-            [g, oa, ob, oc](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            [g, oa, ob, oc, slot](SushiRuntime::Execution::RuntimeContext& rt) -> int
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
                 // device address of an operand; host-resident operands are staged through their mirror
@@ -144,11 +154,44 @@ namespace SushiBLAS
                 if (rc == SUSHI_CUDA_OK) rc = on_device(oc, g.beta != 0.0f || !dense_c, &dc);
                 if (rc != SUSHI_CUDA_OK) return rc;
                 SB_LOG_INFO("CUDA GEMM [Row-Major]: {}x[{}x{}x{}]", g.batch, g.m, g.n, g.k);
-                rc = sushi_cuda_sgemm_strided_batched(ctx, 0, g.trans_a, g.trans_b, g.m, g.n, g.k, g.alpha, da, g.lda,
-                                                      g.stride_a, db, g.ldb, g.stride_b, g.beta, dc, g.ldc, g.stride_c,
-                                                      g.batch);
+                rc = sushi_cuda_sgemm_strided_batched_ex(ctx, 0, g.trans_a, g.trans_b, g.m, g.n, g.k, g.alpha, da, g.lda,
+                                                         g.stride_a, db, g.ldb, g.stride_b, g.beta, dc, g.ldc, g.stride_c,
+                                                         g.batch, slot->activation);
                 if (rc == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
                     rc = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
+                return rc;
+            }, producer);
+        return SushiRuntime::Execution::Event();
+    }
+
+    // ---------------------------------------------------------------- NonLinearOps::relu
+    inline SushiRuntime::Execution::Event NonLinearOps::relu(Tensor& t)
+    {
+        using namespace SushiRuntime::Graph::Literals;
+        SB_THROW_IF(t.dtype != Core::DataType::FLOAT32, "Unsupported data type for ReLU (the CUDA backend serves FLOAT32 only).");
+        SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
+        float* ptr = t.data_as<float>();
+        const int64_t count = t.num_elements;
+        if (engine_.get_graph().try_fuse_activation(ptr, count, SUSHI_EPILOGUE_RELU)) return SushiRuntime::Execution::Event();
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = "math.nonlinear.relu";
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = "math.nonlinear.relu"_op;
+        auto storage = t.storage;
+        const bool host = storage->host_resident();
+        engine_.get_graph().add_task(meta, {storage->data_ptr}, {storage->data_ptr},
+            [storage, ptr, count, host](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            {
+                sushi_cuda_ctx* ctx = rt.native_handle();
+                char* base = static_cast<char*>(storage->allocator->device_view(storage->data_ptr));
+                if (!base) return SUSHI_CUDA_ERR_OOM;
+                float* dptr = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(ptr) - static_cast<char*>(storage->data_ptr)));
+                const std::size_t bytes = static_cast<std::size_t>(count) * sizeof(float);
+                int rc = SUSHI_CUDA_OK;
+                if (host) rc = sushi_cuda_memcpy_h2d(ctx, 0, dptr, ptr, bytes);
+                if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_relu(ctx, 0, dptr, count);
+                if (rc == SUSHI_CUDA_OK && host) rc = sushi_cuda_memcpy_d2h(ctx, 0, ptr, dptr, bytes);
                 return rc;
             });
         return SushiRuntime::Execution::Event();

@@ -23,6 +23,7 @@
 #include <cstdint>
 #include <cstring>
 #include <functional>
+#include <memory>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -361,6 +362,22 @@ namespace SushiRuntime
         /// Work item of a task: enqueue onto the context's stream, return a sushi_cuda status.
         using HostWork = std::function<int(Execution::RuntimeContext&)>;
 
+        /// Epilogue a producer task applies to its output; shared between the recorded closure and
+        /// the graph so that a later element-wise task can be folded into the producer.
+        struct EpilogueSlot
+        {
+            int activation = 0;        ///< sushi_cuda_epilogue value
+        };
+
+        /// What a producer task writes, for record-time fusion ("TaskMetadata ... for fusers",
+        /// reference task_graph.hpp:99-105): `out_count` contiguous elements at `out_ptr`.
+        struct FusionInfo
+        {
+            void* out_ptr = nullptr;
+            std::int64_t out_count = 0;
+            std::shared_ptr<EpilogueSlot> slot;
+        };
+
         /// Deferred task list.  add_task() records; execute() replays in order on the stream.
         class TaskGraph
         {
@@ -370,10 +387,27 @@ namespace SushiRuntime
                 TaskGraph& operator=(const TaskGraph&) = delete;
 
                 void add_task(const TaskMetadata& meta, const std::vector<void*>& read_access,
-                              const std::vector<void*>& write_access, HostWork work)
+                              const std::vector<void*>& write_access, HostWork work, FusionInfo producer = {})
                 {
-                    tasks_.push_back(Task{meta, read_access, write_access, std::move(work)});
+                    tasks_.push_back(Task{meta, read_access, write_access, std::move(work), std::move(producer)});
                 }
+
+                /// Folds an in-place activation over `count` elements at `ptr` into the task recorded
+                /// just before it, if that task produces exactly this range and has no activation yet.
+                /// Returns true when folded (the caller then records no task of its own).
+                bool try_fuse_activation(void* ptr, std::int64_t count, int activation)
+                {
+                    if (!fusion_enabled_ || tasks_.empty()) return false;
+                    FusionInfo& f = tasks_.back().producer;
+                    if (!f.slot || f.out_ptr != ptr || f.out_count != count || f.slot->activation != 0) return false;
+                    f.slot->activation = activation;
+                    ++fused_;
+                    return true;
+                }
+
+                /// Record-time fusion switch (on by default) and the number of tasks folded so far.
+                void set_fusion(bool on) { fusion_enabled_ = on; }
+                std::size_t fused_count() const { return fused_; }
 
                 /// Number of tasks recorded and not yet executed.
                 std::size_t pending() const { return tasks_.size(); }
@@ -403,9 +437,12 @@ namespace SushiRuntime
                     TaskMetadata meta;
                     std::vector<void*> reads, writes;
                     HostWork work;
+                    FusionInfo producer;
                 };
                 Execution::RuntimeContext& ctx_;
                 std::vector<Task> tasks_;
+                bool fusion_enabled_ = true;
+                std::size_t fused_ = 0;
         };
     } // namespace Graph
 } // namespace SushiRuntime

@@ -125,6 +125,22 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched(sushi_cuda_ctx* ctx, int dev
                                                     float beta, float* c, int64_t ldc, int64_t stride_c,
                                                     int64_t batch);
 
+/* GEMM with a fused epilogue activation (no counterpart call in the reference, which runs
+ * ReLU as a separate element-wise task after the GEMM: tests/runtime/test_framework_sim.cpp:47-58,
+ * src/ops/math/nonlinear/relu.cpp:36-40).  epilogue: SUSHI_EPILOGUE_NONE or SUSHI_EPILOGUE_RELU,
+ * C <- act(alpha * op(A) * op(B) + beta * C).                                                 */
+enum sushi_cuda_epilogue { SUSHI_EPILOGUE_NONE = 0, SUSHI_EPILOGUE_RELU = 1 };
+SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                       int64_t m, int64_t n, int64_t k, float alpha,
+                                                       const float* a, int64_t lda, int64_t stride_a,
+                                                       const float* b, int64_t ldb, int64_t stride_b,
+                                                       float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                       int64_t batch, int epilogue);
+
+/* In-place ReLU on `count` contiguous floats (replaces the element-wise kernel of
+ * src/ops/math/nonlinear/relu.cpp:36-40 for FLOAT32).                                         */
+SUSHI_CUDA_API int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count);
+
 /* Same operation on HOST buffers (the SHARED / HOST strategies of the reference, whose
  * tensors callers fill and read on the host: tests/test_common.hpp:36-58): stages A, B
  * (and C when beta != 0) to the device, runs the GEMM, stages C back; all queued on the

@@ -46,6 +46,9 @@ SIGNATURES = {
                                 _f32, _vp, _i64]),
     "sushi_cuda_sgemm_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                 _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
+    "sushi_cuda_sgemm_strided_batched_ex": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
+                                                   _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
+    "sushi_cuda_relu": (_int, [_vp, _int, _vp, _i64]),
     "sushi_cuda_sgemm_strided_batched_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                      _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
     "sushi_cuda_gemm_workspace_bytes": (_int, [_i64, _i64, _i64, _i64, ctypes.POINTER(_sz)]),
@@ -242,6 +245,15 @@ class SushiCuda:
         self._check(self.lib.sushi_cuda_sgemm_strided_batched(
             self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
             _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch))
+
+    def sgemm_strided_batched_ex(self, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,
+                                 beta, c, ldc, stride_c, batch, epilogue: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_strided_batched_ex(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
+            _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch, epilogue))
+
+    def relu(self, x, count: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_relu(self._ctx, dev, _addr(x), count))
 
     # -- GEMM (host pointers, staged)
     def sgemm_strided_batched_host(self, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,

@@ -24,6 +24,7 @@ struct SimtGemmArgs
     int64_t stride_a, stride_b, stride_c;
     int64_t tiles_m, tiles_n;
     float alpha, beta;
+    int relu;            // epilogue activation: max(alpha*acc + beta*C, 0)
 };
 
 constexpr int SIMT_THREADS = 256;
@@ -158,6 +159,10 @@ sgemm_simt_kernel(const SimtGemmArgs p)
                     o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
                     o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
                 }
+                if (p.relu)
+                {
+                    o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+                }
                 *reinterpret_cast<float4*>(dst) = o;
             }
             else
@@ -169,7 +174,7 @@ sgemm_simt_kernel(const SimtGemmArgs p)
                     {
                         float o = p.alpha * acc[i][g * 4 + j];
                         if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
-                        dst[j] = o;
+                        dst[j] = p.relu ? fmaxf(o, 0.0f) : o;
                     }
                 }
             }
@@ -178,8 +183,9 @@ sgemm_simt_kernel(const SimtGemmArgs p)
 }
 
 // C <- beta * C (k == 0 or alpha == 0): no operand is read.  One thread per element.
+// relu != 0 additionally clamps at zero (beta == 1 with relu is the standalone in-place ReLU).
 __global__ void scale_c_kernel(float* c, int64_t m, int64_t n, int64_t ldc, int64_t stride_c,
-                               int64_t batch, float beta)
+                               int64_t batch, float beta, int relu = 0)
 {
     const int64_t total = m * n * batch;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -189,7 +195,8 @@ __global__ void scale_c_kernel(float* c, int64_t m, int64_t n, int64_t ldc, int6
         const int64_t row = (i / n) % m;
         const int64_t bi = i / (n * m);
         float* dst = c + bi * stride_c + row * ldc + col;
-        *dst = (beta == 0.0f) ? 0.0f : beta * (*dst);
+        float v = (beta == 0.0f) ? 0.0f : beta * (*dst);
+        *dst = relu ? fmaxf(v, 0.0f) : v;
     }
 }
 

@@ -85,6 +85,7 @@ struct Params
     int32_t tiles_m, tiles_n;
     int64_t total_tiles;           // tiles_m * tiles_n * batch
     float alpha, beta;
+    int32_t relu;                  // epilogue activation: max(alpha*acc + beta*C, 0)
     int* status;
     // work distribution
     int64_t dp_tiles;              // tiles [0, dp_tiles) are dealt whole, round-robin over the grid
@@ -627,6 +628,10 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                     o.x = fmaf(p.beta, old[i].x, o.x); o.y = fmaf(p.beta, old[i].y, o.y);
                                     o.z = fmaf(p.beta, old[i].z, o.z); o.w = fmaf(p.beta, old[i].w, o.w);
                                 }
+                                if (p.relu)
+                                {
+                                    o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+                                }
                                 *reinterpret_cast<float4*>(dst) = o;
                             }
                             else
@@ -639,7 +644,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                     {
                                         float o = p.alpha * av[j];
                                         if (has_beta) o = fmaf(p.beta, dst[j], o);
-                                        dst[j] = o;
+                                        dst[j] = p.relu ? fmaxf(o, 0.0f) : o;
                                     }
                                 }
                             }
@@ -833,7 +838,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
                                      float alpha, float beta, int* status, int sm_count, cudaStream_t st,
                                      void* sk_area = nullptr, unsigned int sk_epoch = 0,
-                                     float* const* peer_c = nullptr, int n_peers = 0)
+                                     float* const* peer_c = nullptr, int n_peers = 0, bool relu = false)
 {
     // per-device attribute; cheap enough to set on every launch
     cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -854,7 +859,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.num_kb = (int32_t)num_kb;
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
-    p.alpha = alpha; p.beta = beta; p.status = status;
+    p.alpha = alpha; p.beta = beta; p.status = status; p.relu = relu ? 1 : 0;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
     p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split;
     p.sk_flags = static_cast<unsigned int*>(sk_area);

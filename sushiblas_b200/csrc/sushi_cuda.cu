@@ -208,6 +208,7 @@ struct SlabReuse
     int64_t max_rows = 0;      // largest slab (sizes the A planes once)
     float* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int n_peers = 0;           // fused all-gather: the GEMM epilogue also stores C to these addresses
+    bool relu = false;         // epilogue activation
 };
 
 int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int64_t n, int64_t k, float alpha,
@@ -216,13 +217,14 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
 {
     if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
     SC_CUDA(ctx, cudaSetDevice(d.device));
+    const bool relu = reuse && reuse->relu;
     if (k == 0 || alpha == 0.0f)
     {
-        if (beta == 1.0f) return SUSHI_CUDA_OK;
+        if (beta == 1.0f && !relu) return SUSHI_CUDA_OK;
         const int64_t total = m * n * batch;
         int64_t blocks = (total + 255) / 256;
         if (blocks > (int64_t)d.sm_count * 16) blocks = (int64_t)d.sm_count * 16;
-        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d.stream>>>(c, m, n, ldc, sc, batch, beta);
+        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d.stream>>>(c, m, n, ldc, sc, batch, beta, relu ? 1 : 0);
         ctx->launches++;
         SC_CUDA(ctx, cudaGetLastError());
         return SUSHI_CUDA_OK;
@@ -291,7 +293,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,
                                                    d.status, d.sm_count, d.stream, sk_area, d.sk_epoch,
-                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0));
+                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, relu));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
         ctx->launches += 1 + prepass_launches;
         return SUSHI_CUDA_OK;
@@ -300,7 +302,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     sushi::SimtGemmArgs g;
     g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
     g.stride_a = sa; g.stride_b = sb; g.stride_c = sc; g.tiles_m = 0; g.tiles_n = 0;
-    g.alpha = alpha; g.beta = beta;
+    g.alpha = alpha; g.beta = beta; g.relu = relu ? 1 : 0;
     int rc = timing_mark(ctx, d, 0, 0);
     if (rc == SUSHI_CUDA_OK) rc = timing_mark(ctx, d, 1, 0);
     if (rc != SUSHI_CUDA_OK) return rc;
@@ -633,6 +635,39 @@ extern "C" int sushi_cuda_sgemm_strided_batched(sushi_cuda_ctx* ctx, int dev, in
     if (rc != SUSHI_CUDA_OK) return rc;
     return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc,
                     stride_c, batch);
+}
+
+extern "C" int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                   int64_t m, int64_t n, int64_t k, float alpha,
+                                                   const float* a, int64_t lda, int64_t stride_a,
+                                                   const float* b, int64_t ldb, int64_t stride_b,
+                                                   float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                   int64_t batch, int epilogue)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_ex: bad context or device index");
+    if (epilogue != SUSHI_EPILOGUE_NONE && epilogue != SUSHI_EPILOGUE_RELU)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_ex: unknown epilogue");
+    int rc = validate_gemm(ctx, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, stride_a, stride_b, stride_c, batch);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    SlabReuse opts;
+    opts.relu = (epilogue == SUSHI_EPILOGUE_RELU);
+    return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc,
+                    stride_c, batch, &opts);
+}
+
+extern "C" int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || count < 0 || (count > 0 && !x)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "relu: bad argument");
+    if (count == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    int64_t blocks = (count + 255) / 256;
+    if (blocks > (int64_t)d->sm_count * 32) blocks = (int64_t)d->sm_count * 32;
+    sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(x, 1, count, count, 0, 1, 1.0f, 1);
+    ctx->launches++;
+    SC_CUDA(ctx, cudaGetLastError());
+    return SUSHI_CUDA_OK;
 }
 
 extern "C" int sushi_cuda_sgemm(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,

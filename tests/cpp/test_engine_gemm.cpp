@@ -175,6 +175,68 @@ TEST_CASE(ChainedGemmsKeepOrder)
     verify_tensor(*cur, ref, 1e-4f);
 }
 
+TEST_CASE(ReLUForward)
+{
+    // tests/math/nonlinear/test_relu.cpp:38-47
+    sb::Engine engine(runtime());
+    auto t = engine.create_tensor({4});
+    fill_tensor(t, {-2.0f, -0.5f, 0.0f, 3.5f});
+    engine.nonlinear().relu(t);
+    EXPECT_EQ(engine.get_graph().pending(), size_t(1));        // nothing to fold into: its own task
+    engine.execute().wait();
+    verify_tensor(t, {0.0f, 0.0f, 0.0f, 3.5f});
+}
+
+TEST_CASE(GemmReluChainIsFusedAndEqualsUnfused)
+{
+    // H_{i+1} = relu(H_i * W_i) as in DeepForwardPass (tests/runtime/test_framework_sim.cpp:47-58):
+    // each relu is folded into the GEMM recorded just before it; results equal the unfused run bit for bit
+    const int batch = 96, hidden = 160, layers = 4;
+    auto w = random_vec(size_t(hidden) * hidden, 41);
+    for (auto& v : w) v *= 0.2f;
+    auto x = random_vec(size_t(batch) * hidden, 42);
+    std::vector<float> results[2];
+    for (int fused = 0; fused < 2; ++fused)
+    {
+        sb::Engine engine(runtime());
+        engine.get_graph().set_fusion(fused == 1);
+        auto W = engine.create_tensor({hidden, hidden});
+        auto h0 = engine.create_tensor({batch, hidden}), h1 = engine.create_tensor({batch, hidden});
+        fill_tensor(W, w); fill_tensor(h0, x);
+        sb::Tensor* cur = &h0; sb::Tensor* nxt = &h1;
+        for (int l = 0; l < layers; ++l)
+        {
+            engine.blas().gemm(*cur, W, *nxt);
+            if (l < layers - 1) engine.nonlinear().relu(*nxt);
+            std::swap(cur, nxt);
+        }
+        EXPECT_EQ(engine.get_graph().pending(), size_t(fused ? layers : 2 * layers - 1));
+        EXPECT_EQ(engine.get_graph().fused_count(), size_t(fused ? layers - 1 : 0));
+        engine.execute().wait();
+        results[fused].assign(cur->data_as<float>(), cur->data_as<float>() + cur->num_elements);
+    }
+    EXPECT_TRUE(results[0] == results[1]);
+    // and against the host reference
+    std::vector<float> ref = x;
+    for (int l = 0; l < layers; ++l)
+    {
+        ref = host_gemm(false, false, batch, hidden, hidden, 1.0f, ref, w, 0.0f, ref);
+        if (l < layers - 1) for (auto& v : ref) v = v > 0 ? v : 0;
+    }
+    for (size_t i = 0; i < ref.size(); ++i) EXPECT_NEAR(results[1][i], ref[i], 2e-4);
+    // a relu on a different tensor, or on a slice of the output, is not folded
+    sb::Engine engine(runtime());
+    auto A = engine.create_tensor({8, 8}), B = engine.create_tensor({8, 8}), C = engine.create_tensor({8, 8});
+    fill_tensor(A, std::vector<float>(64, 1.0f)); fill_tensor(B, std::vector<float>(64, -1.0f));
+    engine.blas().gemm(A, B, C);
+    auto top = C.slice(0, 0, 4);
+    engine.nonlinear().relu(top);
+    EXPECT_EQ(engine.get_graph().pending(), size_t(2));
+    engine.execute().wait();
+    EXPECT_EQ(C.data_as<float>()[0], 0.0f);          // top half clamped
+    EXPECT_EQ(C.data_as<float>()[63], -8.0f);        // bottom half untouched
+}
+
 TEST_CASE(FrameworkSimShapesAndStress)
 {
     // DeepForwardPass: 10 x (512x1024 * 1024x1024); ParallelBatchedInference: 24 x (256x256 * 256x512);
@@ -190,7 +252,12 @@ TEST_CASE(FrameworkSimShapesAndStress)
         for (auto& w : wts) w.from_host(ones.data());
         act[0].from_host(ones.data());
         auto t0 = std::chrono::steady_clock::now();
-        for (int l = 0; l < 10; ++l) engine.blas().gemm(act[l], wts[l], act[l + 1]);
+        for (int l = 0; l < 10; ++l)
+        {
+            engine.blas().gemm(act[l], wts[l], act[l + 1]);
+            if (l < 9) engine.nonlinear().relu(act[l + 1]);
+        }
+        EXPECT_EQ(engine.get_graph().pending(), size_t(10));          // the nine ReLUs were folded
         engine.execute().wait();
         double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         std::printf("       DeepForwardPass 10 x (512x1024x1024): %.3f ms\n", ms);

@@ -36,6 +36,21 @@ def main():
     ctx.comm_init_rank(ids[0], world, rank)
     failures = []
 
+    import zlib
+    import numpy as np
+
+    def compare(got, want, k, alpha, beta, label):
+        """got / want: numpy arrays.  (1) every rank holds identical bits (the exchange is exact);
+        (2) agreement with one GPU computing everything, up to fp32 summation order (a block with
+        fewer tiles than SMs is cut along K, the full problem may be cut differently)."""
+        sums = [None] * world
+        dist.all_gather_object(sums, zlib.crc32(np.ascontiguousarray(got).tobytes()))
+        if len(set(sums)) != 1:
+            failures.append(f"{label}: ranks hold different results ({sums})")
+        err = float(np.abs(got.astype(np.float64) - want).max())
+        if not err <= 64 * 2.0 ** -24 * (abs(alpha) * k * 0.5 + abs(beta)):
+            failures.append(f"{label}: max |diff| {err} vs single GPU on rank {rank}")
+
     def full(seed, rows, cols):
         t = torch.empty(rows, cols, device=dev)
         ctx.fill_uniform(t, t.numel(), seed)
@@ -58,12 +73,9 @@ def main():
         ctx.sgemm(ta, 0, m, n, k, alpha, a, m if ta else k, b, n, beta, c_one, n)
         ctx.sync()
         torch.cuda.synchronize()
-        if not torch.equal(c_shard, c_one):
-            bad = int((c_shard != c_one).sum())
-            failures.append(f"row_sharded m={m} n={n} k={k} ta={ta}: {bad} elements differ on rank {rank}")
+        compare(c_shard.cpu().numpy(), c_one.cpu().numpy(), k, alpha, beta, f"row_sharded m={m} n={n} k={k} ta={ta}")
 
     # ---- fused GEMM + all-gather: the epilogue stores finished tiles into the peers' buffers
-    import numpy as np
     for (m, n, k, alpha, beta) in [(4096, 1024, 512, 1.0, 0.0), (2048 * world, 768, 640, 1.5, 0.5), (1000, 512, 256, 1.0, 0.0)]:
         nbytes = m * n * 4
         c_mine = ctx.malloc(nbytes)                      # base of a cudaMalloc block: exportable
@@ -87,17 +99,7 @@ def main():
         ctx.sync()
         torch.cuda.synchronize()
         want = c_one.cpu().numpy()
-        # (1) the exchange itself is exact: every rank ends up with the same bits everywhere
-        import zlib
-        sums = [None] * world
-        dist.all_gather_object(sums, zlib.crc32(got.tobytes()))
-        if len(set(sums)) != 1:
-            failures.append(f"fused gather m={m} n={n} k={k}: ranks hold different C ({sums})")
-        # (2) against one GPU computing everything: equal up to the fp32 summation order (a block
-        # with fewer tiles than SMs is cut along K, the full problem may not be)
-        err = float(np.abs(got.astype(np.float64) - want).max())
-        if not err <= 64 * 2.0 ** -24 * (abs(alpha) * k * 0.5 + abs(beta)):
-            failures.append(f"fused gather m={m} n={n} k={k}: max |diff| {err} vs single GPU on rank {rank}")
+        compare(got, want, k, alpha, beta, f"fused gather m={m} n={n} k={k}")
         dist.barrier()
         ctx.comm_set_peer_buffers([], 0)
         for r in range(world):
@@ -120,8 +122,7 @@ def main():
         ctx.sgemm_strided_batched(0, 0, m, n, k, 1.0, a, k, m * k, b, n, k * n, 0.0, c_one, n, m * n, batch)
         ctx.sync()
         torch.cuda.synchronize()
-        if not torch.equal(c_shard, c_one):
-            failures.append(f"batch_sharded batch={batch} m={m}: mismatch on rank {rank}")
+        compare(c_shard.cpu().numpy(), c_one.cpu().numpy(), k, 1.0, 0.0, f"batch_sharded batch={batch} m={m}")
 
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)

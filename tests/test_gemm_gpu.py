@@ -335,6 +335,41 @@ def test_config4_tall_skinny(ctx):
     assert bool(torch.isfinite(c).all())
 
 
+# ------------------------------------------------------------------ fused activation epilogue
+@pytest.mark.parametrize("variant", [SIMT, TC3X])
+def test_relu_epilogue_and_standalone_relu(ctx, variant):
+    """C <- relu(alpha*op(A)*op(B) + beta*C) in the GEMM epilogue equals GEMM followed by the
+    standalone in-place ReLU bit for bit, and lies within the GEMM tolerance of relu(oracle)
+    (|relu(x) - relu(y)| <= |x - y|)."""
+    for (ta, tb, m, n, k, alpha, beta, batch) in [(0, 0, 300, 260, 100, 1.0, 0.0, 1), (1, 0, 512, 256, 384, 1.5, 0.5, 2),
+                                                   (0, 1, 129, 65, 33, -1.0, 1.0, 1)]:
+        cs = make_case(321, ta, tb, m, n, k, batch)
+        ctx.set_gemm_variant(variant)
+        da, db = dev(cs["a"]), dev(cs["b"])
+        c_fused, c_two = dev(cs["c"].copy()), dev(cs["c"].copy())
+        ctx.sgemm_strided_batched_ex(ta, tb, m, n, k, alpha, da, cs["lda"], cs["sa"], db, cs["ldb"], cs["sb"], beta,
+                                     c_fused, cs["ldc"], cs["sc"], batch, 1)
+        ctx.sgemm_strided_batched_ex(ta, tb, m, n, k, alpha, da, cs["lda"], cs["sa"], db, cs["ldb"], cs["sb"], beta,
+                                     c_two, cs["ldc"], cs["sc"], batch, 0)
+        ctx.relu(c_two, c_two.numel())
+        ctx.sync()
+        ctx.set_gemm_variant(AUTO)
+        assert torch.equal(c_fused, c_two)
+        ref, absab = og.gemm_f64_np(ta, tb, m, n, k, alpha, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"],
+                                    beta, cs["c"], cs["ldc"], cs["sc"], batch)
+        got = c_fused.cpu().numpy().reshape(batch, m, n)
+        assert got.min() >= 0.0
+        r, _ = og.tolerance_ratio(got, np.maximum(ref, 0.0), absab, k, beta=beta, c_in=cs["c"].reshape(batch, m, n),
+                                  budget=BUDGET)
+        assert r <= 1.0, r
+    x = torch.tensor([-2.0, -0.5, 0.0, 3.5, float("nan")], device="cuda")     # reference's ReLU vector + NaN -> 0
+    ctx.relu(x, 5); ctx.sync()
+    assert x.tolist() == [0.0, 0.0, 0.0, 3.5, 0.0]
+    from sushiblas_b200 import SushiCudaError
+    with pytest.raises(SushiCudaError):
+        ctx.sgemm_strided_batched_ex(0, 0, 4, 4, 4, 1.0, x, 4, 0, x, 4, 0, 0.0, x, 4, 0, 1, 7)   # unknown epilogue
+
+
 # ------------------------------------------------------------------ host-buffer entry point and storage calls
 def test_host_entry_point_matches_device_path(ctx):
     m, n, k, batch = 300, 200, 150, 2

@@ -1,5 +1,6 @@
 """Sharded entry points on real GPUs (needs at least 2; skipped otherwise): one process per
-GPU, NCCL exchange, result must equal the single-GPU result bit for bit."""
+GPU, NCCL and fused peer-store exchange; every rank must hold identical bits, equal to the
+single-GPU result up to fp32 summation order."""
 import os
 import subprocess
 import sys
