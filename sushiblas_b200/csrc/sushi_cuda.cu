@@ -36,6 +36,9 @@ struct DeviceState
     size_t stage_bytes[3] = {0, 0, 0};
     int* status = nullptr;                // device word written by bounded in-kernel waits
     int* status_host = nullptr;           // pinned mirror
+    // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t pipe_events[10] = {};
     void* sk_area = nullptr;              // split-K exchange area (epoch flags + slots), flags zeroed at allocation
     size_t sk_area_bytes = 0;
     unsigned int sk_epoch = 0;            // last epoch handed to a launch
@@ -459,6 +462,9 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         if (d.status) cudaFree(d.status);
         if (d.status_host) cudaFreeHost(d.status_host);
         for (cudaEvent_t e : d.timing_events) cudaEventDestroy(e);
+        if (d.copy_in) { cudaStreamSynchronize(d.copy_in); cudaStreamDestroy(d.copy_in); }
+        if (d.copy_out) { cudaStreamSynchronize(d.copy_out); cudaStreamDestroy(d.copy_out); }
+        for (cudaEvent_t e : d.pipe_events) if (e) cudaEventDestroy(e);
         if (d.own_stream) cudaStreamDestroy(d.own_stream);
     }
     delete ctx;
@@ -701,15 +707,107 @@ extern "C" int sushi_cuda_sgemm_strided_batched_host(sushi_cuda_ctx* ctx, int de
     float* da = static_cast<float*>(d->stage[0]);
     float* db = static_cast<float*>(d->stage[1]);
     float* dc = static_cast<float*>(d->stage[2]);
-    if (ea) SC_CUDA(ctx, cudaMemcpyAsync(da, a, ea, cudaMemcpyHostToDevice, d->stream));
-    if (eb) SC_CUDA(ctx, cudaMemcpyAsync(db, b, eb, cudaMemcpyHostToDevice, d->stream));
     // C goes up when it is read (beta != 0) or when its buffer has gaps the copy back must preserve
     const bool dense_c = (ldc == n) && (batch == 1 || stride_c == m * n);
-    if (beta != 0.0f || !dense_c) SC_CUDA(ctx, cudaMemcpyAsync(dc, c, ec, cudaMemcpyHostToDevice, d->stream));
-    rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, da, lda, stride_a, db, ldb, stride_b, beta, dc, ldc,
-                  stride_c, batch);
-    if (rc != SUSHI_CUDA_OK) return rc;
-    SC_CUDA(ctx, cudaMemcpyAsync(c, dc, ec, cudaMemcpyDeviceToHost, d->stream));
+    const bool upload_c = beta != 0.0f || !dense_c;
+
+    // Large problems are cut into chunks -- row blocks of A and C, or batch entries -- so that the
+    // upload of chunk i+1, the multiplication of chunk i and the download of chunk i-1 overlap
+    // (PCIe is full duplex and the copies dwarf the arithmetic).  B goes up once and is split
+    // into planes once.  Row blocks of a transposed A are column blocks of the stored k x m matrix
+    // and go up as strided 2-D copies.  Small problems take the plain sequence.
+    const size_t total_bytes = ea + eb + ec;
+    int chunks = 1;
+    if (total_bytes >= ((size_t)32 << 20))
+    {
+        if (batch >= 4) chunks = 4;
+        else if (batch == 1 && m >= 2048) chunks = 4;
+    }
+    if (chunks == 1)
+    {
+        if (ea) SC_CUDA(ctx, cudaMemcpyAsync(da, a, ea, cudaMemcpyHostToDevice, d->stream));
+        if (eb) SC_CUDA(ctx, cudaMemcpyAsync(db, b, eb, cudaMemcpyHostToDevice, d->stream));
+        if (upload_c) SC_CUDA(ctx, cudaMemcpyAsync(dc, c, ec, cudaMemcpyHostToDevice, d->stream));
+        rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, da, lda, stride_a, db, ldb, stride_b, beta, dc, ldc,
+                      stride_c, batch);
+        if (rc != SUSHI_CUDA_OK) return rc;
+        SC_CUDA(ctx, cudaMemcpyAsync(c, dc, ec, cudaMemcpyDeviceToHost, d->stream));
+        return SUSHI_CUDA_OK;
+    }
+
+    if (!d->copy_in)
+    {
+        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->copy_in, cudaStreamNonBlocking));
+        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->copy_out, cudaStreamNonBlocking));
+        for (cudaEvent_t& e : d->pipe_events) SC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    cudaEvent_t* ev = d->pipe_events;          // [0] start, [1..4] chunk uploaded, [5..8] chunk multiplied, [9] all downloaded
+    SC_CUDA(ctx, cudaEventRecord(ev[0], d->stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_in, ev[0], 0));      // after everything queued before this call
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[0], 0));
+    SlabReuse reuse;
+    const bool by_batch = batch > 1;
+    const int64_t units = by_batch ? batch : m;
+    int64_t per = (units + chunks - 1) / chunks;
+    if (!by_batch) per = (per + 255) / 256 * 256;                 // whole tiles per chunk
+    if (by_batch)
+    {
+        // batch entries do not share B: upload and split per chunk
+        for (int i = 0; i < chunks; ++i)
+        {
+            const int64_t u0 = i * per, u1 = (u0 + per < units) ? u0 + per : units;
+            if (u1 <= u0) { SC_CUDA(ctx, cudaEventRecord(ev[1 + i], d->copy_in)); SC_CUDA(ctx, cudaEventRecord(ev[5 + i], d->stream)); continue; }
+            const int64_t nb = u1 - u0;
+            const size_t ca = (size_t)extent(trans_a ? k : m, trans_a ? m : k, lda, stride_a, nb) * sizeof(float);
+            const size_t cb = (size_t)extent(trans_b ? n : k, trans_b ? k : n, ldb, stride_b, nb) * sizeof(float);
+            const size_t cc = (size_t)extent(m, n, ldc, stride_c, nb) * sizeof(float);
+            SC_CUDA(ctx, cudaMemcpyAsync(da + u0 * stride_a, a + u0 * stride_a, ca, cudaMemcpyHostToDevice, d->copy_in));
+            SC_CUDA(ctx, cudaMemcpyAsync(db + u0 * stride_b, b + u0 * stride_b, cb, cudaMemcpyHostToDevice, d->copy_in));
+            if (upload_c) SC_CUDA(ctx, cudaMemcpyAsync(dc + u0 * stride_c, c + u0 * stride_c, cc, cudaMemcpyHostToDevice, d->copy_in));
+            SC_CUDA(ctx, cudaEventRecord(ev[1 + i], d->copy_in));
+            SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[1 + i], 0));
+            rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, da + u0 * stride_a, lda, stride_a, db + u0 * stride_b,
+                          ldb, stride_b, beta, dc + u0 * stride_c, ldc, stride_c, nb);
+            if (rc != SUSHI_CUDA_OK) return rc;
+            SC_CUDA(ctx, cudaEventRecord(ev[5 + i], d->stream));
+            SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[5 + i], 0));
+            SC_CUDA(ctx, cudaMemcpyAsync(c + u0 * stride_c, dc + u0 * stride_c, cc, cudaMemcpyDeviceToHost, d->copy_out));
+        }
+    }
+    else
+    {
+        if (eb) SC_CUDA(ctx, cudaMemcpyAsync(db, b, eb, cudaMemcpyHostToDevice, d->copy_in));
+        reuse.max_rows = per < m ? per : m;
+        for (int i = 0; i < chunks; ++i)
+        {
+            const int64_t r0 = i * per, r1 = (r0 + per < m) ? r0 + per : m;
+            if (r1 <= r0) continue;
+            const int64_t rows = r1 - r0;
+            const size_t ca = (size_t)extent(rows, k, lda, 0, 1) * sizeof(float);
+            const size_t cc = (size_t)extent(rows, n, ldc, 0, 1) * sizeof(float);
+            const float* a_chunk = trans_a ? da + r0 : da + r0 * lda;
+            if (k > 0)
+            {
+                if (trans_a)
+                    SC_CUDA(ctx, cudaMemcpy2DAsync(da + r0, (size_t)lda * sizeof(float), a + r0, (size_t)lda * sizeof(float),
+                                                   (size_t)rows * sizeof(float), (size_t)k, cudaMemcpyHostToDevice, d->copy_in));
+                else
+                    SC_CUDA(ctx, cudaMemcpyAsync(da + r0 * lda, a + r0 * lda, ca, cudaMemcpyHostToDevice, d->copy_in));
+            }
+            if (upload_c) SC_CUDA(ctx, cudaMemcpyAsync(dc + r0 * ldc, c + r0 * ldc, cc, cudaMemcpyHostToDevice, d->copy_in));
+            SC_CUDA(ctx, cudaEventRecord(ev[1 + i], d->copy_in));
+            SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[1 + i], 0));
+            rc = run_gemm(ctx, *d, trans_a, trans_b, rows, n, k, alpha, a_chunk, lda, 0, db, ldb, 0, beta,
+                          dc + r0 * ldc, ldc, 0, 1, &reuse);
+            if (rc != SUSHI_CUDA_OK) return rc;
+            SC_CUDA(ctx, cudaEventRecord(ev[5 + i], d->stream));
+            SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[5 + i], 0));
+            SC_CUDA(ctx, cudaMemcpyAsync(c + r0 * ldc, dc + r0 * ldc, cc, cudaMemcpyDeviceToHost, d->copy_out));
+        }
+    }
+    // the call completes on the caller's stream once the last download has
+    SC_CUDA(ctx, cudaEventRecord(ev[9], d->copy_out));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[9], 0));
     return SUSHI_CUDA_OK;
 }
 

@@ -390,6 +390,43 @@ def test_host_entry_point_matches_device_path(ctx):
     assert np.array_equal(v[:, :, n:], og._view(cs["c"], m, cs["ldc"], cs["ldc"], cs["sc"], batch)[:, :, n:])
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (0, 1), (1, 1)])
+def test_host_entry_point_chunked_pipeline(ctx, ta, tb):
+    """Above 32 MiB the host-buffer call uploads, multiplies and downloads in four chunks on
+    separate copy streams; the result must equal the device path on the same data."""
+    m, n, k = 2304, 2048, 1800                       # 2304 rows: chunks of 768 (last one shorter after rounding)
+    cs = make_case(77, ta, tb, m, n, k)
+    ctx.set_gemm_variant(TC3X)
+    for beta in (0.5, 0.0):
+        c_host = cs["c"].copy()
+        ctx.sgemm_strided_batched_host(ta, tb, m, n, k, 1.5, cs["a"], cs["lda"], 0, cs["b"], cs["ldb"], 0, beta, c_host,
+                                       cs["ldc"], 0, 1)
+        # a second call right behind the first reuses the staging buffers
+        c_host2 = cs["c"].copy()
+        ctx.sgemm_strided_batched_host(ta, tb, m, n, k, 1.5, cs["a"], cs["lda"], 0, cs["b"], cs["ldb"], 0, beta, c_host2,
+                                       cs["ldc"], 0, 1)
+        ctx.sync()
+        ref, absab = og.gemm_f64_np(ta, tb, m, n, k, 1.5, cs["a"], cs["lda"], 0, cs["b"], cs["ldb"], 0, beta, cs["c"],
+                                    cs["ldc"], 0, 1)
+        r, _ = og.tolerance_ratio(c_host.reshape(1, m, n), ref, absab, k, beta=beta, c_in=cs["c"].reshape(1, m, n),
+                                  budget=BUDGET)
+        assert r <= 1.0, (ta, tb, beta, r)
+        assert np.array_equal(c_host, c_host2)
+    ctx.set_gemm_variant(AUTO)
+    # batched: chunks of batch entries
+    batch, m, n, k = 10, 512, 384, 640
+    cs = make_case(78, ta, tb, m, n, k, batch)
+    c_host = cs["c"].copy()
+    ctx.sgemm_strided_batched_host(ta, tb, m, n, k, 1.0, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"], 1.0,
+                                   c_host, cs["ldc"], cs["sc"], batch)
+    ctx.sync()
+    ref, absab = og.gemm_f64_np(ta, tb, m, n, k, 1.0, cs["a"], cs["lda"], cs["sa"], cs["b"], cs["ldb"], cs["sb"], 1.0,
+                                cs["c"], cs["ldc"], cs["sc"], batch)
+    r, _ = og.tolerance_ratio(c_host.reshape(batch, m, n), ref, absab, k, beta=1.0, c_in=cs["c"].reshape(batch, m, n),
+                              budget=BUDGET)
+    assert r <= 1.0, (ta, tb, r)
+
+
 def test_storage_calls_round_trip(ctx):
     nbytes = 1 << 20
     d = ctx.malloc(nbytes)
