@@ -34,8 +34,9 @@ UNIT = "TFLOP/s"
 SEED = 20240601
 
 # DRAM bytes per launch of the dominant kernel from the committed ncu capture
-# (profiles/sgemm_tc3x_4096_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum); None where no capture exists.
-NCU_TRAFFIC_BYTES = {"sgemm_4096_nn_nt_tn_tt": 592.1e6}
+# (profiles/sgemm_tc3x_4096_ncu.md, profiles/sgemm_tc3x_65536x256x4096_ncu.md: dram__bytes_read.sum +
+# dram__bytes_write.sum); None where no capture exists.
+NCU_TRAFFIC_BYTES = {"sgemm_4096_nn_nt_tn_tt": 588.9e6, "sgemm_65536x256x4096_nn_row_sharded": 1136.1e6}
 
 
 def log(*a):

@@ -131,36 +131,63 @@ namespace SushiBLAS
         if (dense_out) { producer.out_ptr = C.data(); producer.out_count = g.m * g.n * g.batch; }
         auto slot = producer.slot;
 
-        engine_.get_graph().add_task(meta, reads, writes,
-            [g, oa, ob, oc, slot](SushiRuntime::Execution::RuntimeContext& rt) -> int
+        // stage inputs and describe the call with device addresses
+        auto prepare = [g, oa, ob, oc, slot](SushiRuntime::Execution::RuntimeContext& rt, sushi_cuda_gemm_desc& q) -> int
+        {
+            sushi_cuda_ctx* ctx = rt.native_handle();
+            // device address of an operand; host-resident operands are staged through their mirror
+            auto on_device = [ctx](const Operand& o, bool upload, float** out) -> int
             {
-                sushi_cuda_ctx* ctx = rt.native_handle();
-                // device address of an operand; host-resident operands are staged through their mirror
-                auto on_device = [ctx](const Operand& o, bool upload, float** out) -> int
-                {
-                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
-                    if (!base) return SUSHI_CUDA_ERR_OOM;
-                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) -
-                                                            static_cast<char*>(o.storage->data_ptr)));
-                    if (o.host && upload && o.extent > 0)
-                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
-                    return SUSHI_CUDA_OK;
-                };
-                float *da = nullptr, *db = nullptr, *dc = nullptr;
-                int rc = on_device(oa, true, &da);
-                if (rc == SUSHI_CUDA_OK) rc = on_device(ob, true, &db);
-                // C goes up when it is read (beta != 0) or when the call leaves gaps in it
-                const bool dense_c = (g.ldc == g.n) && (g.batch == 1 || g.stride_c == g.m * g.n);
-                if (rc == SUSHI_CUDA_OK) rc = on_device(oc, g.beta != 0.0f || !dense_c, &dc);
-                if (rc != SUSHI_CUDA_OK) return rc;
-                SB_LOG_INFO("CUDA GEMM [Row-Major]: {}x[{}x{}x{}]", g.batch, g.m, g.n, g.k);
-                rc = sushi_cuda_sgemm_strided_batched_ex(ctx, 0, g.trans_a, g.trans_b, g.m, g.n, g.k, g.alpha, da, g.lda,
-                                                         g.stride_a, db, g.ldb, g.stride_b, g.beta, dc, g.ldc, g.stride_c,
-                                                         g.batch, slot->activation);
-                if (rc == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
-                    rc = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
-                return rc;
-            }, producer);
+                char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
+                if (!base) return SUSHI_CUDA_ERR_OOM;
+                *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) -
+                                                        static_cast<char*>(o.storage->data_ptr)));
+                if (o.host && upload && o.extent > 0)
+                    return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
+                return SUSHI_CUDA_OK;
+            };
+            float *da = nullptr, *db = nullptr, *dc = nullptr;
+            int rc = on_device(oa, true, &da);
+            if (rc == SUSHI_CUDA_OK) rc = on_device(ob, true, &db);
+            // C goes up when it is read (beta != 0) or when the call leaves gaps in it
+            const bool dense_c = (g.ldc == g.n) && (g.batch == 1 || g.stride_c == g.m * g.n);
+            if (rc == SUSHI_CUDA_OK) rc = on_device(oc, g.beta != 0.0f || !dense_c, &dc);
+            if (rc != SUSHI_CUDA_OK) return rc;
+            q.trans_a = g.trans_a; q.trans_b = g.trans_b; q.m = g.m; q.n = g.n; q.k = g.k; q.alpha = g.alpha;
+            q.a = da; q.lda = g.lda; q.stride_a = g.stride_a;
+            q.b = db; q.ldb = g.ldb; q.stride_b = g.stride_b;
+            q.beta = g.beta; q.c = dc; q.ldc = g.ldc; q.stride_c = g.stride_c; q.batch = g.batch;
+            q.epilogue = slot->activation;
+            return SUSHI_CUDA_OK;
+        };
+        // stage the output back (host-resident C only); `dc` is recomputed, nothing is shared with prepare
+        auto finish = [oc](SushiRuntime::Execution::RuntimeContext& rt) -> int
+        {
+            if (!oc.host || oc.extent <= 0) return SUSHI_CUDA_OK;
+            char* base = static_cast<char*>(oc.storage->allocator->device_view(oc.storage->data_ptr));
+            if (!base) return SUSHI_CUDA_ERR_OOM;
+            float* dc = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(oc.ptr) - static_cast<char*>(oc.storage->data_ptr)));
+            return sushi_cuda_memcpy_d2h(rt.native_handle(), 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
+        };
+        auto work = [g, prepare, finish](SushiRuntime::Execution::RuntimeContext& rt) -> int
+        {
+            sushi_cuda_gemm_desc q{};
+            int rc = prepare(rt, q);
+            if (rc != SUSHI_CUDA_OK) return rc;
+            SB_LOG_INFO("CUDA GEMM [Row-Major]: {}x[{}x{}x{}]", g.batch, g.m, g.n, g.k);
+            rc = sushi_cuda_sgemm_strided_batched_ex(rt.native_handle(), 0, q.trans_a, q.trans_b, q.m, q.n, q.k, q.alpha,
+                                                     q.a, q.lda, q.stride_a, q.b, q.ldb, q.stride_b, q.beta, q.c, q.ldc,
+                                                     q.stride_c, q.batch, q.epilogue);
+            return rc == SUSHI_CUDA_OK ? finish(rt) : rc;
+        };
+        // small problems may be batched with their neighbours into one grouped launch at execute()
+        SushiRuntime::Graph::GroupableGemm groupable;
+        if (g.m <= 128 && g.n <= 128 && g.k <= 1024 && g.batch <= 8)
+        {
+            groupable.prepare = prepare;
+            groupable.finish = finish;
+        }
+        engine_.get_graph().add_task(meta, reads, writes, work, producer, groupable);
         return SushiRuntime::Execution::Event();
     }
 

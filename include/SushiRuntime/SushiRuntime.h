@@ -29,6 +29,7 @@
 #include <string>
 #include <type_traits>
 #include <unordered_map>
+#include <unordered_set>
 #include <utility>
 #include <vector>
 
@@ -378,6 +379,16 @@ namespace SushiRuntime
             std::shared_ptr<EpilogueSlot> slot;
         };
 
+        /// A task that is one GEMM and may be batched with its neighbours into a grouped launch:
+        /// prepare() stages inputs and fills the descriptor with device addresses, finish() stages
+        /// the output back.  Tasks without these run through their HostWork closure alone.
+        struct GroupableGemm
+        {
+            std::function<int(Execution::RuntimeContext&, sushi_cuda_gemm_desc&)> prepare;
+            std::function<int(Execution::RuntimeContext&)> finish;
+            explicit operator bool() const { return static_cast<bool>(prepare); }
+        };
+
         /// Deferred task list.  add_task() records; execute() replays in order on the stream.
         class TaskGraph
         {
@@ -387,9 +398,11 @@ namespace SushiRuntime
                 TaskGraph& operator=(const TaskGraph&) = delete;
 
                 void add_task(const TaskMetadata& meta, const std::vector<void*>& read_access,
-                              const std::vector<void*>& write_access, HostWork work, FusionInfo producer = {})
+                              const std::vector<void*>& write_access, HostWork work, FusionInfo producer = {},
+                              GroupableGemm groupable = {})
                 {
-                    tasks_.push_back(Task{meta, read_access, write_access, std::move(work), std::move(producer)});
+                    tasks_.push_back(Task{meta, read_access, write_access, std::move(work), std::move(producer),
+                                          std::move(groupable)});
                 }
 
                 /// Folds an in-place activation over `count` elements at `ptr` into the task recorded
@@ -417,19 +430,57 @@ namespace SushiRuntime
                 const std::vector<void*>& writes(std::size_t i) const { return tasks_.at(i).writes; }
 
                 /// Enqueues every pending task; the returned Event completes when the stream drains.
+                /// Runs of consecutive small GEMM tasks that do not depend on one another (judged, as
+                /// the reference's dependency tracker does, by the base pointers they read and write)
+                /// go out as one grouped launch; everything else runs in submission order.
                 Execution::Event execute()
                 {
                     std::vector<Task> run;
                     run.swap(tasks_);
-                    for (Task& t : run)
+                    std::size_t i = 0;
+                    while (i < run.size())
                     {
-                        const int rc = t.work(ctx_);
-                        if (rc != SUSHI_CUDA_OK)
-                            throw std::runtime_error(std::string(t.meta.name) + ": " +
-                                                     sushi_cuda_last_error(ctx_.native_handle()));
+                        std::size_t j = i;
+                        if (grouping_enabled_ && run[i].groupable)
+                        {
+                            std::unordered_set<void*> reads, writes;
+                            auto touches = [](const std::unordered_set<void*>& set, const std::vector<void*>& ptrs) {
+                                for (void* p : ptrs)
+                                    if (set.count(p)) return true;
+                                return false;
+                            };
+                            // grow the run while the next task neither reads nor writes an earlier output
+                            // and does not write an earlier input
+                            while (j < run.size() && run[j].groupable && !touches(writes, run[j].reads) &&
+                                   !touches(writes, run[j].writes) && !touches(reads, run[j].writes))
+                            {
+                                writes.insert(run[j].writes.begin(), run[j].writes.end());
+                                reads.insert(run[j].reads.begin(), run[j].reads.end());
+                                ++j;
+                            }
+                        }
+                        if (j - i >= 2)
+                        {
+                            std::vector<sushi_cuda_gemm_desc> descs(j - i);
+                            for (std::size_t t = i; t < j; ++t) check(run[t], run[t].groupable.prepare(ctx_, descs[t - i]));
+                            check(run[i], sushi_cuda_sgemm_grouped(ctx_.native_handle(), 0, descs.data(),
+                                                                   static_cast<std::int64_t>(descs.size())));
+                            for (std::size_t t = i; t < j; ++t) check(run[t], run[t].groupable.finish(ctx_));
+                            grouped_ += j - i;
+                            i = j;
+                        }
+                        else
+                        {
+                            check(run[i], run[i].work(ctx_));
+                            ++i;
+                        }
                     }
                     return Execution::Event(&ctx_);
                 }
+
+                /// Grouped-launch switch (on by default) and the number of tasks sent in groups so far.
+                void set_grouping(bool on) { grouping_enabled_ = on; }
+                std::size_t grouped_count() const { return grouped_; }
 
             private:
                 struct Task
@@ -438,11 +489,17 @@ namespace SushiRuntime
                     std::vector<void*> reads, writes;
                     HostWork work;
                     FusionInfo producer;
+                    GroupableGemm groupable;
                 };
+                void check(const Task& t, int rc) const
+                {
+                    if (rc != SUSHI_CUDA_OK)
+                        throw std::runtime_error(std::string(t.meta.name) + ": " + sushi_cuda_last_error(ctx_.native_handle()));
+                }
                 Execution::RuntimeContext& ctx_;
                 std::vector<Task> tasks_;
-                bool fusion_enabled_ = true;
-                std::size_t fused_ = 0;
+                bool fusion_enabled_ = true, grouping_enabled_ = true;
+                std::size_t fused_ = 0, grouped_ = 0;
         };
     } // namespace Graph
 } // namespace SushiRuntime

@@ -137,6 +137,26 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int 
                                                        float beta, float* c, int64_t ldc, int64_t stride_c,
                                                        int64_t batch, int epilogue);
 
+/* Many independent GEMMs in one call (no counterpart call in the reference; it is what its
+ * scheduler stress tests submit per execute(): 5000 GEMMs of 32^3 and 3000 of 8^3,
+ * tests/runtime/test_dependency_stress.cpp:17-45,67-83).  No output of one problem may overlap
+ * an input or output of another.  Small problems run as ONE grouped kernel launch (64 x 64 FFMA
+ * tiles); problems large enough for the tensor-core path run one by one after it.             */
+typedef struct sushi_cuda_gemm_desc
+{
+    int32_t trans_a, trans_b;
+    int64_t m, n, k;
+    float alpha;
+    const float* a; int64_t lda, stride_a;
+    const float* b; int64_t ldb, stride_b;
+    float beta;
+    float* c; int64_t ldc, stride_c;
+    int64_t batch;
+    int32_t epilogue;          /* sushi_cuda_epilogue */
+} sushi_cuda_gemm_desc;
+SUSHI_CUDA_API int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sushi_cuda_gemm_desc* problems,
+                                            int64_t count);
+
 /* In-place ReLU on `count` contiguous floats (replaces the element-wise kernel of
  * src/ops/math/nonlinear/relu.cpp:36-40 for FLOAT32).                                         */
 SUSHI_CUDA_API int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count);

@@ -20,6 +20,16 @@ _sz = ctypes.c_size_t
 
 GEMM_AUTO, GEMM_SIMT, GEMM_TC3X = 0, 1, 2
 
+class GemmDesc(ctypes.Structure):
+    """sushi_cuda_gemm_desc"""
+    _fields_ = [("trans_a", ctypes.c_int32), ("trans_b", ctypes.c_int32),
+                ("m", _i64), ("n", _i64), ("k", _i64), ("alpha", _f32),
+                ("a", _vp), ("lda", _i64), ("stride_a", _i64),
+                ("b", _vp), ("ldb", _i64), ("stride_b", _i64),
+                ("beta", _f32), ("c", _vp), ("ldc", _i64), ("stride_c", _i64),
+                ("batch", _i64), ("epilogue", ctypes.c_int32)]
+
+
 # name -> (restype, argtypes); mirrors include/sushiblas_cuda.h one to one
 SIGNATURES = {
     "sushi_cuda_device_count": (_int, [ctypes.POINTER(_int)]),
@@ -49,6 +59,7 @@ SIGNATURES = {
     "sushi_cuda_sgemm_strided_batched_ex": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                    _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
     "sushi_cuda_relu": (_int, [_vp, _int, _vp, _i64]),
+    "sushi_cuda_sgemm_grouped": (_int, [_vp, _int, ctypes.POINTER(GemmDesc), _i64]),
     "sushi_cuda_sgemm_strided_batched_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                      _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
     "sushi_cuda_gemm_workspace_bytes": (_int, [_i64, _i64, _i64, _i64, ctypes.POINTER(_sz)]),
@@ -251,6 +262,20 @@ class SushiCuda:
         self._check(self.lib.sushi_cuda_sgemm_strided_batched_ex(
             self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
             _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch, epilogue))
+
+    def sgemm_grouped(self, problems, dev: int = 0):
+        """problems: iterable of dicts with the fields of sushi_cuda_gemm_desc (pointers may be tensors)."""
+        problems = list(problems)
+        arr = (GemmDesc * len(problems))()
+        for d, q in zip(arr, problems):
+            d.trans_a, d.trans_b = int(q.get("trans_a", 0)), int(q.get("trans_b", 0))
+            d.m, d.n, d.k = q["m"], q["n"], q["k"]
+            d.alpha, d.beta = q.get("alpha", 1.0), q.get("beta", 0.0)
+            d.a, d.lda, d.stride_a = _addr(q["a"]), q["lda"], q.get("stride_a", 0)
+            d.b, d.ldb, d.stride_b = _addr(q["b"]), q["ldb"], q.get("stride_b", 0)
+            d.c, d.ldc, d.stride_c = _addr(q["c"]), q["ldc"], q.get("stride_c", 0)
+            d.batch, d.epilogue = q.get("batch", 1), q.get("epilogue", 0)
+        self._check(self.lib.sushi_cuda_sgemm_grouped(self._ctx, dev, arr, len(problems)))
 
     def relu(self, x, count: int, dev: int = 0):
         self._check(self.lib.sushi_cuda_relu(self._ctx, dev, _addr(x), count))

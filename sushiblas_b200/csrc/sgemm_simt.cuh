@@ -66,23 +66,16 @@ __device__ __forceinline__ void simt_store_tile(float (*smem)[R + 4],
     }
 }
 
-// TA / TB: op(A) = A^T / op(B) = B^T.  BM == BN in {64, 128}; TM == TN == BM / 16.
+// One BM x BN tile (tm, tn) of batch entry bi.  TA / TB: op(A) = A^T / op(B) = B^T.
+// BM == BN in {64, 128}; TM == TN == BM / 16.  As / Bs: shared-memory staging of the caller.
 template <int BM, int BN, bool TA, bool TB>
-__global__ void __launch_bounds__(SIMT_THREADS)
-sgemm_simt_kernel(const SimtGemmArgs p)
+__device__ __forceinline__ void simt_gemm_tile(const SimtGemmArgs& p, int64_t tm, int64_t tn, int64_t bi,
+                                               float (*As)[BM + 4], float (*Bs)[BN + 4])
 {
     constexpr int TM = BM / 16, TN = BN / 16;
     constexpr int GM = TM / 4, GN = TN / 4;
-    __shared__ __align__(16) float As[SIMT_BK][BM + 4];
-    __shared__ __align__(16) float Bs[SIMT_BK][BN + 4];
-
     const int t = threadIdx.x;
     const int tx = t % 16, ty = t / 16;
-
-    int64_t tile = blockIdx.x;
-    const int64_t tn = tile % p.tiles_n; tile /= p.tiles_n;
-    const int64_t tm = tile % p.tiles_m;
-    const int64_t bi = tile / p.tiles_m;
 
     const float* __restrict__ A = p.a + bi * p.stride_a;
     const float* __restrict__ B = p.b + bi * p.stride_b;
@@ -180,6 +173,57 @@ sgemm_simt_kernel(const SimtGemmArgs p)
             }
         }
     }
+}
+
+template <int BM, int BN, bool TA, bool TB>
+__global__ void __launch_bounds__(SIMT_THREADS)
+sgemm_simt_kernel(const SimtGemmArgs p)
+{
+    __shared__ __align__(16) float As[SIMT_BK][BM + 4];
+    __shared__ __align__(16) float Bs[SIMT_BK][BN + 4];
+    int64_t tile = blockIdx.x;
+    const int64_t tn = tile % p.tiles_n; tile /= p.tiles_n;
+    const int64_t tm = tile % p.tiles_m;
+    const int64_t bi = tile / p.tiles_m;
+    simt_gemm_tile<BM, BN, TA, TB>(p, tm, tn, bi, As, Bs);
+}
+
+// Grouped launch: many independent small GEMMs in one grid.  Problem i owns the tiles
+// [first_tile, first_tile + tiles_m*tiles_n*batch) of the grid (64 x 64 tiles).
+struct GroupedGemm
+{
+    SimtGemmArgs g;
+    int32_t trans_a, trans_b;
+    int64_t first_tile;
+};
+
+__global__ void __launch_bounds__(SIMT_THREADS)
+sgemm_grouped_simt_kernel(const GroupedGemm* __restrict__ problems, int count)
+{
+    __shared__ __align__(16) float As[SIMT_BK][64 + 4];
+    __shared__ __align__(16) float Bs[SIMT_BK][64 + 4];
+    __shared__ GroupedGemm prob;
+    if (threadIdx.x == 0)
+    {
+        // last problem whose first tile is <= this CTA's tile
+        const int64_t t = blockIdx.x;
+        int lo = 0, hi = count - 1;
+        while (lo < hi)
+        {
+            const int mid = (lo + hi + 1) >> 1;
+            if (problems[mid].first_tile <= t) lo = mid; else hi = mid - 1;
+        }
+        prob = problems[lo];
+    }
+    __syncthreads();
+    int64_t tile = (int64_t)blockIdx.x - prob.first_tile;
+    const int64_t tn = tile % prob.g.tiles_n; tile /= prob.g.tiles_n;
+    const int64_t tm = tile % prob.g.tiles_m;
+    const int64_t bi = tile / prob.g.tiles_m;
+    if (!prob.trans_a && !prob.trans_b) simt_gemm_tile<64, 64, false, false>(prob.g, tm, tn, bi, As, Bs);
+    else if (!prob.trans_a) simt_gemm_tile<64, 64, false, true>(prob.g, tm, tn, bi, As, Bs);
+    else if (!prob.trans_b) simt_gemm_tile<64, 64, true, false>(prob.g, tm, tn, bi, As, Bs);
+    else simt_gemm_tile<64, 64, true, true>(prob.g, tm, tn, bi, As, Bs);
 }
 
 // C <- beta * C (k == 0 or alpha == 0): no operand is read.  One thread per element.

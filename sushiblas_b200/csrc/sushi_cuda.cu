@@ -39,6 +39,8 @@ struct DeviceState
     // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t pipe_events[10] = {};
+    void* group_buf = nullptr;            // device copy of the grouped-launch problem list
+    size_t group_bytes = 0;
     void* sk_area = nullptr;              // split-K exchange area (epoch flags + slots), flags zeroed at allocation
     size_t sk_area_bytes = 0;
     unsigned int sk_epoch = 0;            // last epoch handed to a launch
@@ -458,6 +460,7 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         if (d.own_stream) cudaStreamSynchronize(d.own_stream);
         if (d.workspace) cudaFree(d.workspace);
         if (d.sk_area) cudaFree(d.sk_area);
+        if (d.group_buf) cudaFree(d.group_buf);
         for (void* s : d.stage) if (s) cudaFree(s);
         if (d.status) cudaFree(d.status);
         if (d.status_host) cudaFreeHost(d.status_host);
@@ -660,6 +663,65 @@ extern "C" int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int dev,
     opts.relu = (epilogue == SUSHI_EPILOGUE_RELU);
     return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc,
                     stride_c, batch, &opts);
+}
+
+extern "C" int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sushi_cuda_gemm_desc* problems, int64_t count)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || count < 0 || (count > 0 && !problems))
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_grouped: bad argument");
+    if (count == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    std::vector<sushi::GroupedGemm> small;
+    std::vector<int64_t> large;
+    small.reserve((size_t)count);
+    int64_t tiles = 0;
+    for (int64_t i = 0; i < count; ++i)
+    {
+        const sushi_cuda_gemm_desc& q = problems[i];
+        int rc = validate_gemm(ctx, q.m, q.n, q.k, q.a, q.lda, q.b, q.ldb, q.c, q.ldc, q.trans_a, q.trans_b, q.stride_a,
+                               q.stride_b, q.stride_c, q.batch);
+        if (rc != SUSHI_CUDA_OK) return rc;
+        if (q.epilogue != SUSHI_EPILOGUE_NONE && q.epilogue != SUSHI_EPILOGUE_RELU)
+            return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_grouped: unknown epilogue");
+        if (q.m == 0 || q.n == 0 || q.batch == 0) continue;
+        const bool tensor = ctx->variant == SUSHI_GEMM_TC3X ||
+                            (ctx->variant == SUSHI_GEMM_AUTO && prefer_tc3x(q.m, q.n, q.k, q.batch, d->sm_count));
+        if (tensor || q.k == 0 || q.alpha == 0.0f) { large.push_back(i); continue; }
+        sushi::GroupedGemm g;
+        g.g.a = q.a; g.g.b = q.b; g.g.c = q.c; g.g.m = q.m; g.g.n = q.n; g.g.k = q.k;
+        g.g.lda = q.lda; g.g.ldb = q.ldb; g.g.ldc = q.ldc;
+        g.g.stride_a = q.stride_a; g.g.stride_b = q.stride_b; g.g.stride_c = q.stride_c;
+        g.g.tiles_m = (q.m + 63) / 64; g.g.tiles_n = (q.n + 63) / 64;
+        g.g.alpha = q.alpha; g.g.beta = q.beta; g.g.relu = q.epilogue == SUSHI_EPILOGUE_RELU;
+        g.trans_a = q.trans_a != 0; g.trans_b = q.trans_b != 0;
+        g.first_tile = tiles;
+        tiles += g.g.tiles_m * g.g.tiles_n * q.batch;
+        small.push_back(g);
+    }
+    if (tiles > 0x7fffffffLL) return set_error(ctx, SUSHI_CUDA_ERR_UNSUPPORTED, "sgemm_grouped: too many tiles for one launch");
+    if (!small.empty())
+    {
+        const size_t bytes = small.size() * sizeof(sushi::GroupedGemm);
+        int rc = grow(ctx, *d, &d->group_buf, &d->group_bytes, bytes);
+        if (rc != SUSHI_CUDA_OK) return rc;
+        // pageable source: the runtime stages it before returning, so `small` may go out of scope
+        SC_CUDA(ctx, cudaMemcpyAsync(d->group_buf, small.data(), bytes, cudaMemcpyHostToDevice, d->stream));
+        sushi::sgemm_grouped_simt_kernel<<<(unsigned)tiles, sushi::SIMT_THREADS, 0, d->stream>>>(
+            static_cast<const sushi::GroupedGemm*>(d->group_buf), (int)small.size());
+        ctx->launches++;
+        SC_CUDA(ctx, cudaGetLastError());
+    }
+    for (int64_t i : large)
+    {
+        const sushi_cuda_gemm_desc& q = problems[i];
+        SlabReuse opts;
+        opts.relu = q.epilogue == SUSHI_EPILOGUE_RELU;
+        int rc = run_gemm(ctx, *d, q.trans_a, q.trans_b, q.m, q.n, q.k, q.alpha, q.a, q.lda, q.stride_a, q.b, q.ldb,
+                          q.stride_b, q.beta, q.c, q.ldc, q.stride_c, q.batch, &opts);
+        if (rc != SUSHI_CUDA_OK) return rc;
+    }
+    return SUSHI_CUDA_OK;
 }
 
 extern "C" int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count)

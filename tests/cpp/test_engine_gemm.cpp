@@ -269,16 +269,54 @@ TEST_CASE(FrameworkSimShapesAndStress)
         for (int i = 0; i < 5000; ++i) outs.push_back(engine.create_tensor({32, 32}, dev));
         std::vector<float> v(1024, 0.5f);
         src.from_host(v.data()); w.from_host(v.data());
+        for (int grouped = 1; grouped >= 0; --grouped)
+        {
+            engine.get_graph().set_grouping(grouped == 1);
+            const size_t before = engine.get_graph().grouped_count();
+            auto t0 = std::chrono::steady_clock::now();
+            engine.blas().gemm(w, w, src);
+            for (auto& o : outs) engine.blas().gemm(src, w, o);
+            engine.execute().wait();
+            double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+            std::printf("       1 writer + 5000 reader GEMMs (32^3), %s: %.3f ms\n",
+                        grouped ? "grouped launch" : "one launch each", ms);
+            // the writer stays alone (the readers depend on it); the 5000 readers form one group
+            EXPECT_EQ(engine.get_graph().grouped_count() - before, size_t(grouped ? 5000 : 0));
+            std::vector<float> got(1024);
+            outs[4999].to_host(got.data());
+            EXPECT_NEAR(got[0], 32 * (32 * 0.25f) * 0.5f, 1e-3);
+            outs[17].to_host(got.data());
+            EXPECT_NEAR(got[1023], 128.0f, 1e-3);
+            EXPECT_TRUE(ms > 0);
+        }
+        engine.get_graph().set_grouping(true);
+    }
+    {
+        // 3000 independent 8x8 GEMMs on SHARED tensors (tests/runtime/test_dependency_stress.cpp:67-83):
+        // inputs are staged up, one grouped launch, outputs staged back
+        std::vector<sb::Tensor> as, bs, cs;
+        for (int i = 0; i < 3000; ++i)
+        {
+            as.push_back(engine.create_tensor({8, 8})); bs.push_back(engine.create_tensor({8, 8})); cs.push_back(engine.create_tensor({8, 8}));
+            std::fill_n(as.back().data_as<float>(), 64, float(i % 7)); std::fill_n(bs.back().data_as<float>(), 64, 0.5f);
+        }
         auto t0 = std::chrono::steady_clock::now();
-        engine.blas().gemm(w, w, src);
-        for (auto& o : outs) engine.blas().gemm(src, w, o);
+        for (int i = 0; i < 3000; ++i) engine.blas().gemm(as[i], bs[i], cs[i]);
         engine.execute().wait();
         double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-        std::printf("       1 writer + 5000 reader GEMMs (32^3): %.3f ms\n", ms);
-        std::vector<float> got(1024);
-        outs[4999].to_host(got.data());
-        EXPECT_NEAR(got[0], 32 * (32 * 0.25f) * 0.5f, 1e-3);
-        EXPECT_TRUE(ms > 0);
+        std::printf("       3000 independent GEMMs (8^3, SHARED tensors): %.3f ms\n", ms);
+        for (int i : {0, 1, 6, 2999}) EXPECT_NEAR(cs[i].data_as<float>()[63], 8 * float(i % 7) * 0.5f, 1e-4);
+    }
+    {
+        // dependent small GEMMs must not be grouped together: C1 = A*B, C2 = C1*B, C3 = C2*B
+        auto A = engine.create_tensor({16, 16}), B = engine.create_tensor({16, 16});
+        auto C1 = engine.create_tensor({16, 16}), C2 = engine.create_tensor({16, 16}), C3 = engine.create_tensor({16, 16});
+        std::fill_n(A.data_as<float>(), 256, 1.0f); std::fill_n(B.data_as<float>(), 256, 0.25f);
+        engine.blas().gemm(A, B, C1); engine.blas().gemm(C1, B, C2); engine.blas().gemm(C2, B, C3);
+        const size_t before = engine.get_graph().grouped_count();
+        engine.execute().wait();
+        EXPECT_EQ(engine.get_graph().grouped_count(), before);
+        EXPECT_NEAR(C3.data_as<float>()[100], 64.0f, 1e-4);      // (16*0.25)^3
     }
 }
 

@@ -370,6 +370,50 @@ def test_relu_epilogue_and_standalone_relu(ctx, variant):
         ctx.sgemm_strided_batched_ex(0, 0, 4, 4, 4, 1.0, x, 4, 0, x, 4, 0, 0.0, x, 4, 0, 1, 7)   # unknown epilogue
 
 
+# ------------------------------------------------------------------ grouped launch of small GEMMs
+def test_grouped_small_gemms(ctx):
+    """Independent small problems of mixed shapes, transposes, alpha/beta and epilogues in one
+    call equal the same problems run one by one (same FFMA kernel body) bit for bit; a large
+    problem in the list takes the tensor-core path and stays within tolerance."""
+    rng = np.random.default_rng(17)
+    probs, singles = [], []
+    for i in range(200):
+        m, n, k = (int(rng.choice([1, 3, 8, 17, 32, 64, 65, 100])) for _ in range(3))
+        ta, tb = int(rng.integers(2)), int(rng.integers(2))
+        batch = int(rng.choice([1, 1, 2]))
+        cs = make_case(1000 + i, ta, tb, m, n, k, batch, pad=(int(rng.integers(3)), 0, int(rng.integers(3))))
+        alpha, beta = float(rng.choice([1.0, -0.5])), float(rng.choice([0.0, 1.0, 0.5]))
+        epi = int(rng.integers(2))
+        da, db = dev(cs["a"]), dev(cs["b"])
+        c_grp, c_one = dev(cs["c"].copy()), dev(cs["c"].copy())
+        probs.append(dict(trans_a=ta, trans_b=tb, m=m, n=n, k=k, alpha=alpha, beta=beta, a=da, lda=cs["lda"],
+                          stride_a=cs["sa"], b=db, ldb=cs["ldb"], stride_b=cs["sb"], c=c_grp, ldc=cs["ldc"],
+                          stride_c=cs["sc"], batch=batch, epilogue=epi))
+        singles.append((c_one, c_grp))
+    before = ctx.launch_count()
+    ctx.sgemm_grouped(probs)
+    assert ctx.launch_count() - before == 1          # one kernel for all 200 problems
+    ctx.set_gemm_variant(SIMT)
+    for q, (c_one, _) in zip(probs, singles):
+        ctx.sgemm_strided_batched_ex(q["trans_a"], q["trans_b"], q["m"], q["n"], q["k"], q["alpha"], q["a"], q["lda"],
+                                     q["stride_a"], q["b"], q["ldb"], q["stride_b"], q["beta"], c_one, q["ldc"],
+                                     q["stride_c"], q["batch"], q["epilogue"])
+    ctx.sync()
+    ctx.set_gemm_variant(AUTO)
+    for i, (c_one, c_grp) in enumerate(singles):
+        assert torch.equal(c_one, c_grp), i
+    # a list mixing a big problem (tensor-core path) with small ones
+    big = make_case(5, 0, 0, 1024, 1024, 512)
+    dA, dB, dC = dev(big["a"]), dev(big["b"]), dev(big["c"].copy())
+    small = probs[:3]
+    ctx.sgemm_grouped([dict(m=1024, n=1024, k=512, a=dA, lda=512, b=dB, ldb=1024, c=dC, ldc=1024)] + small)
+    ctx.sync()
+    ref, absab = og.gemm_f64_np(0, 0, 1024, 1024, 512, 1.0, big["a"], 512, 0, big["b"], 1024, 0, 0.0, None, 1024, 0, 1)
+    r, _ = og.tolerance_ratio(dC.cpu().numpy().reshape(1, 1024, 1024), ref, absab, 512, budget=BUDGET)
+    assert r <= 1.0
+    ctx.sgemm_grouped([])                            # empty list: no-op
+
+
 # ------------------------------------------------------------------ host-buffer entry point and storage calls
 def test_host_entry_point_matches_device_path(ctx):
     m, n, k, batch = 300, 200, 150, 2
