@@ -77,6 +77,13 @@ SUSHI_CUDA_API int sushi_cuda_sync(sushi_cuda_ctx* ctx, int dev);
 SUSHI_CUDA_API int sushi_cuda_set_stream(sushi_cuda_ctx* ctx, int dev, void* cuda_stream);
 SUSHI_CUDA_API int sushi_cuda_get_stream(sushi_cuda_ctx* ctx, int dev, void** cuda_stream);
 
+/* Failure-detection self-test: launches one CTA that waits, with the same bounded-wait routine
+ * the GEMM kernel uses, on a barrier nothing ever arrives on; after `limit_ms` (1..2000) the
+ * wait gives up and records its code.  The next sushi_cuda_sync() must then return
+ * SUSHI_CUDA_ERR_KERNEL_TIMEOUT, clear the status and leave the context usable.  Nothing
+ * faults, traps or hangs.                                                                    */
+SUSHI_CUDA_API int sushi_cuda_selftest_bounded_wait(sushi_cuda_ctx* ctx, int dev, int limit_ms);
+
 SUSHI_CUDA_API int sushi_cuda_set_gemm_variant(sushi_cuda_ctx* ctx, int variant);
 /* Number of kernels this context has launched so far (all devices). */
 SUSHI_CUDA_API int sushi_cuda_launch_count(sushi_cuda_ctx* ctx, int64_t* launches);

@@ -39,6 +39,7 @@ SIGNATURES = {
     "sushi_cuda_sync": (_int, [_vp, _int]),
     "sushi_cuda_set_stream": (_int, [_vp, _int, _vp]),
     "sushi_cuda_get_stream": (_int, [_vp, _int, ctypes.POINTER(_vp)]),
+    "sushi_cuda_selftest_bounded_wait": (_int, [_vp, _int, _int]),
     "sushi_cuda_set_gemm_variant": (_int, [_vp, _int]),
     "sushi_cuda_launch_count": (_int, [_vp, ctypes.POINTER(_i64)]),
     "sushi_cuda_kernel_timing_enable": (_int, [_vp, _int]),
@@ -194,6 +195,9 @@ class SushiCuda:
         out = _vp()
         self._check(self.lib.sushi_cuda_get_stream(self._ctx, dev, ctypes.byref(out)))
         return out.value or 0
+
+    def selftest_bounded_wait(self, limit_ms: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_selftest_bounded_wait(self._ctx, dev, limit_ms))
 
     def set_gemm_variant(self, variant: int):
         self._check(self.lib.sushi_cuda_set_gemm_variant(self._ctx, variant))

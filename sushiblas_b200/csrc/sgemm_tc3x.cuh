@@ -69,7 +69,7 @@ constexpr unsigned long long DRAIN_LIMIT_NS = 2000000ull;    // 2 ms per drain w
 
 // status codes written to *status (first writer wins)
 enum : int { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA_FULL = 2, ST_TIMEOUT_MMA_ACC = 3,
-             ST_TIMEOUT_EPILOGUE = 4, ST_TIMEOUT_PARTIAL_FLAG = 5, ST_TIMEOUT_PARTIAL_PUBLISH = 6, ST_TIMEOUT_CONVERT = 7 };
+             ST_TIMEOUT_EPILOGUE = 4, ST_TIMEOUT_PARTIAL_FLAG = 5, ST_TIMEOUT_PARTIAL_PUBLISH = 6, ST_TIMEOUT_CONVERT = 7, ST_SELFTEST = 99 };
 
 constexpr int SK_SLOT_FLOATS = BM * BN;               // one raw accumulator tile per published slice
 constexpr int SK_MAX_SPLIT = 4;                       // at most this many K slices per tile
@@ -717,6 +717,21 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// One CTA, one thread: the bounded wait on a barrier that never completes (failure-detection
+// self-test).  Returns after limit_ns with ST_SELFTEST in *status.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0)
+    {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait_bounded(smem_u32(&bar), 0, &abort_flag, status, ST_SELFTEST, limit_ns);
     }
 }
 

@@ -497,6 +497,18 @@ extern "C" int sushi_cuda_sync(sushi_cuda_ctx* ctx, int dev)
     return SUSHI_CUDA_OK;
 }
 
+extern "C" int sushi_cuda_selftest_bounded_wait(sushi_cuda_ctx* ctx, int dev, int limit_ms)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || limit_ms < 1 || limit_ms > 2000)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "selftest_bounded_wait: bad argument (limit 1..2000 ms)");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    sushi::tc3x::bounded_wait_selftest_kernel<<<1, 32, 0, d->stream>>>(d->status, (unsigned long long)limit_ms * 1000000ull);
+    ctx->launches++;
+    SC_CUDA(ctx, cudaGetLastError());
+    return SUSHI_CUDA_OK;
+}
+
 extern "C" int sushi_cuda_set_stream(sushi_cuda_ctx* ctx, int dev, void* cuda_stream)
 {
     DeviceState* d = get_dev(ctx, dev);

@@ -69,3 +69,14 @@ def test_no_device_fails_loudly(lib_path):
     with pytest.raises(SushiCudaError) as e:
         SushiCuda([0])
     assert e.value.code in (-2, -3)
+
+
+def test_missing_library_is_an_error_not_a_fallback(tmp_path):
+    from sushiblas_b200 import capi
+    with pytest.raises(FileNotFoundError, match="no CPU fallback"):
+        capi.load_library(str(tmp_path / "libsushiblas_cuda.so"))
+    # the product package never imports the oracle
+    import subprocess, sys
+    code = ("import sys; import sushiblas_b200, sushiblas_b200.capi; "
+            "bad = [m for m in sys.modules if m == 'oracle' or m.startswith('oracle.')]; sys.exit(1 if bad else 0)")
+    assert subprocess.run([sys.executable, "-c", code], cwd=ROOT).returncode == 0

@@ -492,6 +492,27 @@ def test_storage_calls_round_trip(ctx):
     ctx.free(d); ctx.free(d2); ctx.host_free(h)
 
 
+def test_bounded_wait_expiry_reaches_the_host_and_context_survives(ctx):
+    """Failure detection without a fault: a kernel-side wait on a barrier nothing arrives on gives
+    up after its limit and records a code; sync reports KERNEL_TIMEOUT once, clears it, and the
+    same context keeps computing correctly."""
+    import time
+    from sushiblas_b200 import SushiCudaError
+    ctx.sync()
+    t0 = time.perf_counter()
+    ctx.selftest_bounded_wait(50)
+    with pytest.raises(SushiCudaError) as e:
+        ctx.sync()
+    dt = time.perf_counter() - t0
+    assert e.value.code == -5 and "code 99" in str(e.value)
+    assert 0.04 < dt < 1.0, dt                  # waited about the limit, not forever
+    ctx.sync()                                   # status was cleared: no error any more
+    check(ctx, TC3X, 0, 0, 512, 512, 256, 1.0, 0.0)
+    check(ctx, SIMT, 0, 0, 64, 64, 64, 1.0, 0.0)
+    with pytest.raises(SushiCudaError):
+        ctx.selftest_bounded_wait(100000)        # limit out of range is rejected, nothing is launched
+
+
 def test_launch_counter_counts_kernels(ctx):
     before = ctx.launch_count()
     check(ctx, SIMT, 0, 0, 64, 64, 64, 1.0, 0.0)
