@@ -191,6 +191,48 @@ namespace SushiBLAS
         return SushiRuntime::Execution::Event();
     }
 
+    // ---------------------------------------------------------------- Level3::gemm_row_sharded
+    inline SushiRuntime::Execution::Event Level3::gemm_row_sharded(const Tensor& A_local, const Tensor& B, Tensor& C_full,
+                                                                   bool transA, bool transB, float alpha, float beta)
+    {
+        using namespace SushiRuntime::Graph::Literals;
+        SB_THROW_IF(A_local.rank != 2 || B.rank != 2 || C_full.rank != 2, "Sharded GEMM requires 2D tensors.");
+        SB_THROW_IF(A_local.dtype != B.dtype || A_local.dtype != C_full.dtype, "Data type mismatch in GEMM operation.");
+        SB_THROW_IF(A_local.dtype != Core::DataType::FLOAT32,
+                    "Unsupported data type for GEMM operation (the CUDA backend serves FLOAT32 only).");
+        SB_THROW_IF(A_local.layout != Core::Layout::ROW_MAJOR || B.layout != Core::Layout::ROW_MAJOR ||
+                    C_full.layout != Core::Layout::ROW_MAJOR, "Sharded GEMM serves row-major tensors only.");
+        for (const Tensor* t : {&A_local, &B, static_cast<const Tensor*>(&C_full)})
+            SB_THROW_IF(!t->storage || t->storage->host_resident(), "Sharded GEMM requires DEVICE tensors.");
+        auto& rt = engine_.get_context();
+        const int64_t m = C_full.shape[0], n = C_full.shape[1];
+        const int64_t k = transB ? B.shape[1] : B.shape[0];
+        int64_t first = 0, count = 0;
+        sushi_cuda_partition(m, rt.nranks(), rt.rank(), &first, &count);
+        const int64_t a_rows = transA ? A_local.shape[1] : A_local.shape[0];
+        const int64_t a_k = transA ? A_local.shape[0] : A_local.shape[1];
+        SB_THROW_IF(a_rows != count || a_k != k, "A_local must hold this rank's {} rows of op(A) with k = {} (got {} x {}).",
+                    count, k, a_rows, a_k);
+        SB_THROW_IF((transB ? B.shape[0] : B.shape[1]) != n, "B does not match C ({} columns expected).", n);
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = "blas.lvl3.gemm_row_sharded";
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = "blas.lvl3.gemm_row_sharded"_op;
+        meta.set_param(0, alpha); meta.set_param(1, beta); meta.set_param(2, transA); meta.set_param(3, transB);
+        auto sa = A_local.storage; auto sb_ = B.storage; auto sc = C_full.storage;
+        const float* pa = A_local.data_as<float>(); const float* pb = B.data_as<float>(); float* pc = C_full.data_as<float>();
+        const int64_t lda = A_local.shape[1], ldb = B.shape[1], ldc = n;
+        engine_.get_graph().add_task(meta, {sa->data_ptr, sb_->data_ptr}, {sc->data_ptr},
+            [=](SushiRuntime::Execution::RuntimeContext& ctx) -> int
+            {
+                (void)sa; (void)sb_; (void)sc;       // keep the storages alive until the task has run
+                return sushi_cuda_sgemm_row_sharded(ctx.native_handle(), 0, transA, transB, m, n, k, alpha, pa, lda, pb, ldb,
+                                                    beta, pc, ldc, /*gather=*/1);
+            });
+        return SushiRuntime::Execution::Event();
+    }
+
     // ---------------------------------------------------------------- NonLinearOps::relu
     inline SushiRuntime::Execution::Event NonLinearOps::relu(Tensor& t)
     {

@@ -105,5 +105,16 @@ namespace SushiBLAS
             inline SushiRuntime::Execution::Event gemm(const Tensor& A, const Tensor& B, Tensor& C,
                                                        bool transA = false, bool transB = false,
                                                        float alpha = 1.0f, float beta = 0.0f);
+
+            /// Multi-GPU GEMM, one process per GPU (no counterpart in the reference).  The global
+            /// problem is C (m x n, the shape of C_full) = alpha*op(A)*op(B) + beta*C with A cut into
+            /// row blocks of op(A): this rank passes its block A_local (rows
+            /// [first, first+count) of op(A) as sushi_cuda_partition(m, nranks, rank) gives them; a
+            /// count x k tensor, or k x count when transA), the whole B, and a full-size C_full in
+            /// which it computes its own rows; the blocks are then exchanged so that every rank ends
+            /// with the complete C (NCCL over NVLink).  Row-major DEVICE tensors only.
+            inline SushiRuntime::Execution::Event gemm_row_sharded(const Tensor& A_local, const Tensor& B, Tensor& C_full,
+                                                                   bool transA = false, bool transB = false,
+                                                                   float alpha = 1.0f, float beta = 0.0f);
     };
 } // namespace SushiBLAS

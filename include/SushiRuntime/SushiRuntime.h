@@ -19,6 +19,9 @@
 #pragma once
 
 #include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <thread>
 #include <cstddef>
 #include <cstdint>
 #include <cstring>
@@ -306,6 +309,18 @@ namespace SushiRuntime
             };
         } // namespace detail
 
+        /// One process per GPU: which rank this process is, how many there are, which CUDA device it
+        /// drives, and a file through which rank 0 hands the 128-byte NCCL id to the others (any
+        /// path all ranks can read; it is created by rank 0 and may be deleted afterwards).
+        struct DistributedConfig
+        {
+            int rank = 0;
+            int nranks = 1;
+            int device = 0;
+            std::string id_file;
+            int timeout_s = 60;
+        };
+
         /// Owns the device context.  Construction needs a CUDA device (sm_100a): there is no CPU
         /// fallback, so it throws std::runtime_error otherwise.  The device is device 0 or the
         /// one named by $SUSHI_CUDA_DEVICE.
@@ -320,6 +335,54 @@ namespace SushiRuntime
                                                  sushi_cuda_last_error(nullptr));
                     allocator_ = make_sushi<detail::CudaAllocator>(ctx_);
                 }
+
+                /// Member of a multi-GPU job (the reference has no counterpart: its only multi-device
+                /// hook is get_queue(xpu_index), runtime_context.hpp:65).  Creates the context on
+                /// cfg.device and joins the NCCL communicator of cfg.nranks processes.
+                explicit RuntimeContext(const DistributedConfig& cfg) : rank_(cfg.rank), nranks_(cfg.nranks)
+                {
+                    if (cfg.nranks < 1 || cfg.rank < 0 || cfg.rank >= cfg.nranks)
+                        throw std::runtime_error("RuntimeContext: bad rank / nranks");
+                    const int dev = cfg.device;
+                    int rc = sushi_cuda_init(&dev, 1, &ctx_);
+                    if (rc != SUSHI_CUDA_OK)
+                        throw std::runtime_error(std::string("RuntimeContext: cannot create the CUDA context: ") +
+                                                 sushi_cuda_last_error(nullptr));
+                    allocator_ = make_sushi<detail::CudaAllocator>(ctx_);
+                    if (cfg.nranks == 1) return;
+                    unsigned char id[128];
+                    if (cfg.rank == 0)
+                    {
+                        rc = sushi_cuda_comm_unique_id(id);
+                        if (rc != SUSHI_CUDA_OK) fail("cannot create the NCCL id");
+                        const std::string tmp = cfg.id_file + ".tmp";
+                        std::FILE* f = std::fopen(tmp.c_str(), "wb");
+                        if (!f || std::fwrite(id, 1, sizeof id, f) != sizeof id) fail("cannot write the NCCL id file");
+                        std::fclose(f);
+                        if (std::rename(tmp.c_str(), cfg.id_file.c_str()) != 0) fail("cannot publish the NCCL id file");
+                    }
+                    else
+                    {
+                        // the host-side rendezvous is bounded: give up after timeout_s
+                        const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(cfg.timeout_s);
+                        bool got = false;
+                        while (!got && std::chrono::steady_clock::now() < deadline)
+                        {
+                            if (std::FILE* f = std::fopen(cfg.id_file.c_str(), "rb"))
+                            {
+                                got = std::fread(id, 1, sizeof id, f) == sizeof id;
+                                std::fclose(f);
+                            }
+                            if (!got) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+                        }
+                        if (!got) fail("timed out waiting for the NCCL id file of rank 0");
+                    }
+                    rc = sushi_cuda_comm_init_rank(ctx_, 0, id, cfg.nranks, cfg.rank);
+                    if (rc != SUSHI_CUDA_OK) fail("cannot join the NCCL communicator");
+                }
+
+                int rank() const { return rank_; }
+                int nranks() const { return nranks_; }
 
                 ~RuntimeContext()
                 {
@@ -348,8 +411,17 @@ namespace SushiRuntime
                 sushi_cuda_ctx* native_handle() const { return ctx_; }
 
             private:
+                [[noreturn]] void fail(const char* what)
+                {
+                    std::string msg = std::string("RuntimeContext: ") + what + ": " + sushi_cuda_last_error(ctx_);
+                    allocator_.reset();
+                    if (ctx_) sushi_cuda_destroy(ctx_);
+                    ctx_ = nullptr;
+                    throw std::runtime_error(msg);
+                }
                 sushi_cuda_ctx* ctx_ = nullptr;
                 sushi_ptr<Memory::USMAllocator> allocator_;
+                int rank_ = 0, nranks_ = 1;
         };
 
         inline void Event::wait()

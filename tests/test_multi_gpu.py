@@ -22,3 +22,20 @@ def test_sharded_gemm_matches_single_gpu(world, lib_path):
                        capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-4000:]
     assert "total failures=0" in p.stdout
+
+
+def test_cpp_engine_row_sharded_two_processes(tmp_path, lib_path):
+    """The C++ API's distributed RuntimeContext + gemm_row_sharded, two processes on two GPUs;
+    the NCCL id travels through a file."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from sushiblas_b200 import build_cpp_tests
+    exe = build_cpp_tests()["test_engine_sharded"]
+    id_file = str(tmp_path / "nccl_id.bin")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([exe, str(r), "2", id_file], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+             for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for p, out in zip(procs, outs):
+        assert p.returncode == 0, out
+        assert " 0 failed" in out
