@@ -191,6 +191,81 @@ namespace SushiBLAS
         return SushiRuntime::Execution::Event();
     }
 
+    // ---------------------------------------------------------------- Level3::syrk
+    inline SushiRuntime::Execution::Event Level3::syrk(const Tensor& A, Tensor& C, bool upper, bool transA, float alpha,
+                                                       float beta)
+    {
+        using namespace SushiRuntime::Graph::Literals;
+        SB_THROW_IF(A.rank < 2 || C.rank < 2, "SYRK requires at least 2D tensors.");
+        SB_THROW_IF(A.dtype != C.dtype, "Data type mismatch in SYRK operation.");
+        SB_THROW_IF(A.dtype != Core::DataType::FLOAT32,
+                    "Unsupported data type for SYRK operation (the CUDA backend serves FLOAT32 only).");
+        const int32_t ra = A.rank, rc = C.rank;
+        const int64_t n = C.shape[rc - 2];
+        SB_THROW_IF(C.shape[rc - 1] != n, "SYRK requires C to be a square matrix.");
+        const int64_t inner_n = transA ? A.shape[ra - 1] : A.shape[ra - 2];
+        const int64_t k = transA ? A.shape[ra - 2] : A.shape[ra - 1];
+        SB_THROW_IF(inner_n != n, "Dimension mismatch in SYRK: A does not match C dimension.");
+        int64_t batch = 1;
+        for (int i = 0; i < rc - 2; ++i) batch *= C.shape[i];
+        const bool row = A.layout == Core::Layout::ROW_MAJOR;
+        const int64_t lda = row ? A.shape[ra - 1] : A.shape[ra - 2];
+        const int64_t ldc = (C.layout == Core::Layout::ROW_MAJOR) ? C.shape[rc - 1] : C.shape[rc - 2];
+        int64_t stride_a = 0, stride_c = 0;
+        if (batch > 1)
+        {
+            SB_THROW_IF(ra < 3, "Batched SYRK requires A of rank >= 3 (got {}).", ra);
+            stride_a = A.strides[ra - 3];
+            stride_c = C.strides[rc - 3];
+        }
+        // a column-major update is the row-major update of the other triangle with the other transpose
+        const bool rm_upper = row ? upper : !upper;
+        const bool rm_trans = row ? transA : !transA;
+
+        struct Operand { SushiRuntime::sushi_ptr<Storage> storage; float* ptr; int64_t extent; bool host; };
+        auto describe = [](const Tensor& t, int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t nb) {
+            Operand o{t.storage, t.data_as<float>(), detail::operand_extent(rows, cols, ld, stride, nb), false};
+            o.host = t.storage->host_resident();
+            const std::size_t need = (static_cast<std::size_t>(t.storage_offset) + static_cast<std::size_t>(o.extent)) * sizeof(float);
+            SB_THROW_IF(need > t.storage->size_bytes, "SYRK operand does not fit its storage (needs {} bytes, has {}).", need,
+                        t.storage->size_bytes);
+            return o;
+        };
+        Operand oa = describe(A, rm_trans ? k : n, rm_trans ? n : k, lda, stride_a, batch);
+        Operand oc = describe(C, n, n, ldc, stride_c, batch);
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = "blas.lvl3.syrk";
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = "blas.lvl3.syrk"_op;
+        meta.set_param(0, alpha); meta.set_param(1, beta); meta.set_param(2, upper); meta.set_param(3, transA);
+        engine_.get_graph().add_task(meta, {A.storage->data_ptr}, {C.storage->data_ptr},
+            [=](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            {
+                sushi_cuda_ctx* ctx = rt.native_handle();
+                auto on_device = [ctx](const Operand& o, bool upload, float** out) -> int
+                {
+                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
+                    if (!base) return SUSHI_CUDA_ERR_OOM;
+                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
+                    if (o.host && upload && o.extent > 0)
+                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
+                    return SUSHI_CUDA_OK;
+                };
+                float *da = nullptr, *dc = nullptr;
+                int rc2 = on_device(oa, true, &da);
+                // the untouched triangle must survive the copy back: host-resident C always goes up
+                if (rc2 == SUSHI_CUDA_OK) rc2 = on_device(oc, true, &dc);
+                if (rc2 != SUSHI_CUDA_OK) return rc2;
+                rc2 = sushi_cuda_ssyrk_strided_batched(ctx, 0, rm_upper, rm_trans, n, k, alpha, da, lda, stride_a, beta, dc, ldc,
+                                                       stride_c, batch);
+                if (rc2 == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
+                    rc2 = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
+                return rc2;
+            });
+        return SushiRuntime::Execution::Event();
+    }
+
     // ---------------------------------------------------------------- Level3::gemm_row_sharded
     inline SushiRuntime::Execution::Event Level3::gemm_row_sharded(const Tensor& A_local, const Tensor& B, Tensor& C_full,
                                                                    bool transA, bool transB, float alpha, float beta)

@@ -5,7 +5,8 @@
 //
 // The record phase is the reference's: validate, derive m/n/k/ld/stride/batch from the Tensor
 // metadata, build TaskMetadata, add a task.  The task body calls the C ABI instead of oneMKL.
-// Only FLOAT32 is served (the named path); SYRK / TRSM are not part of this build.
+// Only FLOAT32 is served (the named path).  SYRK runs on the same kernels; TRSM is not part of
+// this build.
 #pragma once
 
 #include <cstdint>
@@ -104,6 +105,15 @@ namespace SushiBLAS
             /// a tensor without storage, or operands that do not fit their storage.
             inline SushiRuntime::Execution::Event gemm(const Tensor& A, const Tensor& B, Tensor& C,
                                                        bool transA = false, bool transB = false,
+                                                       float alpha = 1.0f, float beta = 0.0f);
+
+            /// Symmetric rank-k update C <- alpha*op(A)*op(A)^T + beta*C on the upper or lower triangle
+            /// of the square C; the other triangle is left untouched (reference declaration
+            /// level3.hpp syrk, definition src/ops/blas/level3/syrk.cpp:84-193).  n comes from C, k from
+            /// A (A is n x k, or k x n when transA), leading dimensions from the shapes, batch strides
+            /// from strides[rank-3].  FLOAT32 only.  Throws std::runtime_error on rank < 2, dtype
+            /// mismatch, a non-square C or A not matching C.
+            inline SushiRuntime::Execution::Event syrk(const Tensor& A, Tensor& C, bool upper = false, bool transA = false,
                                                        float alpha = 1.0f, float beta = 0.0f);
 
             /// Multi-GPU GEMM, one process per GPU (no counterpart in the reference).  The global

@@ -144,6 +144,19 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int 
                                                        float beta, float* c, int64_t ldc, int64_t stride_c,
                                                        int64_t batch, int epilogue);
 
+/* Symmetric rank-k update, row-major:  C <- alpha * op(A) * op(A)^T + beta * C  on the upper
+ * (upper != 0) or lower triangle of the n x n matrix C; the other triangle is neither read nor
+ * written.  op(A) = A (n x k, trans == 0) or A^T (A stored k x n, trans != 0).
+ * Replaces oneapi::mkl::blas::row_major::syrk / syrk_batch (call sites
+ * src/ops/blas/level3/syrk.cpp:60-78).  Runs on the GEMM main loop: tiles outside the triangle
+ * are skipped, diagonal tiles store under a mask, and A's hi/lo planes serve as both operands.  */
+SUSHI_CUDA_API int sushi_cuda_ssyrk(sushi_cuda_ctx* ctx, int dev, int upper, int trans, int64_t n, int64_t k,
+                                    float alpha, const float* a, int64_t lda, float beta, float* c, int64_t ldc);
+SUSHI_CUDA_API int sushi_cuda_ssyrk_strided_batched(sushi_cuda_ctx* ctx, int dev, int upper, int trans,
+                                                    int64_t n, int64_t k, float alpha,
+                                                    const float* a, int64_t lda, int64_t stride_a, float beta,
+                                                    float* c, int64_t ldc, int64_t stride_c, int64_t batch);
+
 /* Many independent GEMMs in one call (no counterpart call in the reference; it is what its
  * scheduler stress tests submit per execute(): 5000 GEMMs of 32^3 and 3000 of 8^3,
  * tests/runtime/test_dependency_stress.cpp:17-45,67-83).  No output of one problem may overlap

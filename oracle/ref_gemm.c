@@ -188,3 +188,48 @@ double oracle_check_tolerance(int64_t m, int64_t n, int64_t k, int64_t batch,
     if (max_ulps_noK) *max_ulps_noK = worst_nok;
     return worst;
 }
+
+/*
+ * oracle_syrk_f64acc: symmetric rank-k update, fp32 operands, fp64 accumulation.
+ *
+ *      C <- alpha * op(A) * op(A)^T + beta * C   on one triangle of the n x n matrix C
+ *
+ * Restates what the reference forwards to oneapi::mkl::blas::{row,column}_major::syrk[_batch]
+ * (call sites src/ops/blas/level3/syrk.cpp:60-78) after deriving n, k, lda, ldc and the batch
+ * strides from the tensors (syrk.cpp:84-116): n from C, k from A (A is n x k, or k x n when
+ * trans), only the `upper` or lower triangle is referenced and updated, the other one is left
+ * as it is.  c_out64 must arrive holding C's current values (as double) everywhere; elements of
+ * the updated triangle are overwritten.  abs_aa (optional) receives sum_k |a_ik||a_jk| there.
+ * Pinned by the reference's own known answers tests/blas/level3/test_syrk.cpp:39-103.
+ */
+int oracle_syrk_f64acc(int layout_row, int upper, int trans, int64_t n, int64_t k, float alpha,
+                       const float* a, int64_t lda, int64_t stride_a, float beta,
+                       const float* c_in, int64_t ldc, int64_t stride_c, int64_t batch,
+                       double* c_out64, double* abs_aa)
+{
+    if (n < 0 || k < 0 || batch < 0 || !c_out64) return -1;
+    for (int64_t bi = 0; bi < batch; ++bi)
+    {
+        const float* ab = a + bi * stride_a;
+        for (int64_t i = 0; i < n; ++i)
+            for (int64_t j = 0; j < n; ++j)
+            {
+                if (upper ? (j < i) : (j > i)) continue;
+                double s = 0.0, sabs = 0.0;
+                for (int64_t kk = 0; kk < k; ++kk)
+                {
+                    /* op(A)(i, kk): A stored n x k (trans == 0) or k x n (trans != 0) */
+                    double x = (double)ab[op_index(layout_row, trans, i, kk, lda)];
+                    double y = (double)ab[op_index(layout_row, trans, j, kk, lda)];
+                    s += x * y;
+                    sabs += fabs(x) * fabs(y);
+                }
+                int64_t ci = bi * stride_c + (layout_row ? i * ldc + j : j * ldc + i);
+                double v = (double)alpha * s;
+                if (beta != 0.0f) v += (double)beta * (double)c_in[ci];
+                c_out64[ci] = v;
+                if (abs_aa) abs_aa[ci] = sabs;
+            }
+    }
+    return 0;
+}

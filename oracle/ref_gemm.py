@@ -58,6 +58,9 @@ def _lib():
         lib.oracle_gemm_f32.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                         i64, i64, i64, f32, p, i64, i64, p, i64, i64,
                                         f32, p, i64, i64, i64]
+        lib.oracle_syrk_f64acc.restype = ctypes.c_int
+        lib.oracle_syrk_f64acc.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, i64, i64, f32, p, i64, i64, f32,
+                                           p, i64, i64, i64, p, p]
         lib.oracle_check_tolerance.restype = dbl
         lib.oracle_check_tolerance.argtypes = [i64, i64, i64, i64, f32, dbl, p, p, p, p,
                                                i64, i64, ctypes.POINTER(dbl)]
@@ -136,6 +139,32 @@ def gemm_f64_c(trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, strid
     if rc != 0:
         raise ValueError("oracle_gemm_f64acc rejected its arguments")
     return out, absab
+
+
+def syrk_f64_c(upper, trans, n, k, alpha, a, lda, stride_a, beta, c_in, ldc, stride_c, batch, layout=ROW_MAJOR):
+    """fp64-accumulated SYRK through the C restatement (syrk.cpp:84-116 semantics).  Returns
+    (c float64 flat indexed like C, with the untouched triangle equal to c_in; abs_aa)."""
+    a = np.ascontiguousarray(a, dtype=np.float32).ravel()
+    c32 = np.ascontiguousarray(c_in, dtype=np.float32).ravel()
+    out = c32.astype(np.float64)
+    absaa = np.zeros(out.shape, dtype=np.float64)
+    rc = _lib().oracle_syrk_f64acc(1 if layout == ROW_MAJOR else 0, int(upper), int(trans), n, k, alpha, _ptr(a), lda,
+                                   stride_a, beta, _ptr(c32), ldc, stride_c, batch, _ptr(out), _ptr(absaa))
+    if rc != 0:
+        raise ValueError("oracle_syrk_f64acc rejected its arguments")
+    return out, absaa
+
+
+def syrk_f64_np(upper, trans, n, k, alpha, a, lda, stride_a, beta, c_in, ldc, stride_c, batch):
+    """numpy twin for row-major storage and larger sizes: the GEMM oracle with B = A, masked to
+    the triangle.  Returns dense (batch, n, n): result (other triangle = c_in), abs_aa, mask."""
+    full, absab = gemm_f64_np(trans, not trans, n, n, k, alpha, a, lda, stride_a, a, lda, stride_a, beta, c_in, ldc,
+                              stride_c, batch)
+    c32 = np.asarray(c_in, dtype=np.float32).ravel()
+    cin = _view(c32, n, n, ldc, stride_c, batch).astype(np.float64)
+    i, j = np.indices((n, n))
+    mask = (j >= i) if upper else (j <= i)
+    return np.where(mask[None], full, cin), np.where(mask[None], absab, 0.0), mask
 
 
 def gemm_f32_c(trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,

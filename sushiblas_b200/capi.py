@@ -60,6 +60,9 @@ SIGNATURES = {
     "sushi_cuda_sgemm_strided_batched_ex": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                    _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
     "sushi_cuda_relu": (_int, [_vp, _int, _vp, _i64]),
+    "sushi_cuda_ssyrk": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
+    "sushi_cuda_ssyrk_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _i64, _f32,
+                                                _vp, _i64, _i64, _i64]),
     "sushi_cuda_sgemm_grouped": (_int, [_vp, _int, ctypes.POINTER(GemmDesc), _i64]),
     "sushi_cuda_sgemm_strided_batched_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                      _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
@@ -266,6 +269,10 @@ class SushiCuda:
         self._check(self.lib.sushi_cuda_sgemm_strided_batched_ex(
             self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
             _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch, epilogue))
+
+    def ssyrk(self, upper, trans, n, k, alpha, a, lda, beta, c, ldc, stride_a=0, stride_c=0, batch=1, dev: int = 0):
+        self._check(self.lib.sushi_cuda_ssyrk_strided_batched(self._ctx, dev, int(upper), int(trans), n, k, alpha,
+                                                              _addr(a), lda, stride_a, beta, _addr(c), ldc, stride_c, batch))
 
     def sgemm_grouped(self, problems, dev: int = 0):
         """problems: iterable of dicts with the fields of sushi_cuda_gemm_desc (pointers may be tensors)."""

@@ -25,6 +25,7 @@ struct SimtGemmArgs
     int64_t tiles_m, tiles_n;
     float alpha, beta;
     int relu;            // epilogue activation: max(alpha*acc + beta*C, 0)
+    int tri;             // 0: full C; 1: only row >= col is written (lower triangle); 2: only row <= col (upper)
 };
 
 constexpr int SIMT_THREADS = 256;
@@ -81,6 +82,9 @@ __device__ __forceinline__ void simt_gemm_tile(const SimtGemmArgs& p, int64_t tm
     const float* __restrict__ B = p.b + bi * p.stride_b;
     float* __restrict__ C = p.c + bi * p.stride_c;
     const int64_t m0 = tm * BM, n0 = tn * BN;
+    // triangular output: a tile wholly outside the triangle has nothing to do (uniform per CTA)
+    if (p.tri == 1 && n0 > m0 + BM - 1) return;
+    if (p.tri == 2 && m0 > n0 + BN - 1) return;
 
     float acc[TM][TN];
 #pragma unroll
@@ -141,7 +145,9 @@ __device__ __forceinline__ void simt_gemm_tile(const SimtGemmArgs& p, int64_t tm
             const int64_t col = n0 + g * (BN / GN) + tx * 4;
             if (col >= p.n) continue;
             float* dst = C + row * p.ldc + col;
-            if (vec_ok && col + 3 < p.n)
+            // triangular output: 4 columns wholly inside -> vector path; straddling -> per element
+            const bool tri_all = p.tri == 0 || (p.tri == 1 ? col + 3 <= row : col >= row);
+            if (vec_ok && col + 3 < p.n && tri_all)
             {
                 float4 o;
                 o.x = p.alpha * acc[i][g * 4 + 0]; o.y = p.alpha * acc[i][g * 4 + 1];
@@ -163,7 +169,8 @@ __device__ __forceinline__ void simt_gemm_tile(const SimtGemmArgs& p, int64_t tm
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                 {
-                    if (col + j < p.n)
+                    const bool inside = p.tri == 0 || (p.tri == 1 ? col + j <= row : col + j >= row);
+                    if (col + j < p.n && inside)
                     {
                         float o = p.alpha * acc[i][g * 4 + j];
                         if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);

@@ -86,6 +86,7 @@ struct Params
     int64_t total_tiles;           // tiles_m * tiles_n * batch
     float alpha, beta;
     int32_t relu;                  // epilogue activation: max(alpha*acc + beta*C, 0)
+    int32_t tri;                   // 0: full C; 1: only row >= col is written (lower triangle); 2: only row <= col
     int* status;
     // work distribution
     int64_t dp_tiles;              // tiles [0, dp_tiles) are dealt whole, round-robin over the grid
@@ -125,6 +126,15 @@ __device__ __forceinline__ bool get_work_item(const Params& p, int32_t cta, int3
     if (q == p.sk_split - 1) { w.kind = 2; w.slot = t; }
     else { w.kind = 1; w.slot = q * p.sk_tiles + t; }
     return true;
+}
+
+// Triangular output (SYRK): true when tile (tm, tn) lies wholly outside the triangle that is
+// written, so that every role skips the work item.
+__device__ __forceinline__ bool tile_outside_triangle(int32_t tri, int32_t tm, int32_t tn)
+{
+    if (tri == 1) return (int64_t)tn * BN > (int64_t)tm * BM + BM - 1;
+    if (tri == 2) return (int64_t)tm * BM > (int64_t)tn * BN + BN - 1;
+    return false;
 }
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* ptr)
@@ -356,6 +366,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
             const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+            if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
             for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
             {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
@@ -396,8 +407,13 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t it = 0, tl = 0;
         bool ok = true;
         WorkItem w;
-        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx, ++tl)
+        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
+            {
+                const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+                if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
+            }
+            const uint32_t tl_now = tl++;
             for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
             {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
@@ -410,8 +426,8 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (okl && kb == w.kb0)
                     {
                         // both accumulator halves must have been drained by the previous tile's epilogue
-                        okl = mbar_wait_bounded(acc_empty0, (tl & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS) &&
-                              mbar_wait_bounded(acc_empty0 + 8, (tl & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS);
+                        okl = mbar_wait_bounded(acc_empty0, (tl_now & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS) &&
+                              mbar_wait_bounded(acc_empty0 + 8, (tl_now & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, WAIT_LIMIT_NS);
                     }
                     if (okl)
                     {
@@ -465,9 +481,11 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t tl = 0, published = 0, it = 0;
         bool ok = true;
         WorkItem w;
-        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx, ++tl)
+        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
             const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+            if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
+            const uint32_t tl_now = tl++;
             if (p.raw_mask)
             {
                 // converter duty: split the raw operand tiles of every stage of this run in place
@@ -504,7 +522,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 if (!ok) break;
             }
-            int okl = mbar_wait_bounded(acc_full, tl & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
+            int okl = mbar_wait_bounded(acc_full, tl_now & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
             if (okl && w.kind == 2)
             {
                 // owner of a cut tile: the earlier slices must have been published
@@ -563,7 +581,8 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         {
                             const int64_t grow = row_base + i * 4 + rsub;
                             old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (grow < p.m && gcol + 3 < p.n)
+                            const bool tri_all = p.tri == 0 || (p.tri == 1 ? gcol + 3 <= grow : gcol >= grow);
+                            if (grow < p.m && gcol + 3 < p.n && tri_all)
                                 old[i] = *reinterpret_cast<const float4*>(cb + grow * p.ldc + gcol);
                         }
                     }
@@ -619,7 +638,9 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                             const int64_t grow = row_base + i * 4 + rsub;
                             if (grow >= p.m || gcol >= p.n) continue;
                             float* dst = cb + grow * p.ldc + gcol;
-                            if (vec_ok && gcol + 3 < p.n)
+                            // triangular output: 4 columns wholly inside -> vector path; straddling -> per element
+                            const bool tri_all = p.tri == 0 || (p.tri == 1 ? gcol + 3 <= grow : gcol >= grow);
+                            if (vec_ok && gcol + 3 < p.n && tri_all)
                             {
                                 float4 o;
                                 o.x = p.alpha * a.x; o.y = p.alpha * a.y; o.z = p.alpha * a.z; o.w = p.alpha * a.w;
@@ -640,7 +661,8 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
                                 {
-                                    if (gcol + j < p.n)
+                                    const bool inside = p.tri == 0 || (p.tri == 1 ? gcol + j <= grow : gcol + j >= grow);
+                                    if (gcol + j < p.n && inside)
                                     {
                                         float o = p.alpha * av[j];
                                         if (has_beta) o = fmaf(p.beta, dst[j], o);
@@ -853,7 +875,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
                                      float alpha, float beta, int* status, int sm_count, cudaStream_t st,
                                      void* sk_area = nullptr, unsigned int sk_epoch = 0,
-                                     float* const* peer_c = nullptr, int n_peers = 0, bool relu = false)
+                                     float* const* peer_c = nullptr, int n_peers = 0, bool relu = false, int tri = 0)
 {
     // per-device attribute; cheap enough to set on every launch
     cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -874,7 +896,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.num_kb = (int32_t)num_kb;
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
-    p.alpha = alpha; p.beta = beta; p.status = status; p.relu = relu ? 1 : 0;
+    p.alpha = alpha; p.beta = beta; p.status = status; p.relu = relu ? 1 : 0; p.tri = tri;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
     p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split;
     p.sk_flags = static_cast<unsigned int*>(sk_area);

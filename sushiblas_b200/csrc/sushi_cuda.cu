@@ -214,6 +214,7 @@ struct SlabReuse
     float* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int n_peers = 0;           // fused all-gather: the GEMM epilogue also stores C to these addresses
     bool relu = false;         // epilogue activation
+    int tri = 0;               // triangular output (SYRK): 1 lower, 2 upper
 };
 
 int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int64_t n, int64_t k, float alpha,
@@ -223,7 +224,8 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
     SC_CUDA(ctx, cudaSetDevice(d.device));
     const bool relu = reuse && reuse->relu;
-    if (k == 0 || alpha == 0.0f)
+    const int tri = reuse ? reuse->tri : 0;
+    if ((k == 0 || alpha == 0.0f) && tri == 0)
     {
         if (beta == 1.0f && !relu) return SUSHI_CUDA_OK;
         const int64_t total = m * n * batch;
@@ -255,13 +257,18 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         // size can follow without moving it
         const int64_t a_rows = (reuse && reuse->max_rows > m) ? reuse->max_rows : m;
         const size_t bytes_a = fuse_a ? 0 : sushi::split_plane_bytes(a_rows, k, batch);
-        const size_t bytes_b = fuse_b ? 0 : sushi::split_plane_bytes(n, k, batch);
+        size_t bytes_b = fuse_b ? 0 : sushi::split_plane_bytes(n, k, batch);
+        if ((b == a) && (ldb == lda) && (sb == sa) && ((tb != 0) == (ta == 0)) && (m == n) && !(reuse && reuse->max_rows > m))
+            bytes_b = 0;           // shares A's planes (see below)
         int rc = SUSHI_CUDA_OK;
         if (bytes_a + bytes_b > 0 && (rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_a + bytes_b)) != SUSHI_CUDA_OK)
             return rc;
         float* planes_b = static_cast<float*>(d.workspace);
         float* planes_a = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b);
-        const bool split_b = !fuse_b && !(reuse && reuse->b_planes_ready);
+        // SYRK-shaped call (op(B)^T is op(A) itself): one set of planes serves both operands
+        const bool same_operand = (b == a) && (ldb == lda) && (sb == sa) && ((tb != 0) == (ta == 0)) && (m == n) &&
+                                  !(reuse && reuse->max_rows > m);
+        const bool split_b = !fuse_b && !same_operand && !(reuse && reuse->b_planes_ready);
         const int prepass_launches = (fuse_a ? 0 : 1) + (split_b ? 1 : 0);
         if ((rc = timing_mark(ctx, d, 0, prepass_launches)) != SUSHI_CUDA_OK) return rc;
         if (!fuse_a)
@@ -294,11 +301,12 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         }
         sushi::tc3x::OperandSource src_a, src_b;
         if (fuse_a) { src_a.raw = a; src_a.ld = lda; src_a.stride = sa; } else src_a.planes = planes_a;
-        if (fuse_b) { src_b.raw = b; src_b.ld = ldb; src_b.stride = sb; } else src_b.planes = planes_b;
+        if (fuse_b) { src_b.raw = b; src_b.ld = ldb; src_b.stride = sb; }
+        else src_b.planes = (same_operand && !fuse_a) ? planes_a : planes_b;
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,
                                                    d.status, d.sm_count, d.stream, sk_area, d.sk_epoch,
-                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, relu));
+                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, relu, tri));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
         ctx->launches += 1 + prepass_launches;
         return SUSHI_CUDA_OK;
@@ -307,7 +315,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     sushi::SimtGemmArgs g;
     g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
     g.stride_a = sa; g.stride_b = sb; g.stride_c = sc; g.tiles_m = 0; g.tiles_n = 0;
-    g.alpha = alpha; g.beta = beta; g.relu = relu ? 1 : 0;
+    g.alpha = alpha; g.beta = beta; g.relu = relu ? 1 : 0; g.tri = tri;
     int rc = timing_mark(ctx, d, 0, 0);
     if (rc == SUSHI_CUDA_OK) rc = timing_mark(ctx, d, 1, 0);
     if (rc != SUSHI_CUDA_OK) return rc;
@@ -705,7 +713,7 @@ extern "C" int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sush
         g.g.lda = q.lda; g.g.ldb = q.ldb; g.g.ldc = q.ldc;
         g.g.stride_a = q.stride_a; g.g.stride_b = q.stride_b; g.g.stride_c = q.stride_c;
         g.g.tiles_m = (q.m + 63) / 64; g.g.tiles_n = (q.n + 63) / 64;
-        g.g.alpha = q.alpha; g.g.beta = q.beta; g.g.relu = q.epilogue == SUSHI_EPILOGUE_RELU;
+        g.g.alpha = q.alpha; g.g.beta = q.beta; g.g.relu = q.epilogue == SUSHI_EPILOGUE_RELU; g.g.tri = 0;
         g.trans_a = q.trans_a != 0; g.trans_b = q.trans_b != 0;
         g.first_tile = tiles;
         tiles += g.g.tiles_m * g.g.tiles_n * q.batch;
@@ -734,6 +742,35 @@ extern "C" int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sush
         if (rc != SUSHI_CUDA_OK) return rc;
     }
     return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_ssyrk_strided_batched(sushi_cuda_ctx* ctx, int dev, int upper, int trans, int64_t n, int64_t k,
+                                                float alpha, const float* a, int64_t lda, int64_t stride_a, float beta,
+                                                float* c, int64_t ldc, int64_t stride_c, int64_t batch)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "ssyrk: bad context or device index");
+    // C <- alpha * op(A) * op(A)^T + beta * C is the GEMM with B = A and op(B) = op(A)^T
+    int rc = validate_gemm(ctx, n, n, k, a, lda, a, lda, c, ldc, trans, !trans, stride_a, stride_a, stride_c, batch);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    SlabReuse opts;
+    opts.tri = upper ? 2 : 1;
+    if (k == 0 || alpha == 0.0f)
+    {
+        // only beta * C on the triangle remains: run the FFMA kernel with k = 0 (it reads no operand)
+        opts.variant = SUSHI_GEMM_SIMT;
+        if (beta == 1.0f) return SUSHI_CUDA_OK;
+        return run_gemm(ctx, *d, trans, !trans, n, n, 0, 1.0f, c, lda > 0 ? lda : 1, stride_a, c, lda > 0 ? lda : 1, stride_a,
+                        beta, c, ldc, stride_c, batch, &opts);
+    }
+    return run_gemm(ctx, *d, trans, !trans, n, n, k, alpha, a, lda, stride_a, a, lda, stride_a, beta, c, ldc, stride_c,
+                    batch, &opts);
+}
+
+extern "C" int sushi_cuda_ssyrk(sushi_cuda_ctx* ctx, int dev, int upper, int trans, int64_t n, int64_t k, float alpha,
+                                const float* a, int64_t lda, float beta, float* c, int64_t ldc)
+{
+    return sushi_cuda_ssyrk_strided_batched(ctx, dev, upper, trans, n, k, alpha, a, lda, 0, beta, c, ldc, 0, 1);
 }
 
 extern "C" int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count)

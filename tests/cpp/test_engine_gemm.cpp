@@ -175,6 +175,58 @@ TEST_CASE(ChainedGemmsKeepOrder)
     verify_tensor(*cur, ref, 1e-4f);
 }
 
+TEST_CASE(SimpleSYRK)
+{
+    // tests/blas/level3/test_syrk.cpp:39-63
+    sb::Engine engine(runtime());
+    const int N = 3, K = 2;
+    auto A = engine.create_tensor({N, K});
+    auto C = engine.create_tensor({N, N});
+    fill_tensor(A, {1, 2, 3, 4, 5, 6});
+    fill_tensor(C, std::vector<float>(N * N, 0.0f));
+    engine.blas().syrk(A, C, false, false, 1.0f, 0.0f);
+    engine.execute().wait();
+    verify_tensor(C, {5, 0, 0, 11, 25, 0, 17, 39, 61});
+}
+
+TEST_CASE(SimpleSYRKColumnMajor)
+{
+    // tests/blas/level3/test_syrk.cpp:65-88
+    sb::Engine engine(runtime(), sb::Core::Layout::COLUMN_MAJOR);
+    const int N = 2, K = 3;
+    auto A = engine.create_tensor({K, N});
+    auto C = engine.create_tensor({N, N});
+    fill_tensor(A, {1, 2, 3, 4, 5, 6});
+    fill_tensor(C, std::vector<float>(N * N, 0.0f));
+    engine.blas().syrk(A, C, false, true, 1.0f, 0.0f);
+    engine.execute().wait();
+    verify_tensor(C, {14, 32, 0, 77});
+}
+
+TEST_CASE(SyrkLargeUpperKeepsTheOtherTriangle)
+{
+    sb::Engine engine(runtime());
+    const int n = 520, k = 300;                       // tensor-core path, ragged tiles
+    auto A = engine.create_tensor({n, k}), C = engine.create_tensor({n, n});
+    auto a = random_vec(size_t(n) * k, 51), c = random_vec(size_t(n) * n, 52);
+    fill_tensor(A, a); fill_tensor(C, c);
+    engine.blas().syrk(A, C, true, false, 2.0f, 0.5f);
+    engine.execute().wait();
+    const float* got = C.data_as<float>();
+    for (int i = 0; i < n; i += 3)
+        for (int j = 0; j < n; j += 5)
+        {
+            if (j < i) { EXPECT_EQ(got[size_t(i) * n + j], c[size_t(i) * n + j]); continue; }
+            double s = 0;
+            for (int p = 0; p < k; ++p) s += double(a[size_t(i) * k + p]) * double(a[size_t(j) * k + p]);
+            EXPECT_NEAR(got[size_t(i) * n + j], 2.0 * s + 0.5 * c[size_t(i) * n + j], 3e-4);
+        }
+    auto R = engine.create_tensor({4, 5});
+    EXPECT_THROWS(engine.blas().syrk(A, R), "square matrix");
+    auto S = engine.create_tensor({7, 7});
+    EXPECT_THROWS(engine.blas().syrk(A, S), "does not match C");
+}
+
 TEST_CASE(ReLUForward)
 {
     // tests/math/nonlinear/test_relu.cpp:38-47

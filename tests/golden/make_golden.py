@@ -55,6 +55,13 @@ def main():
     d["ref_colmajor2x2.b"] = np.array([5, 7, 6, 8], dtype=np.float32)
     d["ref_colmajor2x2.c_out"] = np.array([19, 43, 22, 50], dtype=np.float32)
 
+    # reference SYRK KATs (tests/blas/level3/test_syrk.cpp:39-103): row-major lower 3x3 (A 3x2 = 1..6)
+    # and column-major lower with transA (A stored K x N = 3 x 2, memory 1..6) -> {14, 32, 0, 77}
+    d["ref_syrk_lower3.a"] = np.arange(1, 7, dtype=np.float32)
+    d["ref_syrk_lower3.c_out"] = np.array([5, 0, 0, 11, 25, 0, 17, 39, 61], dtype=np.float32)
+    d["ref_syrk_colmajor_trans.a"] = np.arange(1, 7, dtype=np.float32)
+    d["ref_syrk_colmajor_trans.c_out"] = np.array([14, 32, 0, 77], dtype=np.float32)
+
     names = []
     specs = [
         ("nn_small", 0, 0, 5, 7, 3, 1, 0, 1, (0, 0, 0)),
@@ -75,7 +82,7 @@ def main():
         names.append(name)
     d["names"] = np.array(names)
     np.savez_compressed(os.path.join(HERE, "gemm_integer_kat.npz"), **d)
-    print("wrote", len(names) + 2, "cases")
+    print("wrote", len(names) + 4, "cases")
 
 
 if __name__ == "__main__":

@@ -370,6 +370,66 @@ def test_relu_epilogue_and_standalone_relu(ctx, variant):
         ctx.sgemm_strided_batched_ex(0, 0, 4, 4, 4, 1.0, x, 4, 0, x, 4, 0, 0.0, x, 4, 0, 1, 7)   # unknown epilogue
 
 
+# ------------------------------------------------------------------ SYRK on the GEMM main loop
+def test_reference_kat_syrk(ctx):
+    g = np.load(GOLDEN)
+    # tests/blas/level3/test_syrk.cpp:39-63: row-major, lower, A 3x2
+    c = torch.zeros(9, device="cuda")
+    ctx.ssyrk(False, False, 3, 2, 1.0, dev(g["ref_syrk_lower3.a"]), 2, 0.0, c, 3)
+    ctx.sync()
+    assert np.array_equal(c.cpu().numpy(), g["ref_syrk_lower3.c_out"])
+    # tests/blas/level3/test_syrk.cpp:65-88: column-major lower with transA == row-major upper without
+    c = torch.zeros(4, device="cuda")
+    ctx.ssyrk(True, False, 2, 3, 1.0, dev(g["ref_syrk_colmajor_trans.a"]), 3, 0.0, c, 2)
+    ctx.sync()
+    assert np.array_equal(c.cpu().numpy(), g["ref_syrk_colmajor_trans.c_out"])
+
+
+@pytest.mark.parametrize("variant", [SIMT, TC3X])
+def test_syrk_matches_oracle_and_leaves_the_other_triangle(ctx, variant):
+    rng = np.random.default_rng(23)
+    ctx.set_gemm_variant(variant)
+    for (n, k, batch, pad) in [(7, 5, 1, 0), (65, 33, 2, 3), (300, 260, 1, 4), (512, 384, 3, 0), (1024, 200, 1, 0),
+                                (257, 1000, 1, 1)]:
+        for upper in (0, 1):
+            for trans in (0, 1):
+                alpha, beta = float(rng.choice([1.0, 1.5])), float(rng.choice([0.0, 0.5, 1.0]))
+                ar, ac = (k, n) if trans else (n, k)
+                lda, ldc = ac + pad, n + pad
+                sa, sc = ar * lda, n * ldc
+                a = og.uniform_pm1(int(rng.integers(1 << 30)), batch * sa)
+                c0 = og.uniform_pm1(int(rng.integers(1 << 30)), batch * sc)
+                c_in = c0.copy()
+                if beta == 0.0:
+                    # the written triangle is not read when beta == 0: poison it
+                    v = og._view(c_in, n, ldc, ldc, sc, batch).copy()
+                    i, j = np.indices((n, n))
+                    tri = (j >= i) if upper else (j <= i)
+                    v[:, :, :n][np.broadcast_to(tri, (batch, n, n))] = np.nan
+                    c_in = v.reshape(batch, n * ldc)[:, :sc].ravel().copy()
+                dc = dev(c_in)
+                ctx.ssyrk(upper, trans, n, k, alpha, dev(a), lda, beta, dc, ldc, sa, sc, batch)
+                ctx.sync()
+                out = dc.cpu().numpy()
+                ref, absaa, mask = og.syrk_f64_np(upper, trans, n, k, alpha, a, lda, sa, beta, c0, ldc, sc, batch)
+                got = og._view(out, n, n, ldc, sc, batch)
+                cin = og._view(c0, n, n, ldc, sc, batch)
+                r, _ = og.tolerance_ratio(np.where(mask[None], got, 0.0), np.where(mask[None], ref, 0.0), absaa, k,
+                                          beta=beta, c_in=np.where(mask[None], cin, 0.0), budget=BUDGET)
+                assert r <= 1.0, (variant, n, k, batch, upper, trans, alpha, beta, r)
+                # everything outside the triangle (other triangle and row padding) keeps its bits
+                keep = np.ones(out.shape, dtype=bool)
+                idx = (np.arange(batch)[:, None, None] * sc + np.arange(n)[None, :, None] * ldc + np.arange(n)[None, None, :])
+                keep[idx[np.broadcast_to(mask, (batch, n, n))]] = False
+                assert np.array_equal(out[keep], c_in[keep]), (variant, n, k, upper, trans)
+    ctx.set_gemm_variant(AUTO)
+    # k == 0: only beta * C on the triangle
+    c = torch.ones(16, device="cuda")
+    ctx.ssyrk(False, False, 4, 0, 1.0, c, 1, 0.5, c, 4)
+    ctx.sync()
+    assert c.view(4, 4).cpu().numpy().tolist() == [[0.5, 1, 1, 1], [0.5, 0.5, 1, 1], [0.5, 0.5, 0.5, 1], [0.5] * 4]
+
+
 # ------------------------------------------------------------------ grouped launch of small GEMMs
 def test_grouped_small_gemms(ctx):
     """Independent small problems of mixed shapes, transposes, alpha/beta and epilogues in one

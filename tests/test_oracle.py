@@ -31,6 +31,34 @@ def test_reference_kat_column_major(golden):
     assert np.array_equal(out.astype(np.float32), golden["ref_colmajor2x2.c_out"])
 
 
+def test_reference_kat_syrk(golden):
+    # tests/blas/level3/test_syrk.cpp:39-63 -- row-major, lower, no transpose, alpha=1, beta=0
+    out, _ = og.syrk_f64_c(False, False, 3, 2, 1.0, golden["ref_syrk_lower3.a"], 2, 0, 0.0, np.zeros(9, np.float32), 3, 0, 1)
+    assert np.array_equal(out.astype(np.float32), golden["ref_syrk_lower3.c_out"])
+    # tests/blas/level3/test_syrk.cpp:65-88 -- column-major engine, A created as {K, N} = {3, 2}, transA = true
+    # (column-major: lda = A.shape[rank-2] = 3, syrk.cpp:110)
+    out, _ = og.syrk_f64_c(False, True, 2, 3, 1.0, golden["ref_syrk_colmajor_trans.a"], 3, 0, 0.0, np.zeros(4, np.float32),
+                           2, 0, 1, layout=og.COLUMN_MAJOR)
+    assert np.array_equal(out.astype(np.float32), golden["ref_syrk_colmajor_trans.c_out"])
+    # column-major (uplo, trans) is row-major (other uplo, other trans) on the same memory
+    rng = np.random.default_rng(4)
+    n, k = 5, 7
+    for upper in (0, 1):
+        for trans in (0, 1):
+            a = rng.standard_normal(n * k).astype(np.float32)
+            c = rng.standard_normal(n * n).astype(np.float32)
+            lda_col = k if trans else n
+            col, _ = og.syrk_f64_c(upper, trans, n, k, 1.5, a, lda_col, 0, 0.5, c, n, 0, 1, layout=og.COLUMN_MAJOR)
+            row, _ = og.syrk_f64_c(not upper, not trans, n, k, 1.5, a, lda_col, 0, 0.5, c, n, 0, 1, layout=og.ROW_MAJOR)
+            np.testing.assert_array_equal(col, row)
+    # numpy twin agrees with the C restatement
+    a = rng.uniform(-1, 1, (2, 9, 6)).astype(np.float32); c = rng.uniform(-1, 1, (2, 9, 9)).astype(np.float32)
+    r1, ab1 = og.syrk_f64_c(True, False, 9, 6, 2.0, a, 6, 54, -1.0, c, 9, 81, 2)
+    r2, ab2, _ = og.syrk_f64_np(True, False, 9, 6, 2.0, a, 6, 54, -1.0, c, 9, 81, 2)
+    np.testing.assert_allclose(r1.reshape(2, 9, 9), r2, rtol=1e-13, atol=1e-13)
+    np.testing.assert_allclose(ab1.reshape(2, 9, 9), ab2, rtol=1e-13, atol=1e-13)
+
+
 def test_column_major_equals_swapped_row_major():
     # the identity the C++ front-end uses to serve gemm.cpp:66-78 with a row-major kernel
     rng = np.random.default_rng(3)
