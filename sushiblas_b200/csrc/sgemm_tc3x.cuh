@@ -46,11 +46,13 @@
 // drained with bounded waits, TMEM is freed and the kernel returns.
 #pragma once
 #include <cstdint>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace sushi {
 namespace tc3x {
+
 
 constexpr int BM = 256, BN = 256, BK = 16;
 constexpr int STAGES = 3;
@@ -86,6 +88,7 @@ struct Params
     int64_t total_tiles;           // tiles_m * tiles_n * batch
     float alpha, beta;
     int32_t relu;                  // epilogue activation: max(alpha*acc + beta*C, 0)
+    int32_t lean_epilogue;         // 1: interior work items use the check-free epilogue path
     int32_t tri;                   // 0: full C; 1: only row >= col is written (lower triangle); 2: only row <= col
     int* status;
     // work distribution
@@ -303,6 +306,84 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t t, int32_t tiles_m, int
     tc.tm = first_m + (r % group) % gm;
     tc.tn = (r % group) / gm;
     return tc;
+}
+
+// Epilogue fast path for one warp's 32 x 256 region of a tile that lies wholly inside its
+// destination, with 16-byte aligned rows and no triangle mask: no per-element checks, addresses by
+// pointer increments, and the TMEM load of chunk c+1 issued as soon as chunk c has been written
+// to the staging buffer, so that it is in flight while chunk c is stored.
+// `dst` points at (first row of the warp + lane/8, first column of the tile + 4*(lane%8)) of the
+// destination (C, or the slot of a published K slice with ldc = BN, alpha = 1).
+// `contrib` (owner of a cut tile): the same position inside the first published slot; n_contrib
+// slots, contrib_stride floats apart, are added before alpha/beta.
+template <bool HAS_BETA, bool RELU>
+__device__ __forceinline__ void epilogue_fast(uint32_t taddr0, float4* stg, float* __restrict__ dst, int64_t ldc,
+                                              float alpha, float beta, int lane,
+                                              const float* contrib = nullptr, int n_contrib = 0, size_t contrib_stride = 0)
+{
+    const int rsub = lane >> 3, c4 = lane & 7;
+    const int64_t row_step = 4 * ldc;
+    uint32_t v[32];
+    tcgen05_ld_32x32b_x32(taddr0, v);
+#pragma unroll 1
+    for (int chunk = 0; chunk < BN / 32; ++chunk)
+    {
+        float4 old[8];
+        if (HAS_BETA)
+        {
+            const float* src = dst + chunk * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) old[i] = *reinterpret_cast<const float4*>(src + i * row_step);
+        }
+        tcgen05_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            float4 x;
+            x.x = __uint_as_float(v[4 * j + 0]); x.y = __uint_as_float(v[4 * j + 1]);
+            x.z = __uint_as_float(v[4 * j + 2]); x.w = __uint_as_float(v[4 * j + 3]);
+            stg[lane * 8 + (j ^ (lane & 7))] = x;
+        }
+        if (chunk + 1 < BN / 32) tcgen05_ld_32x32b_x32(taddr0 + (chunk + 1) * 32, v);
+        __syncwarp();
+        float4 acc4[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+        {
+            const int r = i * 4 + rsub;
+            acc4[i] = stg[r * 8 + (c4 ^ (r & 7))];
+        }
+        for (int c = 0; c < n_contrib; ++c)
+        {
+            const float* src = contrib + c * contrib_stride + chunk * 32;
+            float4 t4[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t4[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * 4 * BN));
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+            {
+                acc4[i].x += t4[i].x; acc4[i].y += t4[i].y; acc4[i].z += t4[i].z; acc4[i].w += t4[i].w;
+            }
+        }
+        float* out = dst + chunk * 32;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+        {
+            float4 o;
+            o.x = alpha * acc4[i].x; o.y = alpha * acc4[i].y; o.z = alpha * acc4[i].z; o.w = alpha * acc4[i].w;
+            if (HAS_BETA)
+            {
+                o.x = fmaf(beta, old[i].x, o.x); o.y = fmaf(beta, old[i].y, o.y);
+                o.z = fmaf(beta, old[i].z, o.z); o.w = fmaf(beta, old[i].w, o.w);
+            }
+            if (RELU)
+            {
+                o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+            }
+            *reinterpret_cast<float4*>(out + i * row_step) = o;
+        }
+        __syncwarp();
+    }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -561,7 +642,33 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             float* my_slot = partial ? p.sk_partials + (size_t)w.slot * SK_SLOT_FLOATS : nullptr;
             const int slot_row0 = h * 128 + q * 32;
 
-            if (partial || row_base < p.m)
+            // work items that lie wholly inside their destination take the lean path
+            const bool inside_c = p.lean_epilogue && vec_ok && p.tri == 0 && row_base + 32 <= p.m && col_base + BN <= p.n;
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256);
+            const size_t slot_pos = (size_t)(slot_row0 + rsub) * BN + c4 * 4;       // this lane inside a 256 x 256 slot
+            if (partial && p.lean_epilogue)
+            {
+                // raw accumulators into this slice's slot (alpha = 1, no beta, dense 256-wide rows)
+                epilogue_fast<false, false>(taddr0, stg, my_slot + slot_pos, BN, 1.0f, 0.0f, lane);
+            }
+            else if (inside_c)
+            {
+                float* dst = cb + (row_base + rsub) * p.ldc + col_base + c4 * 4;
+                const float* contrib = w.kind == 2 ? p.sk_partials + (size_t)w.slot * SK_SLOT_FLOATS + slot_pos : nullptr;
+                const int n_contrib = w.kind == 2 ? p.sk_split - 1 : 0;
+                const size_t cstride = (size_t)p.sk_tiles * SK_SLOT_FLOATS;
+                if (has_beta)
+                {
+                    if (p.relu) epilogue_fast<true, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    else epilogue_fast<true, false>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                }
+                else
+                {
+                    if (p.relu) epilogue_fast<false, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    else epilogue_fast<false, false>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                }
+            }
+            else if (partial || row_base < p.m)
             {
                 for (int chunk = 0; chunk < BN / 32; ++chunk)
                 {
@@ -831,6 +938,13 @@ inline void tile_counts(int64_t m, int64_t n, int64_t k, int64_t batch, int64_t*
     *num_kb = (k + BK - 1) / BK;
 }
 
+// Development switch: SUSHI_LEAN_EPILOGUE=0 routes every work item through the general epilogue.
+inline bool lean_epilogue_enabled()
+{
+    static const bool on = [] { const char* e = getenv("SUSHI_LEAN_EPILOGUE"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 // planes_a / planes_b as written by launch_split_tf32 for op(A) (rows = m) and op(B)^T (rows = n).
 // Tensor map over a user operand whose k index is contiguous: element (row, kk) at
 // base[bi*stride + row*ld + kk]; box = {16 k, 256 rows, 1}; outside rows/k reads as zero.
@@ -897,6 +1011,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
     p.alpha = alpha; p.beta = beta; p.status = status; p.relu = relu ? 1 : 0; p.tri = tri;
+    p.lean_epilogue = lean_epilogue_enabled() ? 1 : 0;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
     p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split;
     p.sk_flags = static_cast<unsigned int*>(sk_area);
