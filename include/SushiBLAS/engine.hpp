@@ -266,6 +266,85 @@ namespace SushiBLAS
         return SushiRuntime::Execution::Event();
     }
 
+    // ---------------------------------------------------------------- Level3::trsm
+    inline SushiRuntime::Execution::Event Level3::trsm(const Tensor& A, Tensor& B, bool left_side, bool upper, bool transA,
+                                                       bool unit_diag, float alpha)
+    {
+        using namespace SushiRuntime::Graph::Literals;
+        SB_THROW_IF(A.rank < 2 || B.rank < 2, "TRSM requires at least 2D tensors.");
+        SB_THROW_IF(A.dtype != B.dtype, "Data type mismatch in TRSM operation.");
+        SB_THROW_IF(A.dtype != Core::DataType::FLOAT32,
+                    "Unsupported data type for TRSM operation (the CUDA backend serves FLOAT32 only).");
+        const int32_t ra = A.rank, rb = B.rank;
+        const int64_t m = B.shape[rb - 2], n = B.shape[rb - 1];
+        const int64_t a_rows = A.shape[ra - 2], a_cols = A.shape[ra - 1];
+        SB_THROW_IF(a_rows != a_cols, "TRSM requires matrix A to be square.");
+        if (left_side) SB_THROW_IF(a_rows != m, "Left-sided TRSM: dimensions of A must match rows of B.");
+        else SB_THROW_IF(a_rows != n, "Right-sided TRSM: dimensions of A must match cols of B.");
+        int64_t batch = 1;
+        for (int i = 0; i < rb - 2; ++i) batch *= B.shape[i];
+        const bool row = A.layout == Core::Layout::ROW_MAJOR;
+        const int64_t lda = row ? A.shape[ra - 1] : A.shape[ra - 2];
+        const int64_t ldb = (B.layout == Core::Layout::ROW_MAJOR) ? B.shape[rb - 1] : B.shape[rb - 2];
+        int64_t stride_a = 0, stride_b = 0;
+        if (batch > 1)
+        {
+            SB_THROW_IF(ra < 3, "Batched TRSM requires A of rank >= 3 (got {}).", ra);
+            stride_a = A.strides[ra - 3];
+            stride_b = B.strides[rb - 3];
+        }
+        // A column-major solve is the row-major solve of the transposed equation: the memory of a
+        // column-major B (m x n) is a row-major n x m matrix, A's memory is the other triangle, and
+        // op(A) moves to the other side:  op(A) X = aB  <=>  X^T op(A)^T = aB^T.
+        const bool rm_left = row ? left_side : !left_side;
+        const bool rm_upper = row ? upper : !upper;
+        const int64_t rm_m = row ? m : n, rm_n = row ? n : m;
+        const int64_t dim = left_side ? m : n;
+
+        struct Operand { SushiRuntime::sushi_ptr<Storage> storage; float* ptr; int64_t extent; bool host; };
+        auto describe = [](const Tensor& t, int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t nb) {
+            Operand o{t.storage, t.data_as<float>(), detail::operand_extent(rows, cols, ld, stride, nb), false};
+            o.host = t.storage->host_resident();
+            const std::size_t need = (static_cast<std::size_t>(t.storage_offset) + static_cast<std::size_t>(o.extent)) * sizeof(float);
+            SB_THROW_IF(need > t.storage->size_bytes, "TRSM operand does not fit its storage (needs {} bytes, has {}).", need,
+                        t.storage->size_bytes);
+            return o;
+        };
+        Operand oa = describe(A, dim, dim, lda, stride_a, batch);
+        Operand ob = describe(B, rm_m, rm_n, ldb, stride_b, batch);
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = "blas.lvl3.trsm";
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = "blas.lvl3.trsm"_op;
+        meta.set_param(0, alpha); meta.set_param(1, left_side); meta.set_param(2, upper); meta.set_param(3, transA);
+        meta.set_param(4, unit_diag);
+        engine_.get_graph().add_task(meta, {A.storage->data_ptr}, {B.storage->data_ptr},
+            [=](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            {
+                sushi_cuda_ctx* ctx = rt.native_handle();
+                auto on_device = [ctx](const Operand& o, float** out) -> int
+                {
+                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
+                    if (!base) return SUSHI_CUDA_ERR_OOM;
+                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
+                    if (o.host && o.extent > 0)
+                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
+                    return SUSHI_CUDA_OK;
+                };
+                float *da = nullptr, *db = nullptr;
+                int rc2 = on_device(oa, &da);
+                if (rc2 == SUSHI_CUDA_OK) rc2 = on_device(ob, &db);
+                if (rc2 != SUSHI_CUDA_OK) return rc2;
+                rc2 = sushi_cuda_strsm_strided_batched(ctx, 0, rm_left, rm_upper, transA, unit_diag, rm_m, rm_n, alpha, da, lda,
+                                                       stride_a, db, ldb, stride_b, batch);
+                if (rc2 == SUSHI_CUDA_OK && ob.host && ob.extent > 0)
+                    rc2 = sushi_cuda_memcpy_d2h(ctx, 0, ob.ptr, db, static_cast<std::size_t>(ob.extent) * sizeof(float));
+                return rc2;
+            });
+        return SushiRuntime::Execution::Event();
+    }
+
     // ---------------------------------------------------------------- Level3::gemm_row_sharded
     inline SushiRuntime::Execution::Event Level3::gemm_row_sharded(const Tensor& A_local, const Tensor& B, Tensor& C_full,
                                                                    bool transA, bool transB, float alpha, float beta)

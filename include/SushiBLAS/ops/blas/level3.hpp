@@ -116,6 +116,16 @@ namespace SushiBLAS
             inline SushiRuntime::Execution::Event syrk(const Tensor& A, Tensor& C, bool upper = false, bool transA = false,
                                                        float alpha = 1.0f, float beta = 0.0f);
 
+            /// Triangular solve with multiple right-hand sides, X overwriting B: op(A)*X = alpha*B
+            /// (left_side) or X*op(A) = alpha*B (reference declaration level3.hpp trsm, definition
+            /// src/ops/blas/level3/trsm.cpp:85-202).  m and n come from B, A must be square and match
+            /// m (left) or n (right); leading dimensions from the shapes, batch count from B, batch
+            /// strides from strides[rank-3]; A's layout selects row- or column-major for both tensors
+            /// (trsm.cpp:129).  FLOAT32 only.  Throws std::runtime_error on rank < 2, dtype mismatch,
+            /// a non-square A or A not matching B.
+            inline SushiRuntime::Execution::Event trsm(const Tensor& A, Tensor& B, bool left_side = true, bool upper = false,
+                                                       bool transA = false, bool unit_diag = false, float alpha = 1.0f);
+
             /// Multi-GPU GEMM, one process per GPU (no counterpart in the reference).  The global
             /// problem is C (m x n, the shape of C_full) = alpha*op(A)*op(B) + beta*C with A cut into
             /// row blocks of op(A): this rank passes its block A_local (rows

@@ -157,6 +157,24 @@ SUSHI_CUDA_API int sushi_cuda_ssyrk_strided_batched(sushi_cuda_ctx* ctx, int dev
                                                     const float* a, int64_t lda, int64_t stride_a, float beta,
                                                     float* c, int64_t ldc, int64_t stride_c, int64_t batch);
 
+/* Triangular solve with multiple right-hand sides, row-major; X overwrites B (m x n):
+ *     left != 0:  op(A) * X = alpha * B,  A is m x m        left == 0:  X * op(A) = alpha * B,  A is n x n
+ * A is upper (upper != 0) or lower triangular; only that triangle is read, and its diagonal is
+ * taken as 1 when unit_diag != 0.  Replaces oneapi::mkl::blas::row_major::trsm / trsm_batch (call
+ * sites src/ops/blas/level3/trsm.cpp:61-79).  Recursive blocked substitution: ranges of 256-wide
+ * blocks of the triangular dimension are halved, each halving costing one GEMM update on the
+ * regular GEMM kernels, and single blocks are applied through their explicit inverses (a small
+ * substitution kernel plus two batched GEMMs), so large solves run on the tensor cores.
+ * Accuracy is that of inverse-based blocked solvers: backward stable for well-conditioned diagonal
+ * blocks.                                                                                       */
+SUSHI_CUDA_API int sushi_cuda_strsm(sushi_cuda_ctx* ctx, int dev, int left, int upper, int trans, int unit_diag,
+                                    int64_t m, int64_t n, float alpha, const float* a, int64_t lda,
+                                    float* b, int64_t ldb);
+SUSHI_CUDA_API int sushi_cuda_strsm_strided_batched(sushi_cuda_ctx* ctx, int dev, int left, int upper, int trans,
+                                                    int unit_diag, int64_t m, int64_t n, float alpha,
+                                                    const float* a, int64_t lda, int64_t stride_a,
+                                                    float* b, int64_t ldb, int64_t stride_b, int64_t batch);
+
 /* Many independent GEMMs in one call (no counterpart call in the reference; it is what its
  * scheduler stress tests submit per execute(): 5000 GEMMs of 32^3 and 3000 of 8^3,
  * tests/runtime/test_dependency_stress.cpp:17-45,67-83).  No output of one problem may overlap

@@ -233,3 +233,70 @@ int oracle_syrk_f64acc(int layout_row, int upper, int trans, int64_t n, int64_t 
     }
     return 0;
 }
+
+/*
+ * oracle_trsm_f64: triangular solve with multiple right-hand sides, fp32 inputs, fp64 substitution.
+ *
+ *      left != 0:  op(A) * X = alpha * B  (A is m x m)       left == 0:  X * op(A) = alpha * B  (A is n x n)
+ *
+ * Restates what the reference forwards to oneapi::mkl::blas::{row,column}_major::trsm[_batch]
+ * (call sites src/ops/blas/level3/trsm.cpp:61-79) after deriving m, n from B, lda / ldb from the
+ * shapes and the batch strides from the tensors (trsm.cpp:85-135).  Only the `upper` or lower
+ * triangle of A is read; with unit_diag its diagonal is taken as 1.  x_out64 is indexed like B.
+ * Pinned by the reference's own known answers tests/blas/level3/test_trsm.cpp (row-major lower
+ * left-side case and column-major upper left-side case).
+ */
+int oracle_trsm_f64(int layout_row, int left, int upper, int trans, int unit_diag, int64_t m, int64_t n,
+                    float alpha, const float* a, int64_t lda, int64_t stride_a,
+                    const float* b, int64_t ldb, int64_t stride_b, int64_t batch, double* x_out64)
+{
+    if (m < 0 || n < 0 || batch < 0 || !x_out64) return -1;
+    const int64_t dim = left ? m : n;           /* order of A */
+    const int64_t nrhs = left ? n : m;          /* independent systems */
+    /* op(A) is lower triangular when exactly one of (upper, trans) is clear and the other ... */
+    const int eff_lower = ((upper != 0) == (trans != 0));
+    double* t = (double*)malloc(sizeof(double) * (size_t)(dim > 0 ? dim : 1) * (size_t)(dim > 0 ? dim : 1));
+    double* x = (double*)malloc(sizeof(double) * (size_t)(dim > 0 ? dim : 1));
+    if (!t || !x) { free(t); free(x); return -2; }
+    for (int64_t bi = 0; bi < batch; ++bi)
+    {
+        const float* ab = a + bi * stride_a;
+        /* dense T = op(A) restricted to the referenced triangle */
+        for (int64_t r = 0; r < dim; ++r)
+            for (int64_t c = 0; c < dim; ++c)
+            {
+                int in_tri = eff_lower ? (c <= r) : (c >= r);
+                double v = 0.0;
+                if (r == c && unit_diag) v = 1.0;
+                else if (in_tri) v = (double)ab[op_index(layout_row, trans, r, c, lda)];
+                t[r * dim + c] = v;
+            }
+        for (int64_t s = 0; s < nrhs; ++s)
+        {
+            /* left:  T x = alpha b_col(s);   right:  x^T T = alpha b_row(s)  <=>  T^T x = alpha b_row(s)^T */
+            #define B_IDX(p) (bi * stride_b + (left ? (layout_row ? (p) * ldb + s : s * ldb + (p)) \
+                                                    : (layout_row ? s * ldb + (p) : (p) * ldb + s)))
+            #define T_AT(r, c) (left ? t[(r) * dim + (c)] : t[(c) * dim + (r)])
+            const int lower_system = left ? eff_lower : !eff_lower;
+            if (lower_system)
+                for (int64_t i = 0; i < dim; ++i)
+                {
+                    double acc = (double)alpha * (double)b[B_IDX(i)];
+                    for (int64_t k = 0; k < i; ++k) acc -= T_AT(i, k) * x[k];
+                    x[i] = acc / T_AT(i, i);
+                }
+            else
+                for (int64_t i = dim - 1; i >= 0; --i)
+                {
+                    double acc = (double)alpha * (double)b[B_IDX(i)];
+                    for (int64_t k = i + 1; k < dim; ++k) acc -= T_AT(i, k) * x[k];
+                    x[i] = acc / T_AT(i, i);
+                }
+            for (int64_t i = 0; i < dim; ++i) x_out64[B_IDX(i)] = x[i];
+            #undef B_IDX
+            #undef T_AT
+        }
+    }
+    free(t); free(x);
+    return 0;
+}

@@ -61,6 +61,8 @@ def _lib():
         lib.oracle_syrk_f64acc.restype = ctypes.c_int
         lib.oracle_syrk_f64acc.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, i64, i64, f32, p, i64, i64, f32,
                                            p, i64, i64, i64, p, p]
+        lib.oracle_trsm_f64.restype = ctypes.c_int
+        lib.oracle_trsm_f64.argtypes = [ctypes.c_int] * 5 + [i64, i64, f32, p, i64, i64, p, i64, i64, i64, p]
         lib.oracle_check_tolerance.restype = dbl
         lib.oracle_check_tolerance.argtypes = [i64, i64, i64, i64, f32, dbl, p, p, p, p,
                                                i64, i64, ctypes.POINTER(dbl)]
@@ -165,6 +167,59 @@ def syrk_f64_np(upper, trans, n, k, alpha, a, lda, stride_a, beta, c_in, ldc, st
     i, j = np.indices((n, n))
     mask = (j >= i) if upper else (j <= i)
     return np.where(mask[None], full, cin), np.where(mask[None], absab, 0.0), mask
+
+
+def trsm_f64_c(left, upper, trans, unit_diag, m, n, alpha, a, lda, stride_a, b, ldb, stride_b, batch, layout=ROW_MAJOR):
+    """fp64 substitution through the C restatement (trsm.cpp:85-135 semantics).  Returns X as a
+    float64 array indexed like B."""
+    a = np.ascontiguousarray(a, dtype=np.float32).ravel()
+    b32 = np.ascontiguousarray(b, dtype=np.float32).ravel()
+    out = b32.astype(np.float64)
+    rc = _lib().oracle_trsm_f64(1 if layout == ROW_MAJOR else 0, int(left), int(upper), int(trans), int(unit_diag), m, n,
+                                alpha, _ptr(a), lda, stride_a, _ptr(b32), ldb, stride_b, batch, _ptr(out))
+    if rc != 0:
+        raise ValueError("oracle_trsm_f64 rejected its arguments")
+    return out
+
+
+def trsm_f64_np(left, upper, trans, unit_diag, m, n, alpha, a, lda, stride_a, b, ldb, stride_b, batch):
+    """numpy / LAPACK twin for row-major storage and larger sizes: float64 solve_triangular on the
+    referenced triangle.  Returns dense (batch, m, n) float64 X and the dense op(A) used."""
+    from scipy.linalg import solve_triangular
+    dim = m if left else n
+    a32 = np.asarray(a, dtype=np.float32).ravel()
+    b32 = np.asarray(b, dtype=np.float32).ravel()
+    av = _view(a32, dim, dim, lda, stride_a, batch).astype(np.float64)
+    bv = _view(b32, m, n, ldb, stride_b, batch).astype(np.float64)
+    xs, ts = [], []
+    for i in range(batch):
+        tri = np.triu(av[i]) if upper else np.tril(av[i])
+        if unit_diag:
+            np.fill_diagonal(tri, 1.0)
+        t = tri.T if trans else tri
+        lower = (bool(upper) == bool(trans))
+        if left:
+            x = solve_triangular(t, alpha * bv[i], lower=lower)
+        else:
+            x = solve_triangular(t.T, alpha * bv[i].T, lower=not lower).T
+        xs.append(x)
+        ts.append(t)
+    return np.stack(xs), np.stack(ts)
+
+
+def trsm_residual_ratio(left, t, x, alpha, b, dim):
+    """Componentwise backward-error ratio of a computed solve against the budget
+    8 * dim * 2^-24 * (|op(A)| |X| + |alpha B|): <= 1 passes."""
+    x = np.asarray(x, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    if left:
+        r = t @ x - alpha * b
+        scale = np.abs(t) @ np.abs(x) + np.abs(alpha * b)
+    else:
+        r = x @ t - alpha * b
+        scale = np.abs(x) @ np.abs(t) + np.abs(alpha * b)
+    bound = 8.0 * max(dim, 1) * 2.0 ** -24 * scale + 1e-37
+    return float(np.max(np.abs(r) / bound)) if r.size else 0.0
 
 
 def gemm_f32_c(trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,

@@ -63,6 +63,9 @@ SIGNATURES = {
     "sushi_cuda_ssyrk": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "sushi_cuda_ssyrk_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _i64, _f32,
                                                 _vp, _i64, _i64, _i64]),
+    "sushi_cuda_strsm": (_int, [_vp, _int, _int, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _vp, _i64]),
+    "sushi_cuda_strsm_strided_batched": (_int, [_vp, _int, _int, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _i64,
+                                                _vp, _i64, _i64, _i64]),
     "sushi_cuda_sgemm_grouped": (_int, [_vp, _int, ctypes.POINTER(GemmDesc), _i64]),
     "sushi_cuda_sgemm_strided_batched_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                      _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64]),
@@ -273,6 +276,12 @@ class SushiCuda:
     def ssyrk(self, upper, trans, n, k, alpha, a, lda, beta, c, ldc, stride_a=0, stride_c=0, batch=1, dev: int = 0):
         self._check(self.lib.sushi_cuda_ssyrk_strided_batched(self._ctx, dev, int(upper), int(trans), n, k, alpha,
                                                               _addr(a), lda, stride_a, beta, _addr(c), ldc, stride_c, batch))
+
+    def strsm(self, left, upper, trans, unit_diag, m, n, alpha, a, lda, b, ldb, stride_a=0, stride_b=0, batch=1,
+              dev: int = 0):
+        self._check(self.lib.sushi_cuda_strsm_strided_batched(self._ctx, dev, int(left), int(upper), int(trans),
+                                                              int(unit_diag), m, n, alpha, _addr(a), lda, stride_a,
+                                                              _addr(b), ldb, stride_b, batch))
 
     def sgemm_grouped(self, problems, dev: int = 0):
         """problems: iterable of dicts with the fields of sushi_cuda_gemm_desc (pointers may be tensors)."""

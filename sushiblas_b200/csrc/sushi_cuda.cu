@@ -21,6 +21,7 @@
 #include "sgemm_simt.cuh"
 #include "split_tf32.cuh"
 #include "sgemm_tc3x.cuh"
+#include "trsm_blocks.cuh"
 
 namespace {
 
@@ -39,6 +40,8 @@ struct DeviceState
     // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t pipe_events[10] = {};
+    void* trsm_buf = nullptr;             // TRSM: inverted diagonal blocks + one block row/column of temporaries
+    size_t trsm_bytes = 0;
     void* group_buf = nullptr;            // device copy of the grouped-launch problem list
     size_t group_bytes = 0;
     void* sk_area = nullptr;              // split-K exchange area (epoch flags + slots), flags zeroed at allocation
@@ -469,6 +472,7 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         if (d.workspace) cudaFree(d.workspace);
         if (d.sk_area) cudaFree(d.sk_area);
         if (d.group_buf) cudaFree(d.group_buf);
+        if (d.trsm_buf) cudaFree(d.trsm_buf);
         for (void* s : d.stage) if (s) cudaFree(s);
         if (d.status) cudaFree(d.status);
         if (d.status_host) cudaFreeHost(d.status_host);
@@ -771,6 +775,170 @@ extern "C" int sushi_cuda_ssyrk(sushi_cuda_ctx* ctx, int dev, int upper, int tra
                                 const float* a, int64_t lda, float beta, float* c, int64_t ldc)
 {
     return sushi_cuda_ssyrk_strided_batched(ctx, dev, upper, trans, n, k, alpha, a, lda, 0, beta, c, ldc, 0, 1);
+}
+
+namespace {
+
+// One triangular solve, row-major:  left: op(A) X = alpha B (A m x m);  right: X op(A) = alpha B (A n x n);
+// X overwrites B.  Recursive blocked substitution over 256-wide blocks of the triangular dimension:
+// a range of blocks is cut in two, the first half is solved, its contribution is removed from the
+// second half with ONE GEMM (alpha = -1, beta = 1, in place; at the top level half of all the
+// flops), then the second half is solved.  A single block is applied through its explicit inverse
+// (a GEMM into a temporary, copied back).  The 256 x 256 inverses come from the substitution
+// kernel on the 128 x 128 diagonal sub-blocks, completed by inv21 = -inv22 * T21 * inv11 (lower;
+// inv12 = -inv11 * T12 * inv22 for upper) as two batched GEMMs.
+int run_trsm(sushi_cuda_ctx* ctx, DeviceState& d, int left, int upper, int trans, int unit_diag, int64_t m, int64_t n,
+             float alpha, const float* a, int64_t lda, float* b, int64_t ldb)
+{
+    if (m == 0 || n == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d.device));
+    constexpr int64_t NB = sushi::TRSM_BASE, HB = sushi::TRSM_NB;
+    const int64_t dim = left ? m : n;
+    const int64_t nblk = (dim + NB - 1) / NB;
+    const bool eff_lower = (upper != 0) == (trans != 0);        // op(A) is lower triangular
+    auto scale_b = [&](float f) -> int {
+        int64_t blocks = (m * n + 255) / 256;
+        if (blocks > (int64_t)d.sm_count * 16) blocks = (int64_t)d.sm_count * 16;
+        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d.stream>>>(b, m, n, ldb, 0, 1, f);
+        ctx->launches++;
+        SC_CUDA(ctx, cudaGetLastError());
+        return SUSHI_CUDA_OK;
+    };
+    if (alpha == 0.0f) return scale_b(0.0f);                    // BLAS convention: B <- 0 without reading A
+
+    // workspace: the inverses, the 128 x 128 products T21 * inv11, one block row / column of temporaries
+    const size_t inv_bytes = (size_t)nblk * NB * NB * sizeof(float);
+    const size_t w_bytes = (size_t)nblk * HB * HB * sizeof(float);
+    const size_t tmp_bytes = (size_t)NB * (size_t)(left ? n : m) * sizeof(float);
+    int rc = grow(ctx, d, &d.trsm_buf, &d.trsm_bytes, inv_bytes + w_bytes + tmp_bytes);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    float* inv = static_cast<float*>(d.trsm_buf);
+    float* w = reinterpret_cast<float*>(static_cast<char*>(d.trsm_buf) + inv_bytes);
+    float* tmp = reinterpret_cast<float*>(static_cast<char*>(d.trsm_buf) + inv_bytes + w_bytes);
+
+    SC_CUDA(ctx, cudaMemsetAsync(inv, 0, inv_bytes, d.stream));
+    sushi::TrtriArgs t;
+    t.a = a; t.inv = inv; t.dim = dim; t.lda = lda; t.trans = trans != 0; t.eff_lower = eff_lower; t.unit_diag = unit_diag != 0;
+    SC_CUDA(ctx, sushi::launch_trtri_diag_blocks(t, d.stream));
+    ctx->launches++;
+
+    // complete the 256 x 256 inverses: `count` blocks starting at block q0 whose second sub-block has r2 rows
+    auto complete = [&](int64_t q0, int64_t count, int64_t r2) -> int {
+        if (count <= 0 || r2 <= 0) return SUSHI_CUDA_OK;
+        const int64_t p0 = q0 * NB;
+        float* blk = inv + q0 * NB * NB;
+        float* wq = w + q0 * HB * HB;
+        const int64_t sa = NB * (lda + 1), si = NB * NB, sw = HB * HB;
+        int r;
+        if (eff_lower)
+        {
+            // T21 = op(A)[p0+128 .., p0 ..] (r2 x 128);  W = T21 * inv11;  inv21 = -inv22 * W
+            const float* t21 = trans ? a + p0 * lda + p0 + HB : a + (p0 + HB) * lda + p0;
+            r = run_gemm(ctx, d, trans, 0, r2, HB, HB, 1.0f, t21, lda, sa, blk, NB, si, 0.0f, wq, HB, sw, count);
+            if (r != SUSHI_CUDA_OK) return r;
+            return run_gemm(ctx, d, 0, 0, r2, HB, r2, -1.0f, blk + HB * NB + HB, NB, si, wq, HB, sw, 0.0f, blk + HB * NB, NB, si, count);
+        }
+        // T12 = op(A)[p0 .., p0+128 ..] (128 x r2);  W = T12 * inv22;  inv12 = -inv11 * W
+        const float* t12 = trans ? a + (p0 + HB) * lda + p0 : a + p0 * lda + p0 + HB;
+        r = run_gemm(ctx, d, trans, 0, HB, r2, r2, 1.0f, t12, lda, sa, blk + HB * NB + HB, NB, si, 0.0f, wq, HB, sw, count);
+        if (r != SUSHI_CUDA_OK) return r;
+        return run_gemm(ctx, d, 0, 0, HB, r2, HB, -1.0f, blk, NB, si, wq, HB, sw, 0.0f, blk + HB, NB, si, count);
+    };
+    const int64_t full = dim / NB;                               // blocks with both sub-blocks complete
+    rc = complete(0, full, HB);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    if (full < nblk && dim - full * NB > HB) rc = complete(full, 1, dim - full * NB - HB);
+    if (rc != SUSHI_CUDA_OK) return rc;
+
+    if (alpha != 1.0f) { rc = scale_b(alpha); if (rc != SUSHI_CUDA_OK) return rc; }
+
+    // substitution order: forward when the solved blocks lie before the current one
+    const bool forward = left ? eff_lower : !eff_lower;
+    auto lim = [&](int64_t blk_index) { const int64_t e = blk_index * NB; return e < dim ? e : dim; };
+    // remove the contribution of the solved range [s0, s1) from the target range [r0, r1) (elements)
+    auto update = [&](int64_t r0, int64_t r1, int64_t s0, int64_t s1) -> int {
+        if (r1 <= r0 || s1 <= s0) return SUSHI_CUDA_OK;
+        if (left)
+        {
+            const float* t_op = trans ? a + s0 * lda + r0 : a + r0 * lda + s0;       // op(A)[r0.., s0..]
+            return run_gemm(ctx, d, trans, 0, r1 - r0, n, s1 - s0, -1.0f, t_op, lda, 0, b + s0 * ldb, ldb, 0, 1.0f,
+                            b + r0 * ldb, ldb, 0, 1);
+        }
+        const float* t_op = trans ? a + r0 * lda + s0 : a + s0 * lda + r0;           // op(A)[s0.., r0..]
+        return run_gemm(ctx, d, 0, trans, m, r1 - r0, s1 - s0, -1.0f, b + s0, ldb, 0, t_op, lda, 0, 1.0f, b + r0, ldb, 0, 1);
+    };
+    auto apply_inverse = [&](int64_t blk_index) -> int {
+        const int64_t p0 = blk_index * NB, size = lim(blk_index + 1) - p0;
+        const float* iv = inv + blk_index * NB * NB;
+        if (left)
+        {
+            float* b_blk = b + p0 * ldb;                                              // size x n
+            int r = run_gemm(ctx, d, 0, 0, size, n, size, 1.0f, iv, NB, 0, b_blk, ldb, 0, 0.0f, tmp, n, 0, 1);
+            if (r != SUSHI_CUDA_OK) return r;
+            SC_CUDA(ctx, cudaMemcpy2DAsync(b_blk, (size_t)ldb * sizeof(float), tmp, (size_t)n * sizeof(float),
+                                           (size_t)n * sizeof(float), (size_t)size, cudaMemcpyDeviceToDevice, d.stream));
+            return SUSHI_CUDA_OK;
+        }
+        float* b_blk = b + p0;                                                        // m x size, leading dimension ldb
+        int r = run_gemm(ctx, d, 0, 0, m, size, size, 1.0f, b_blk, ldb, 0, iv, NB, 0, 0.0f, tmp, size, 0, 1);
+        if (r != SUSHI_CUDA_OK) return r;
+        SC_CUDA(ctx, cudaMemcpy2DAsync(b_blk, (size_t)ldb * sizeof(float), tmp, (size_t)size * sizeof(float),
+                                       (size_t)size * sizeof(float), (size_t)m, cudaMemcpyDeviceToDevice, d.stream));
+        return SUSHI_CUDA_OK;
+    };
+    // explicit stack instead of recursion: ranges of blocks [lo, hi); kind 0 = solve, 1 = update
+    struct Frame { int64_t lo, hi, mid; int kind; };
+    std::vector<Frame> stack;
+    stack.push_back({0, nblk, 0, 0});
+    while (!stack.empty())
+    {
+        const Frame f = stack.back();
+        stack.pop_back();
+        if (f.kind == 1)
+        {
+            // [lo, mid) and [mid, hi): the half solved first feeds the other one
+            rc = forward ? update(lim(f.mid), lim(f.hi), lim(f.lo), lim(f.mid))
+                         : update(lim(f.lo), lim(f.mid), lim(f.mid), lim(f.hi));
+        }
+        else if (f.hi - f.lo == 1) rc = apply_inverse(f.lo);
+        else
+        {
+            const int64_t mid = f.lo + (f.hi - f.lo + 1) / 2;
+            // pushed in reverse order of execution
+            if (forward) { stack.push_back({mid, f.hi, 0, 0}); stack.push_back({f.lo, f.hi, mid, 1}); stack.push_back({f.lo, mid, 0, 0}); }
+            else { stack.push_back({f.lo, mid, 0, 0}); stack.push_back({f.lo, f.hi, mid, 1}); stack.push_back({mid, f.hi, 0, 0}); }
+        }
+        if (rc != SUSHI_CUDA_OK) return rc;
+    }
+    return SUSHI_CUDA_OK;
+}
+
+} // namespace
+
+extern "C" int sushi_cuda_strsm_strided_batched(sushi_cuda_ctx* ctx, int dev, int left, int upper, int trans, int unit_diag,
+                                                int64_t m, int64_t n, float alpha, const float* a, int64_t lda,
+                                                int64_t stride_a, float* b, int64_t ldb, int64_t stride_b, int64_t batch)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "strsm: bad context or device index");
+    const int64_t dim = left ? m : n;
+    if (m < 0 || n < 0 || batch < 0 || stride_a < 0 || stride_b < 0)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "strsm: negative dimension or stride");
+    if (lda < (dim > 1 ? dim : 1)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "strsm: lda too small");
+    if (ldb < (n > 1 ? n : 1)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "strsm: ldb too small");
+    if (m > 0 && n > 0 && batch > 0 && (!a || !b)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "strsm: A or B is null");
+    for (int64_t i = 0; i < batch; ++i)
+    {
+        int rc = run_trsm(ctx, *d, left, upper, trans, unit_diag, m, n, alpha, a + i * stride_a, lda, b + i * stride_b, ldb);
+        if (rc != SUSHI_CUDA_OK) return rc;
+    }
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_strsm(sushi_cuda_ctx* ctx, int dev, int left, int upper, int trans, int unit_diag,
+                                int64_t m, int64_t n, float alpha, const float* a, int64_t lda, float* b, int64_t ldb)
+{
+    return sushi_cuda_strsm_strided_batched(ctx, dev, left, upper, trans, unit_diag, m, n, alpha, a, lda, 0, b, ldb, 0, 1);
 }
 
 extern "C" int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count)

@@ -227,6 +227,62 @@ TEST_CASE(SyrkLargeUpperKeepsTheOtherTriangle)
     EXPECT_THROWS(engine.blas().syrk(A, S), "does not match C");
 }
 
+TEST_CASE(SimpleTRSM)
+{
+    // tests/blas/level3/test_trsm.cpp:39-77: lower triangular, left side
+    sb::Engine engine(runtime());
+    auto A = engine.create_tensor({2, 2});
+    auto B = engine.create_tensor({2, 2});
+    fill_tensor(A, {2, 0, 1, 2});
+    fill_tensor(B, {4, 6, 4, 7});
+    engine.blas().trsm(A, B, true, false, false, false, 1.0f);
+    engine.execute().wait();
+    verify_tensor(B, {2, 3, 1, 2});
+}
+
+TEST_CASE(SimpleTRSMColumnMajor)
+{
+    // tests/blas/level3/test_trsm.cpp:79-: upper triangular, column-major engine
+    sb::Engine engine(runtime(), sb::Core::Layout::COLUMN_MAJOR);
+    auto A = engine.create_tensor({2, 2});
+    auto B = engine.create_tensor({2, 2});
+    fill_tensor(A, {2, 0, 1, 2});
+    fill_tensor(B, {4, 4, 6, 7});
+    engine.blas().trsm(A, B, true, true, false, false, 1.0f);
+    engine.execute().wait();
+    verify_tensor(B, {1.0f, 2.0f, 1.25f, 3.5f});
+}
+
+TEST_CASE(TrsmBlockedRightSideRoundTrip)
+{
+    // X * A^T = alpha * B with A 300 x 300 upper (three diagonal blocks, the last one ragged):
+    // multiply the solution back and compare with alpha * B
+    sb::Engine engine(runtime());
+    const int m = 70, n = 300;
+    auto A = engine.create_tensor({n, n}), B = engine.create_tensor({m, n});
+    auto a = random_vec(size_t(n) * n, 61), b = random_vec(size_t(m) * n, 62);
+    for (int i = 0; i < n; ++i)
+        for (int j = 0; j < n; ++j)
+            a[size_t(i) * n + j] = (i == j) ? 4.0f + 0.01f * float(i % 7) : 0.05f * a[size_t(i) * n + j];
+    fill_tensor(A, a); fill_tensor(B, b);
+    engine.blas().trsm(A, B, false, true, true, false, 0.5f);
+    engine.execute().wait();
+    const float* x = B.data_as<float>();
+    for (int i = 0; i < m; i += 3)
+        for (int j = 0; j < n; j += 7)
+        {
+            // (X * A^T)(i, j) = sum_p X(i, p) * A(j, p) over the upper triangle p >= j
+            double s = 0;
+            for (int p = j; p < n; ++p) s += double(x[size_t(i) * n + p]) * double(a[size_t(j) * n + p]);
+            EXPECT_NEAR(s, 0.5 * b[size_t(i) * n + j], 2e-5);
+        }
+    auto R = engine.create_tensor({4, 5});
+    EXPECT_THROWS(engine.blas().trsm(R, B), "square");
+    auto S = engine.create_tensor({7, 7});
+    EXPECT_THROWS(engine.blas().trsm(S, B, true), "must match rows of B");
+    EXPECT_THROWS(engine.blas().trsm(S, B, false), "must match cols of B");
+}
+
 TEST_CASE(ReLUForward)
 {
     // tests/math/nonlinear/test_relu.cpp:38-47

@@ -180,3 +180,38 @@ def test_generator_is_counter_based_and_in_range():
     assert not np.array_equal(x, og.uniform_pm1(43, 1000))
     z = og.normal(7, 20000, std=0.02)
     assert abs(float(z.std()) - 0.02) < 0.002 and abs(float(z.mean())) < 0.001
+
+
+# ------------------------------------------------------------------ TRSM restatement
+def test_trsm_oracle_reproduces_the_reference_known_answers():
+    # tests/blas/level3/test_trsm.cpp:39-77: row-major, lower, left side
+    x = og.trsm_f64_c(1, 0, 0, 0, 2, 2, 1.0, [2, 0, 1, 2], 2, 0, [4, 6, 4, 7], 2, 0, 1)
+    assert np.array_equal(x, [2, 3, 1, 2])
+    # tests/blas/level3/test_trsm.cpp:79-: column-major engine, upper, left side
+    x = og.trsm_f64_c(1, 1, 0, 0, 2, 2, 1.0, [2, 0, 1, 2], 2, 0, [4, 4, 6, 7], 2, 0, 1, layout=og.COLUMN_MAJOR)
+    assert np.array_equal(x, [1.0, 2.0, 1.25, 3.5])
+
+
+def test_trsm_c_restatement_matches_lapack_in_every_mode():
+    rng = np.random.default_rng(5)
+    for left in (0, 1):
+        for upper in (0, 1):
+            for trans in (0, 1):
+                for unit in (0, 1):
+                    m, n, batch = 9, 6, 2
+                    dim = m if left else n
+                    lda, ldb = dim + 2, n + 1
+                    a = (rng.standard_normal((batch, dim, lda)) * 0.2).astype(np.float32)
+                    a[:, np.arange(dim), np.arange(dim)] += 3.0
+                    b = rng.standard_normal((batch, m, ldb)).astype(np.float32)
+                    xc = og.trsm_f64_c(left, upper, trans, unit, m, n, 0.5, a, lda, dim * lda, b, ldb, m * ldb, batch)
+                    xn, t = og.trsm_f64_np(left, upper, trans, unit, m, n, 0.5, a, lda, dim * lda, b, ldb, m * ldb, batch)
+                    got = og._view(xc, m, n, ldb, m * ldb, batch)
+                    assert np.allclose(got, xn, rtol=1e-12, atol=1e-12), (left, upper, trans, unit)
+                    bv = og._view(b.ravel(), m, n, ldb, m * ldb, batch)
+                    for i in range(batch):
+                        assert og.trsm_residual_ratio(left, t[i], got[i], 0.5, bv[i], dim) < 1e-6
+                    # a column-major solve is the row-major solve of the transposed equation
+                    xcm = og.trsm_f64_c(not left, not upper, trans, unit, n, m, 0.5, a, lda, dim * lda, b, ldb, m * ldb,
+                                        batch, layout=og.COLUMN_MAJOR)
+                    assert np.allclose(xcm, xc, rtol=1e-12, atol=1e-12), (left, upper, trans, unit)

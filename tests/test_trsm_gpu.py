@@ -1,0 +1,131 @@
+"""GPU parity tests of the triangular solve (C ABI sushi_cuda_strsm*) against the fp64 oracle.
+
+Tolerance (floating point), written for a solve of order `dim`:
+  * componentwise backward error  |op(A) X - alpha B| <= 8*dim*2^-24 * (|op(A)||X| + |alpha B|)
+    (oracle.ref_gemm.trsm_residual_ratio <= 1), and
+  * forward error against the fp64 substitution  max|X - X_ref| <= 32*dim*2^-24 * max|X_ref|
+    on systems built to be well conditioned (diagonal 3..5, off-diagonal row sums below 2).
+The two 2 x 2 known answers of the reference's own TRSM tests are checked to 1e-6.
+"""
+import numpy as np
+import pytest
+
+from oracle import ref_gemm as og
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def make_system(seed, left, upper, unit, m, n, batch, pad_a=0, pad_b=0, poison=True):
+    """Well-conditioned triangular A (dim x dim, lda = dim + pad_a) and B (m x n, ldb = n + pad_b).
+    With poison, everything the call must not read (the other triangle, the diagonal when
+    unit) is NaN."""
+    dim = m if left else n
+    lda, ldb = dim + pad_a, n + pad_b
+    sa, sb = dim * lda, m * ldb
+    a = og.uniform_pm1(seed, batch * sa).reshape(batch, dim, lda) * np.float32(2.0 / max(dim, 1))
+    diag = 3.0 + 2.0 * np.abs(og.uniform_pm1(seed + 1, batch * dim)).reshape(batch, dim)
+    idx = np.arange(dim)
+    a[:, idx, idx] = diag
+    if poison:
+        i, j = np.indices((dim, dim))
+        other = (j < i) if upper else (j > i)
+        a[:, :, :dim][np.broadcast_to(other, (batch, dim, dim))] = np.nan
+        if unit:
+            a[:, idx, idx] = np.nan
+    b = og.uniform_pm1(seed + 2, batch * sb)
+    return a.astype(np.float32).ravel(), b, lda, ldb, sa, sb, dim
+
+
+def solve_and_check(ctx, left, upper, trans, unit, m, n, alpha, batch=1, pad_a=0, pad_b=0, seed=500):
+    a, b, lda, ldb, sa, sb, dim = make_system(seed, left, upper, unit, m, n, batch, pad_a, pad_b)
+    db = dev(b)
+    ctx.strsm(left, upper, trans, unit, m, n, alpha, dev(a), lda, db, ldb, sa, sb, batch)
+    ctx.sync()
+    out = db.cpu().numpy()
+    clean = np.nan_to_num(a, nan=0.0)
+    xref, t = og.trsm_f64_np(left, upper, trans, unit, m, n, alpha, clean, lda, sa, b, ldb, sb, batch)
+    got = og._view(out, m, n, ldb, sb, batch).astype(np.float64)
+    bv = og._view(b, m, n, ldb, sb, batch).astype(np.float64)
+    tag = (left, upper, trans, unit, m, n, alpha, batch)
+    assert np.isfinite(got).all(), tag
+    for i in range(batch):
+        r = og.trsm_residual_ratio(left, t[i], got[i], alpha, bv[i], dim)
+        assert r <= 1.0, (tag, "residual", r)
+        fwd = np.max(np.abs(got[i] - xref[i])) / (32.0 * dim * 2.0 ** -24 * np.max(np.abs(xref[i])) + 1e-30)
+        assert fwd <= 1.0, (tag, "forward", fwd)
+    if pad_b:
+        keep = np.ones(out.shape, dtype=bool)
+        idx = (np.arange(batch)[:, None, None] * sb + np.arange(m)[None, :, None] * ldb + np.arange(n)[None, None, :])
+        keep[idx.ravel()] = False
+        assert np.array_equal(out[keep], b[keep]), (tag, "B padding was overwritten")
+
+
+def test_reference_kat_trsm(ctx):
+    # tests/blas/level3/test_trsm.cpp:39-77 (row-major, lower, left side)
+    b = dev(np.array([4, 6, 4, 7], np.float32))
+    ctx.strsm(1, 0, 0, 0, 2, 2, 1.0, dev(np.array([2, 0, 1, 2], np.float32)), 2, b, 2)
+    ctx.sync()
+    assert np.allclose(b.cpu().numpy(), [2, 3, 1, 2], rtol=0, atol=1e-6)
+    # tests/blas/level3/test_trsm.cpp:79- (column-major, upper, left side): in row-major terms the
+    # transposed equation, i.e. a right-side solve with the lower triangle
+    b = dev(np.array([4, 4, 6, 7], np.float32))
+    ctx.strsm(0, 0, 0, 0, 2, 2, 1.0, dev(np.array([2, 0, 1, 2], np.float32)), 2, b, 2)
+    ctx.sync()
+    assert np.allclose(b.cpu().numpy(), [1.0, 2.0, 1.25, 3.5], rtol=0, atol=1e-6)
+    # and the C restatement agrees on both
+    assert np.allclose(og.trsm_f64_c(1, 1, 0, 0, 2, 2, 1.0, [2, 0, 1, 2], 2, 0, [4, 4, 6, 7], 2, 0, 1,
+                                     layout=og.COLUMN_MAJOR), [1.0, 2.0, 1.25, 3.5])
+
+
+@pytest.mark.parametrize("left", [0, 1])
+@pytest.mark.parametrize("upper", [0, 1])
+@pytest.mark.parametrize("trans", [0, 1])
+def test_trsm_all_modes_small_and_blocked(ctx, left, upper, trans):
+    for unit in (0, 1):
+        solve_and_check(ctx, left, upper, trans, unit, 37, 29, 1.0, seed=510 + unit)           # one diagonal block
+        solve_and_check(ctx, left, upper, trans, unit, 300, 200, 0.5, batch=2, pad_a=3, pad_b=5,
+                        seed=520 + unit)                                                     # ragged blocks, batched
+        solve_and_check(ctx, left, upper, trans, unit, 128, 256, -2.0, seed=530 + unit)        # exact block edges
+
+
+def test_trsm_large_runs_updates_on_tensor_cores(ctx):
+    before = ctx.launch_count()
+    solve_and_check(ctx, 1, 0, 0, 0, 2048, 1024, 1.0, seed=540)
+    solve_and_check(ctx, 0, 1, 1, 0, 768, 2048, 1.5, seed=541)
+    solve_and_check(ctx, 1, 1, 1, 1, 1500, 700, 1.0, pad_a=4, pad_b=4, seed=542)
+    assert ctx.launch_count() > before
+
+
+def test_trsm_alpha_zero_and_degenerate(ctx):
+    a = torch.full((16,), float("nan"), device="cuda")
+    b = torch.ones(16, device="cuda")
+    ctx.strsm(1, 0, 0, 0, 4, 4, 0.0, a, 4, b, 4)          # alpha == 0: B <- 0, A is not read
+    ctx.sync()
+    assert torch.count_nonzero(b).item() == 0
+    b = torch.ones(16, device="cuda")
+    ctx.strsm(1, 0, 0, 0, 0, 4, 1.0, a, 1, b, 4)          # m == 0
+    ctx.strsm(0, 0, 0, 0, 4, 0, 1.0, a, 1, b, 1)          # n == 0
+    ctx.strsm(1, 0, 0, 0, 4, 4, 1.0, a, 4, b, 4, batch=0)
+    ctx.sync()
+    assert torch.equal(b, torch.ones(16, device="cuda"))
+
+
+def test_trsm_invalid_arguments_are_rejected(ctx):
+    from sushiblas_b200 import SushiCudaError
+    x = torch.zeros(64, device="cuda")
+    with pytest.raises(SushiCudaError) as e:
+        ctx.strsm(1, 0, 0, 0, 4, 4, 1.0, x, 3, x, 4)      # lda < m
+    assert e.value.code == -1
+    with pytest.raises(SushiCudaError):
+        ctx.strsm(0, 0, 0, 0, 4, 6, 1.0, x, 5, x, 6)      # right side: lda < n
+    with pytest.raises(SushiCudaError):
+        ctx.strsm(1, 0, 0, 0, 4, 4, 1.0, x, 4, x, 3)      # ldb < n
+    with pytest.raises(SushiCudaError):
+        ctx.strsm(1, 0, 0, 0, -1, 4, 1.0, x, 4, x, 4)
+    with pytest.raises(SushiCudaError):
+        ctx.strsm(1, 0, 0, 0, 4, 4, 1.0, None, 4, x, 4)
