@@ -1,8 +1,8 @@
 // engine.hpp -- entry object of the library (reference: include/SushiBLAS/engine.hpp:61-194,
 // src/engine.cpp:35-69): holds the runtime context, the deferred task graph, the default
-// layout and the RNG seed; hands out tensors and the op facades.  Only blas() (GEMM) and
-// nonlinear() (ReLU, fusable into a GEMM) are provided: the other op families of the reference
-// are outside the fp32 GEMM path.
+// layout and the RNG seed; hands out tensors and the op facades.  Provided: blas() (Level 3:
+// GEMM, SYRK, TRSM), nonlinear() (ReLU, fusable into a GEMM) and io() (.npy / raw files); the
+// other op families of the reference are outside the GEMM path.
 #pragma once
 
 #include <atomic>
@@ -12,6 +12,7 @@
 
 #include <SushiBLAS/core/common.hpp>
 #include <SushiBLAS/core/logger.hpp>
+#include <SushiBLAS/io.hpp>
 #include <SushiBLAS/ops/blas.hpp>
 #include <SushiBLAS/ops/math/nonlinear.hpp>
 #include <SushiBLAS/storage.hpp>
@@ -34,6 +35,7 @@ namespace SushiBLAS
 
             BLASOps blas() { return BLASOps(*this); }
             NonLinearOps nonlinear() { return NonLinearOps(*this); }
+            IO io() { return IO(*this); }
 
             SushiRuntime::Execution::RuntimeContext& get_context() { return context_; }
             SushiRuntime::Graph::TaskGraph& get_graph() { return graph_; }
@@ -84,8 +86,9 @@ namespace SushiBLAS
     {
         using namespace SushiRuntime::Graph::Literals;
         const detail::GemmCall user = detail::derive_gemm_call(A, B, C, transA, transB, alpha, beta);
+        if (A.dtype == Core::DataType::FLOAT64) return gemm_f64(A, B, C, transA, transB, alpha, beta);
         SB_THROW_IF(A.dtype != Core::DataType::FLOAT32,
-                    "Unsupported data type for GEMM operation (the CUDA backend serves FLOAT32 only).");
+                    "Unsupported data type for GEMM operation (the CUDA backend serves FLOAT32 and FLOAT64).");
 
         bool swapped = false;
         const detail::GemmCall g = detail::row_major_equivalent(user, &swapped);
@@ -188,6 +191,65 @@ namespace SushiBLAS
             groupable.finish = finish;
         }
         engine_.get_graph().add_task(meta, reads, writes, work, producer, groupable);
+        return SushiRuntime::Execution::Event();
+    }
+
+    // ---------------------------------------------------------------- Level3::gemm, FLOAT64
+    inline SushiRuntime::Execution::Event Level3::gemm_f64(const Tensor& A, const Tensor& B, Tensor& C, bool transA,
+                                                           bool transB, float alpha, float beta)
+    {
+        using namespace SushiRuntime::Graph::Literals;
+        const detail::GemmCall user = detail::derive_gemm_call(A, B, C, transA, transB, alpha, beta);
+        bool swapped = false;
+        const detail::GemmCall g = detail::row_major_equivalent(user, &swapped);
+        const Tensor& first = swapped ? B : A;
+        const Tensor& second = swapped ? A : B;
+
+        struct Operand { SushiRuntime::sushi_ptr<Storage> storage; double* ptr; int64_t extent; bool host; };
+        auto describe = [](const Tensor& t, int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t batch) {
+            Operand o{t.storage, t.data_as<double>(), detail::operand_extent(rows, cols, ld, stride, batch), false};
+            o.host = t.storage->host_resident();
+            const std::size_t need = (static_cast<std::size_t>(t.storage_offset) + static_cast<std::size_t>(o.extent)) * sizeof(double);
+            SB_THROW_IF(need > t.storage->size_bytes,
+                        "GEMM operand does not fit its storage (needs {} bytes, has {}).", need, t.storage->size_bytes);
+            return o;
+        };
+        Operand oa = describe(first, g.trans_a ? g.k : g.m, g.trans_a ? g.m : g.k, g.lda, g.stride_a, g.batch);
+        Operand ob = describe(second, g.trans_b ? g.n : g.k, g.trans_b ? g.k : g.n, g.ldb, g.stride_b, g.batch);
+        Operand oc = describe(C, g.m, g.n, g.ldc, g.stride_c, g.batch);
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = "blas.lvl3.gemm";
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = "blas.lvl3.gemm"_op;
+        meta.set_param(0, alpha); meta.set_param(1, beta); meta.set_param(2, transA); meta.set_param(3, transB);
+        engine_.get_graph().add_task(meta, {A.storage->data_ptr, B.storage->data_ptr}, {C.storage->data_ptr},
+            [=](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            {
+                sushi_cuda_ctx* ctx = rt.native_handle();
+                auto on_device = [ctx](const Operand& o, bool upload, double** out) -> int
+                {
+                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
+                    if (!base) return SUSHI_CUDA_ERR_OOM;
+                    *out = reinterpret_cast<double*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
+                    if (o.host && upload && o.extent > 0)
+                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(double));
+                    return SUSHI_CUDA_OK;
+                };
+                double *da = nullptr, *db = nullptr, *dc = nullptr;
+                int rc = on_device(oa, true, &da);
+                if (rc == SUSHI_CUDA_OK) rc = on_device(ob, true, &db);
+                const bool dense_c = (g.ldc == g.n) && (g.batch == 1 || g.stride_c == g.m * g.n);
+                if (rc == SUSHI_CUDA_OK) rc = on_device(oc, g.beta != 0.0f || !dense_c, &dc);
+                if (rc != SUSHI_CUDA_OK) return rc;
+                SB_LOG_INFO("CUDA GEMM f64 [Row-Major]: {}x[{}x{}x{}]", g.batch, g.m, g.n, g.k);
+                rc = sushi_cuda_dgemm_strided_batched(ctx, 0, g.trans_a, g.trans_b, g.m, g.n, g.k, static_cast<double>(g.alpha),
+                                                      da, g.lda, g.stride_a, db, g.ldb, g.stride_b, static_cast<double>(g.beta),
+                                                      dc, g.ldc, g.stride_c, g.batch);
+                if (rc == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
+                    rc = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(double));
+                return rc;
+            });
         return SushiRuntime::Execution::Event();
     }
 
@@ -419,4 +481,113 @@ namespace SushiBLAS
             });
         return SushiRuntime::Execution::Event();
     }
+    // ---------------------------------------------------------------- IO
+    inline void IO::write_payload(std::ofstream& ofs, const Tensor& t)
+    {
+        SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
+        SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
+        const std::size_t bytes = static_cast<std::size_t>(t.num_elements) * detail::io_bytes_per_element(t.dtype);
+        if (bytes == 0) return;
+        if (t.storage->host_resident())
+            ofs.write(static_cast<const char*>(t.data()), static_cast<std::streamsize>(bytes));
+        else
+        {
+            std::vector<char> buf(bytes);
+            t.to_host(buf.data());
+            ofs.write(buf.data(), static_cast<std::streamsize>(bytes));
+        }
+        SB_THROW_IF(!ofs.good(), "Failed while writing {} bytes of tensor data", bytes);
+    }
+
+    inline void IO::read_payload(std::ifstream& ifs, Tensor& t, const std::string& path)
+    {
+        SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
+        SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
+        const std::size_t bytes = static_cast<std::size_t>(t.num_elements) * detail::io_bytes_per_element(t.dtype);
+        if (bytes == 0) return;
+        if (t.storage->host_resident())
+        {
+            ifs.read(static_cast<char*>(t.data()), static_cast<std::streamsize>(bytes));
+            SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != bytes, "File is shorter than the tensor ({} bytes): {}", bytes, path);
+            // the device mirror of a host-resident tensor is refreshed by the next operation that reads it
+        }
+        else
+        {
+            std::vector<char> buf(bytes);
+            ifs.read(buf.data(), static_cast<std::streamsize>(bytes));
+            SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != bytes, "File is shorter than the tensor ({} bytes): {}", bytes, path);
+            t.from_host(buf.data());
+        }
+    }
+
+    inline void IO::save_npy(const Tensor& t, const std::string& path)
+    {
+        SB_THROW_IF(detail::npy_descr(t.dtype)[0] == '\0', "Unsupported data type for .npy export.");
+        engine_.execute().wait();
+        std::ofstream ofs(path, std::ios::binary);
+        SB_THROW_IF(!ofs.is_open(), "Failed to open file: {}", path);
+        const std::string dict = detail::npy_header_dict(t.dtype, t.layout, t.shape.data(), t.rank);
+        SB_THROW_IF(dict.size() > 65535, "Tensor shape does not fit a version 1.0 .npy header");
+        const unsigned char preamble[10] = {0x93, 'N', 'U', 'M', 'P', 'Y', 1, 0,
+                                            static_cast<unsigned char>(dict.size() & 0xff),
+                                            static_cast<unsigned char>(dict.size() >> 8)};
+        ofs.write(reinterpret_cast<const char*>(preamble), 10);
+        ofs.write(dict.data(), static_cast<std::streamsize>(dict.size()));
+        write_payload(ofs, t);
+        SB_LOG_INFO("Exported NumPy file: {}", path);
+    }
+
+    inline void IO::load_npy(Tensor& t, const std::string& path)
+    {
+        engine_.execute().wait();
+        std::ifstream ifs(path, std::ios::binary);
+        SB_THROW_IF(!ifs.is_open(), "Failed to open file for reading: {}", path);
+        unsigned char pre[8] = {0};
+        ifs.read(reinterpret_cast<char*>(pre), 8);
+        SB_THROW_IF(ifs.gcount() != 8 || std::memcmp(pre, "\x93NUMPY", 6) != 0, "Invalid .npy file magic.");
+        const int major = pre[6];
+        SB_THROW_IF(major < 1 || major > 3, "Unsupported .npy format version {}.{}", major, int(pre[7]));
+        unsigned char len_bytes[4] = {0};
+        const int len_size = (major == 1) ? 2 : 4;
+        ifs.read(reinterpret_cast<char*>(len_bytes), len_size);
+        SB_THROW_IF(ifs.gcount() != len_size, "Truncated .npy header: {}", path);
+        const std::size_t header_len = std::size_t(len_bytes[0]) | (std::size_t(len_bytes[1]) << 8) |
+                                       (std::size_t(len_bytes[2]) << 16) | (std::size_t(len_bytes[3]) << 24);
+        std::string header(header_len, ' ');
+        ifs.read(header.data(), static_cast<std::streamsize>(header_len));
+        SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != header_len, "Truncated .npy header: {}", path);
+        const detail::NpyInfo info = detail::parse_npy_header(header);
+
+        std::string want = detail::npy_descr(t.dtype);
+        std::string have = info.descr;
+        if (!have.empty() && (have[0] == '=' || have[0] == '|')) have[0] = '<';     // native order on this host is little-endian
+        SB_THROW_IF(have != want, "Data type mismatch in .npy header: file has '{}', tensor needs '{}'.", info.descr, want);
+        SB_THROW_IF(static_cast<int32_t>(info.shape.size()) != t.rank, "Rank mismatch in .npy header: file has {}, tensor has {}.",
+                    info.shape.size(), t.rank);
+        for (int i = 0; i < t.rank; ++i)
+            SB_THROW_IF(info.shape[static_cast<std::size_t>(i)] != t.shape[i], "Shape dimension {} mismatch in .npy header.", i);
+        int wide_dims = 0;
+        for (int i = 0; i < t.rank; ++i) wide_dims += t.shape[i] > 1;
+        SB_THROW_IF(wide_dims > 1 && info.fortran_order != (t.layout == Core::Layout::COLUMN_MAJOR),
+                    "Memory order mismatch in .npy header: fortran_order is {}.", info.fortran_order ? "True" : "False");
+        read_payload(ifs, t, path);
+        SB_LOG_INFO("Loaded NumPy file: {}", path);
+    }
+
+    inline void IO::save_bin(const Tensor& t, const std::string& path)
+    {
+        engine_.execute().wait();
+        std::ofstream ofs(path, std::ios::binary);
+        SB_THROW_IF(!ofs.is_open(), "Failed to open file: {}", path);
+        write_payload(ofs, t);
+    }
+
+    inline void IO::load_bin(Tensor& t, const std::string& path)
+    {
+        engine_.execute().wait();
+        std::ifstream ifs(path, std::ios::binary);
+        SB_THROW_IF(!ifs.is_open(), "Failed to open file: {}", path);
+        read_payload(ifs, t, path);
+    }
+
 } // namespace SushiBLAS

@@ -5,8 +5,8 @@
 //
 // The record phase is the reference's: validate, derive m/n/k/ld/stride/batch from the Tensor
 // metadata, build TaskMetadata, add a task.  The task body calls the C ABI instead of oneMKL.
-// Only FLOAT32 is served (the named path).  SYRK runs on the same kernels; TRSM is not part of
-// this build.
+// GEMM serves FLOAT32 (tcgen05 3xTF32 / FFMA kernels) and FLOAT64 (DMMA kernel); SYRK and TRSM
+// (FLOAT32) run on the fp32 GEMM kernels.
 #pragma once
 
 #include <cstdint>
@@ -97,12 +97,18 @@ namespace SushiBLAS
             explicit Level3(Engine& e) : engine_(e) {}
             Engine& engine_;
 
+        private:
+            /// FLOAT64 branch of gemm() (gemm.cpp:158-169): same derivation, alpha / beta widened.
+            inline SushiRuntime::Execution::Event gemm_f64(const Tensor& A, const Tensor& B, Tensor& C, bool transA,
+                                                           bool transB, float alpha, float beta);
+
         public:
             /// Records C <- alpha*op(A)*op(B) + beta*C on the engine's task graph; it runs at
             /// Engine::execute().  Returns an already-complete event (as the reference does,
             /// gemm.cpp:197): wait on execute().  C is not read when beta == 0.
-            /// Throws std::runtime_error on rank < 2, dtype mismatch, a dtype other than FLOAT32,
-            /// a tensor without storage, or operands that do not fit their storage.
+            /// FLOAT32 and FLOAT64 tensors are served.  Throws std::runtime_error on rank < 2, dtype
+            /// mismatch, any other dtype, a tensor without storage, or operands that do not fit
+            /// their storage.
             inline SushiRuntime::Execution::Event gemm(const Tensor& A, const Tensor& B, Tensor& C,
                                                        bool transA = false, bool transB = false,
                                                        float alpha = 1.0f, float beta = 0.0f);

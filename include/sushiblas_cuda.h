@@ -157,6 +157,21 @@ SUSHI_CUDA_API int sushi_cuda_ssyrk_strided_batched(sushi_cuda_ctx* ctx, int dev
                                                     const float* a, int64_t lda, int64_t stride_a, float beta,
                                                     float* c, int64_t ldc, int64_t stride_c, int64_t batch);
 
+/* fp64 GEMM, same argument meaning as sushi_cuda_sgemm[_strided_batched] with double data:
+ * replaces oneapi::mkl::blas::row_major::gemm / gemm_batch<double> (FLOAT64 branch of the
+ * front-end, src/ops/blas/level3/gemm.cpp:158-169).  Runs on the FP64 tensor-core instruction
+ * (mma.sync m16n8k8.f64): exact fp64 products, fp64 accumulation.                              */
+SUSHI_CUDA_API int sushi_cuda_dgemm(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                    int64_t m, int64_t n, int64_t k, double alpha,
+                                    const double* a, int64_t lda, const double* b, int64_t ldb,
+                                    double beta, double* c, int64_t ldc);
+SUSHI_CUDA_API int sushi_cuda_dgemm_strided_batched(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                    int64_t m, int64_t n, int64_t k, double alpha,
+                                                    const double* a, int64_t lda, int64_t stride_a,
+                                                    const double* b, int64_t ldb, int64_t stride_b,
+                                                    double beta, double* c, int64_t ldc, int64_t stride_c,
+                                                    int64_t batch);
+
 /* Triangular solve with multiple right-hand sides, row-major; X overwrites B (m x n):
  *     left != 0:  op(A) * X = alpha * B,  A is m x m        left == 0:  X * op(A) = alpha * B,  A is n x n
  * A is upper (upper != 0) or lower triangular; only that triangle is read, and its diagonal is

@@ -300,3 +300,52 @@ int oracle_trsm_f64(int layout_row, int left, int upper, int trans, int unit_dia
     free(t); free(x);
     return 0;
 }
+
+/*
+ * oracle_dgemm_f80acc: the FLOAT64 branch of the GEMM front-end (src/ops/blas/level3/gemm.cpp:158-169:
+ * the same derivation as fp32, alpha / beta widened to double, forwarding to oneMKL gemm[_batch]<double>),
+ * fp64 operands accumulated in x87 extended precision (64-bit significand), so that the result can
+ * judge an fp64 kernel.  Argument meaning as oracle_gemm_f64acc; c_out80 receives the result as
+ * long double, abs_ab (optional) sum_k |a||b|.  The reference holds no fp64 GEMM test; this function
+ * is pinned by the reference's fp32 known answers (exactly representable) evaluated in double.
+ */
+int oracle_dgemm_f80acc(int layout_row, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k, double alpha,
+                        const double* a, int64_t lda, int64_t stride_a, const double* b, int64_t ldb, int64_t stride_b,
+                        double beta, const double* c_in, int64_t ldc, int64_t stride_c, int64_t batch,
+                        long double* c_out80, double* abs_ab)
+{
+    if (m < 0 || n < 0 || k < 0 || batch < 0 || !c_out80) return -1;
+    long double* acc = (long double*)malloc(sizeof(long double) * (size_t)(n > 0 ? n : 1) * 2);
+    if (!acc) return -2;
+    long double* accabs = acc + (n > 0 ? n : 1);
+    for (int64_t bi = 0; bi < batch; ++bi)
+    {
+        const double* ab = a + bi * stride_a;
+        const double* bb = b + bi * stride_b;
+        for (int64_t i = 0; i < m; ++i)
+        {
+            for (int64_t j = 0; j < n; ++j) { acc[j] = 0.0L; accabs[j] = 0.0L; }
+            for (int64_t kk = 0; kk < k; ++kk)
+            {
+                long double av = (long double)ab[op_index(layout_row, trans_a, i, kk, lda)];
+                long double aabs = fabsl(av);
+                for (int64_t j = 0; j < n; ++j)
+                {
+                    long double bv = (long double)bb[op_index(layout_row, trans_b, kk, j, ldb)];
+                    acc[j] += av * bv;
+                    accabs[j] += aabs * fabsl(bv);
+                }
+            }
+            for (int64_t j = 0; j < n; ++j)
+            {
+                int64_t ci = bi * stride_c + (layout_row ? i * ldc + j : j * ldc + i);
+                long double v = (long double)alpha * acc[j];
+                if (beta != 0.0) v += (long double)beta * (long double)c_in[ci];
+                c_out80[ci] = v;
+                if (abs_ab) abs_ab[ci] = (double)accabs[j];
+            }
+        }
+    }
+    free(acc);
+    return 0;
+}

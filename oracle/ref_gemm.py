@@ -63,6 +63,9 @@ def _lib():
                                            p, i64, i64, i64, p, p]
         lib.oracle_trsm_f64.restype = ctypes.c_int
         lib.oracle_trsm_f64.argtypes = [ctypes.c_int] * 5 + [i64, i64, f32, p, i64, i64, p, i64, i64, i64, p]
+        lib.oracle_dgemm_f80acc.restype = ctypes.c_int
+        lib.oracle_dgemm_f80acc.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, i64, i64, i64, dbl, p, i64, i64,
+                                            p, i64, i64, dbl, p, i64, i64, i64, p, p]
         lib.oracle_check_tolerance.restype = dbl
         lib.oracle_check_tolerance.argtypes = [i64, i64, i64, i64, f32, dbl, p, p, p, p,
                                                i64, i64, ctypes.POINTER(dbl)]
@@ -167,6 +170,39 @@ def syrk_f64_np(upper, trans, n, k, alpha, a, lda, stride_a, beta, c_in, ldc, st
     i, j = np.indices((n, n))
     mask = (j >= i) if upper else (j <= i)
     return np.where(mask[None], full, cin), np.where(mask[None], absab, 0.0), mask
+
+
+def dgemm_f80_c(trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c_in, ldc, stride_c, batch,
+                layout=ROW_MAJOR):
+    """FLOAT64 GEMM (gemm.cpp:158-169) accumulated in x87 extended precision through the C
+    restatement.  Returns (c: np.longdouble flat array indexed like C, abs_ab: float64)."""
+    assert np.finfo(np.longdouble).nmant >= 63, "this oracle needs an extended-precision long double"
+    a = np.ascontiguousarray(a, dtype=np.float64).ravel()
+    b = np.ascontiguousarray(b, dtype=np.float64).ravel()
+    c64 = np.ascontiguousarray(c_in, dtype=np.float64).ravel()
+    out = c64.astype(np.longdouble)
+    absab = np.zeros(out.shape, dtype=np.float64)
+    rc = _lib().oracle_dgemm_f80acc(1 if layout == ROW_MAJOR else 0, int(trans_a), int(trans_b), m, n, k, alpha,
+                                    _ptr(a), lda, stride_a, _ptr(b), ldb, stride_b, beta, _ptr(c64), ldc, stride_c, batch,
+                                    _ptr(out), _ptr(absab))
+    if rc != 0:
+        raise ValueError("oracle_dgemm_f80acc rejected its arguments")
+    return out, absab
+
+
+def tolerance_ratio_f64(got, ref, abs_ab, k, beta=0.0, c_in=None, budget=1.0):
+    """fp64 form of the GEMM bound: max over elements of |got - ref| divided by
+    budget * 8*K*2^-53 * (|A||B|) + 2^-53 * |beta * C_in|; <= 1 passes.  `ref` is extended precision."""
+    got = np.asarray(got, dtype=np.float64)
+    if not np.isfinite(got).all():
+        return float("inf")
+    err = np.abs(got.astype(np.longdouble) - np.asarray(ref, dtype=np.longdouble))
+    u = np.longdouble(2.0) ** -53
+    bound = budget * 8.0 * max(int(k), 1) * u * np.asarray(abs_ab, dtype=np.longdouble)
+    if beta != 0.0 and c_in is not None:
+        bound = bound + u * np.abs(np.longdouble(beta) * np.asarray(c_in, dtype=np.longdouble))
+    bound = bound + np.longdouble(1e-300)
+    return float(np.max(err / bound)) if err.size else 0.0
 
 
 def trsm_f64_c(left, upper, trans, unit_diag, m, n, alpha, a, lda, stride_a, b, ldb, stride_b, batch, layout=ROW_MAJOR):

@@ -51,7 +51,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
-CPP_TESTS = ("test_host_logic", "test_engine_gemm", "test_engine_sharded")
+CPP_TESTS = ("test_host_logic", "test_engine_gemm", "test_engine_sharded", "test_io_npy")
 CPP_BIN_DIR = os.path.join(ROOT, "tests", "cpp", "bin")
 
 

@@ -14,6 +14,7 @@ from ._build import LIB_PATH
 
 _i64 = ctypes.c_int64
 _f32 = ctypes.c_float
+_f64 = ctypes.c_double
 _int = ctypes.c_int
 _vp = ctypes.c_void_p
 _sz = ctypes.c_size_t
@@ -63,6 +64,9 @@ SIGNATURES = {
     "sushi_cuda_ssyrk": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "sushi_cuda_ssyrk_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _i64, _f32,
                                                 _vp, _i64, _i64, _i64]),
+    "sushi_cuda_dgemm": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _f64, _vp, _i64]),
+    "sushi_cuda_dgemm_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f64, _vp, _i64, _i64,
+                                                _vp, _i64, _i64, _f64, _vp, _i64, _i64, _i64]),
     "sushi_cuda_strsm": (_int, [_vp, _int, _int, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _vp, _i64]),
     "sushi_cuda_strsm_strided_batched": (_int, [_vp, _int, _int, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _i64,
                                                 _vp, _i64, _i64, _i64]),
@@ -276,6 +280,12 @@ class SushiCuda:
     def ssyrk(self, upper, trans, n, k, alpha, a, lda, beta, c, ldc, stride_a=0, stride_c=0, batch=1, dev: int = 0):
         self._check(self.lib.sushi_cuda_ssyrk_strided_batched(self._ctx, dev, int(upper), int(trans), n, k, alpha,
                                                               _addr(a), lda, stride_a, beta, _addr(c), ldc, stride_c, batch))
+
+    def dgemm(self, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc, stride_a=0, stride_b=0, stride_c=0,
+              batch=1, dev: int = 0):
+        self._check(self.lib.sushi_cuda_dgemm_strided_batched(self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha,
+                                                              _addr(a), lda, stride_a, _addr(b), ldb, stride_b, beta,
+                                                              _addr(c), ldc, stride_c, batch))
 
     def strsm(self, left, upper, trans, unit_diag, m, n, alpha, a, lda, b, ldb, stride_a=0, stride_b=0, batch=1,
               dev: int = 0):

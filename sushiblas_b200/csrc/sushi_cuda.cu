@@ -22,6 +22,7 @@
 #include "split_tf32.cuh"
 #include "sgemm_tc3x.cuh"
 #include "trsm_blocks.cuh"
+#include "dgemm_mma.cuh"
 
 namespace {
 
@@ -144,8 +145,8 @@ int64_t extent(int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t b
     return (batch - 1) * stride + (rows - 1) * ld + cols;
 }
 
-int validate_gemm(sushi_cuda_ctx* ctx, int64_t m, int64_t n, int64_t k, const float* a, int64_t lda,
-                  const float* b, int64_t ldb, const float* c, int64_t ldc, int ta, int tb,
+int validate_gemm(sushi_cuda_ctx* ctx, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda,
+                  const void* b, int64_t ldb, const void* c, int64_t ldc, int ta, int tb,
                   int64_t sa, int64_t sb, int64_t sc, int64_t batch)
 {
     if (m < 0 || n < 0 || k < 0 || batch < 0)
@@ -668,6 +669,46 @@ extern "C" int sushi_cuda_sgemm_strided_batched(sushi_cuda_ctx* ctx, int dev, in
     if (rc != SUSHI_CUDA_OK) return rc;
     return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc,
                     stride_c, batch);
+}
+
+extern "C" int sushi_cuda_dgemm_strided_batched(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                int64_t m, int64_t n, int64_t k, double alpha,
+                                                const double* a, int64_t lda, int64_t stride_a,
+                                                const double* b, int64_t ldb, int64_t stride_b,
+                                                double beta, double* c, int64_t ldc, int64_t stride_c,
+                                                int64_t batch)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "dgemm: bad context or device index");
+    int rc = validate_gemm(ctx, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, stride_a, stride_b, stride_c, batch);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    if (k == 0 || alpha == 0.0)
+    {
+        if (beta == 1.0) return SUSHI_CUDA_OK;
+        int64_t blocks = (m * n * batch + 255) / 256;
+        if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
+        sushi::scale_c_f64_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(c, m, n, ldc, stride_c, batch, beta);
+        ctx->launches++;
+        SC_CUDA(ctx, cudaGetLastError());
+        return SUSHI_CUDA_OK;
+    }
+    sushi::DgemmArgs g;
+    g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.stride_a = stride_a; g.stride_b = stride_b; g.stride_c = stride_c; g.tiles_m = 0; g.tiles_n = 0;
+    g.alpha = alpha; g.beta = beta;
+    g.status = d->status;
+    SC_CUDA(ctx, sushi::launch_dgemm(g, trans_a != 0, trans_b != 0, batch, d->sm_count, d->stream));
+    ctx->launches++;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_dgemm(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k,
+                                double alpha, const double* a, int64_t lda, const double* b, int64_t ldb, double beta,
+                                double* c, int64_t ldc)
+{
+    return sushi_cuda_dgemm_strided_batched(ctx, dev, trans_a, trans_b, m, n, k, alpha, a, lda, 0, b, ldb, 0, beta, c, ldc, 0, 1);
 }
 
 extern "C" int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,

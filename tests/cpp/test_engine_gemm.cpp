@@ -227,6 +227,41 @@ TEST_CASE(SyrkLargeUpperKeepsTheOtherTriangle)
     EXPECT_THROWS(engine.blas().syrk(A, S), "does not match C");
 }
 
+TEST_CASE(Float64GEMM)
+{
+    // FLOAT64 branch of the front-end (src/ops/blas/level3/gemm.cpp:158-169); the 3 x 3 known answer of
+    // tests/blas/level3/test_gemm.cpp:39-62 in double, then a product whose low bits only fp64 keeps
+    sb::Engine engine(runtime());
+    auto A = engine.create_tensor({3, 3}, sb::Core::DataType::FLOAT64);
+    auto B = engine.create_tensor({3, 3}, sb::Core::DataType::FLOAT64);
+    auto C = engine.create_tensor({3, 3}, sb::Core::DataType::FLOAT64);
+    for (int i = 0; i < 9; ++i) { A.data_as<double>()[i] = i + 1; B.data_as<double>()[i] = (i % 4 == 0) ? 1.0 : 0.0; C.data_as<double>()[i] = 0.0; }
+    engine.blas().gemm(A, B, C);
+    engine.execute().wait();
+    for (int i = 0; i < 9; ++i) EXPECT_EQ(C.data_as<double>()[i], double(i + 1));
+
+    const int m = 150, n = 140, k = 130;
+    auto X = engine.create_tensor({m, k}, sb::Core::DataType::FLOAT64, sr::Memory::AllocStrategy::DEVICE);
+    auto Y = engine.create_tensor({n, k}, sb::Core::DataType::FLOAT64, sr::Memory::AllocStrategy::DEVICE);
+    auto Z = engine.create_tensor({m, n}, sb::Core::DataType::FLOAT64, sr::Memory::AllocStrategy::DEVICE);
+    std::vector<double> x(size_t(m) * k), y(size_t(n) * k), z(size_t(m) * n, 1.0);
+    for (size_t i = 0; i < x.size(); ++i) x[i] = 1.0 + double(i % 977) * 1e-9;
+    for (size_t i = 0; i < y.size(); ++i) y[i] = 1.0 - double(i % 991) * 1e-9;
+    X.from_host(x.data()); Y.from_host(y.data()); Z.from_host(z.data());
+    engine.blas().gemm(X, Y, Z, false, true, 2.0f, 0.5f);
+    engine.execute().wait();
+    Z.to_host(z.data());
+    for (int i = 0; i < m; i += 7)
+        for (int j = 0; j < n; j += 11)
+        {
+            long double s = 0;
+            for (int p = 0; p < k; ++p) s += (long double)x[size_t(i) * k + p] * (long double)y[size_t(j) * k + p];
+            EXPECT_NEAR(z[size_t(i) * n + j], double(2.0L * s + 0.5L), 1e-11);     // fp32 would be off by ~1e-5
+        }
+    auto F = engine.create_tensor({3, 3});
+    EXPECT_THROWS(engine.blas().gemm(A, F, C), "Data type mismatch");
+}
+
 TEST_CASE(SimpleTRSM)
 {
     // tests/blas/level3/test_trsm.cpp:39-77: lower triangular, left side
@@ -452,7 +487,8 @@ TEST_CASE(ErrorsAreRuntimeErrors)
     sb::Tensor none;
     EXPECT_THROWS(engine.blas().gemm(v, B, A), "at least 2D");
     EXPECT_THROWS(engine.blas().gemm(A, B, D), "Data type mismatch");
-    EXPECT_THROWS(engine.blas().gemm(D, D, D), "FLOAT32 only");
+    auto Z = engine.create_tensor({4, 4}, sb::Core::DataType::COMPLEX32);
+    EXPECT_THROWS(engine.blas().gemm(Z, Z, Z), "serves FLOAT32 and FLOAT64");
     auto big = engine.create_tensor({64, 64});
     auto small = engine.create_tensor({2, 2});
     EXPECT_THROWS(engine.blas().gemm(small, B, big), "does not fit its storage");

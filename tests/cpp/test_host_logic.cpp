@@ -146,6 +146,42 @@ TEST_CASE(task_metadata_and_op_id)
     EXPECT_EQ(m.get_param<float>(0), 1.5f); EXPECT_EQ(m.get_param<bool>(2), true); EXPECT_EQ(m.get_param<int>(9), 0);
 }
 
+TEST_CASE(npy_header_is_what_numpy_writes_and_parses_back)
+{
+    // src/io.cpp:149-169; the expected strings are the headers numpy.save writes for these arrays
+    // numpy pads each of these dictionaries with spaces to 117 characters and closes it with '\n'
+    auto numpy_header = [](const std::string& text) { return text + std::string(117 - text.size(), ' ') + "\n"; };
+    int64_t s2[] = {3, 4};
+    EXPECT_EQ(sb::detail::npy_header_dict(sb::Core::DataType::FLOAT32, sb::Core::Layout::ROW_MAJOR, s2, 2),
+              numpy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (3, 4), }"));
+    int64_t s1[] = {5};
+    EXPECT_EQ(sb::detail::npy_header_dict(sb::Core::DataType::FLOAT32, sb::Core::Layout::ROW_MAJOR, s1, 1),
+              numpy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (5,), }"));
+    int64_t s3[] = {2, 3, 4};
+    EXPECT_EQ(sb::detail::npy_header_dict(sb::Core::DataType::FLOAT64, sb::Core::Layout::COLUMN_MAJOR, s3, 3),
+              numpy_header("{'descr': '<f8', 'fortran_order': True, 'shape': (2, 3, 4), }"));
+    int64_t s4[] = {1024, 1024, 7};
+    const std::string h4 = sb::detail::npy_header_dict(sb::Core::DataType::FLOAT32, sb::Core::Layout::ROW_MAJOR, s4, 3);
+    EXPECT_EQ(h4, numpy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (1024, 1024, 7), }"));
+    EXPECT_EQ((10 + h4.size()) % 64, 0u);
+
+    auto info = sb::detail::parse_npy_header(h4);
+    EXPECT_EQ(info.descr, std::string("<f4"));
+    EXPECT_TRUE(!info.fortran_order);
+    EXPECT_EQ(info.shape.size(), 3u);
+    EXPECT_EQ(info.shape[0], 1024); EXPECT_EQ(info.shape[1], 1024); EXPECT_EQ(info.shape[2], 7);
+    // key order and spacing are free in the format; () is a scalar, (5,) one dimension
+    info = sb::detail::parse_npy_header("{'shape': (5,), 'fortran_order': True, 'descr': '|f4'}");
+    EXPECT_EQ(info.descr, std::string("|f4"));
+    EXPECT_TRUE(info.fortran_order);
+    EXPECT_EQ(info.shape.size(), 1u);
+    EXPECT_EQ(sb::detail::parse_npy_header("{'descr': '<f8', 'fortran_order': False, 'shape': (), }").shape.size(), 0u);
+    EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'shape': (3,)}"), "fortran_order");
+    EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'fortran_order': 0, 'shape': (3,)}"), "neither True nor False");
+    EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (3, x)}"), "bad character");
+    EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (3, 4"), "unterminated shape");
+}
+
 TEST_CASE(runtime_context_fails_loudly_without_a_device)
 {
     int count = 0;

@@ -1,8 +1,10 @@
 """The C++ Engine/Tensor/Storage API (include/SushiBLAS, include/SushiRuntime) above the C ABI:
 compiled with g++ and run as separate programs.  Host logic runs anywhere; the Engine tests --
 the reference's own GEMM tests and caller shapes -- need the GPU."""
+import os
 import subprocess
 
+import numpy as np
 import pytest
 
 
@@ -30,3 +32,25 @@ def test_cpp_engine_gemm(binaries):
     for name in ("SimpleGEMM3x3", "SimpleGEMMColumnMajor", "DeviceStorageWithExplicitStaging"):
         assert f"[ OK ] {name}" in out
     print(out)
+
+
+@pytest.mark.gpu
+def test_cpp_io_npy_round_trips_with_numpy(binaries, tmp_path):
+    """Files numpy writes load into DEVICE / SHARED tensors, the files written back are byte for
+    byte numpy's, and a GEMM result saved from a DEVICE tensor reads back in numpy."""
+    d = str(tmp_path)
+    x = np.arange(60, dtype=np.float32).reshape(6, 10)
+    np.save(os.path.join(d, "in_rowmajor.npy"), x)
+    np.save(os.path.join(d, "in_fortran.npy"), np.asfortranarray(x))
+    p = subprocess.run([binaries["test_io_npy"], d], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and " 0 failed" in p.stdout, p.stdout + p.stderr
+    assert "skipped" not in p.stdout
+    for name in ("rowmajor", "fortran"):
+        with open(os.path.join(d, f"in_{name}.npy"), "rb") as f, open(os.path.join(d, f"echo_{name}.npy"), "rb") as g:
+            assert f.read() == g.read(), name
+    assert np.isfortran(np.load(os.path.join(d, "echo_fortran.npy")))
+    a, b, c = (np.load(os.path.join(d, f"gemm_{n}.npy")) for n in "abc")
+    assert a.shape == (5, 7) and b.shape == (7, 3) and c.dtype == np.float32
+    assert np.array_equal(c, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))   # small integers: exact
+    assert np.array_equal(np.load(os.path.join(d, "vec.npy")), np.arange(4, dtype=np.float32) * 0.5)
+    assert np.array_equal(np.fromfile(os.path.join(d, "gemm_c.bin"), dtype=np.float32).reshape(5, 3), c)

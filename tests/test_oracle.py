@@ -215,3 +215,33 @@ def test_trsm_c_restatement_matches_lapack_in_every_mode():
                     xcm = og.trsm_f64_c(not left, not upper, trans, unit, n, m, 0.5, a, lda, dim * lda, b, ldb, m * ldb,
                                         batch, layout=og.COLUMN_MAJOR)
                     assert np.allclose(xcm, xc, rtol=1e-12, atol=1e-12), (left, upper, trans, unit)
+
+
+# ------------------------------------------------------------------ FLOAT64 GEMM restatement
+def test_dgemm_oracle_known_answers_and_numpy_agreement():
+    # the reference's fp32 GEMM known answers are exactly representable: evaluated in double they pin the fp64 oracle
+    a = np.arange(1, 10, dtype=np.float64)
+    out, _ = og.dgemm_f80_c(0, 0, 3, 3, 3, 1.0, a, 3, 0, np.eye(3).ravel(), 3, 0, 0.0, np.zeros(9), 3, 0, 1)
+    assert out.dtype == np.longdouble and np.array_equal(out.astype(np.float64), a)
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "gemm_integer_kat.npz"))
+    for name in g["names"]:
+        ta, tb, m, n, k, alpha, beta, batch, lda, ldb, ldc, sa, sb, sc = [int(v) for v in g[f"{name}.meta"]]
+        out, _ = og.dgemm_f80_c(ta, tb, m, n, k, float(alpha), g[f"{name}.a"], lda, sa, g[f"{name}.b"], ldb, sb, float(beta),
+                                g[f"{name}.c_in"], ldc, sc, batch)
+        idx = (np.arange(batch)[:, None, None] * sc + np.arange(m)[None, :, None] * ldc + np.arange(n)[None, None, :]).ravel()
+        assert np.array_equal(out[idx].astype(np.float64), g[f"{name}.c_out"][idx].astype(np.float64)), name
+    # a conforming dgemm (numpy -> BLAS) sits well inside the bound; column-major equals the swapped row-major call
+    rng = np.random.default_rng(11)
+    m, n, k = 33, 21, 57
+    A, B, C = rng.standard_normal((m, k)), rng.standard_normal((k, n)), rng.standard_normal((m, n))
+    for ta, tb in [(0, 0), (0, 1), (1, 0), (1, 1)]:
+        a_st = np.ascontiguousarray(A.T) if ta else A
+        b_st = np.ascontiguousarray(B.T) if tb else B
+        ref, absab = og.dgemm_f80_c(ta, tb, m, n, k, 1.5, a_st, a_st.shape[1], 0, b_st, b_st.shape[1], 0, 0.5, C, n, 0, 1)
+        assert og.tolerance_ratio_f64((1.5 * A @ B + 0.5 * C).ravel(), ref, absab, k, 0.5, C.ravel(), budget=0.5) < 1.0
+    ref_cm, _ = og.dgemm_f80_c(0, 0, m, n, k, 1.0, np.asfortranarray(A).ravel(order="K"), m, 0,
+                               np.asfortranarray(B).ravel(order="K"), k, 0, 0.0, np.zeros(m * n), m, 0, 1,
+                               layout=og.COLUMN_MAJOR)
+    ref_rm, _ = og.dgemm_f80_c(0, 0, m, n, k, 1.0, A, k, 0, B, n, 0, 0.0, np.zeros(m * n), n, 0, 1)
+    assert np.array_equal(ref_cm.reshape(n, m).T, ref_rm.reshape(m, n))
+    assert og.tolerance_ratio_f64(np.array([np.nan]), np.array([0.0], np.longdouble), np.array([1.0]), 1) == float("inf")
