@@ -220,7 +220,6 @@ dgemm_mma_kernel(const DgemmArgs p)
     using TileA = DgTile<BT, !TA>;
     using TileB = DgTile<BT, TB>;
     constexpr int MB = BT / 64, NB = BT / 32;            // per warp: MB 16-row blocks down, NB 8-column blocks across
-    constexpr int P = TileA::P;
     extern __shared__ __align__(16) double dg_smem[];     // DG_STAGES x (A tile | B tile), then the barriers
 
     const int t = threadIdx.x, lane = t % 32, warp = t / 32;

@@ -15,6 +15,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <numeric>
 #include <string>
 #include <vector>
 
@@ -41,6 +42,9 @@ struct DeviceState
     // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t pipe_events[10] = {};
+    // sharded GEMM: side stream on which most of B is split while the first column panel multiplies
+    cudaStream_t prep_stream = nullptr;
+    cudaEvent_t prep_fork = nullptr, prep_join = nullptr;
     void* trsm_buf = nullptr;             // TRSM: inverted diagonal blocks + one block row/column of temporaries
     size_t trsm_bytes = 0;
     void* group_buf = nullptr;            // device copy of the grouped-launch problem list
@@ -87,6 +91,7 @@ struct sushi_cuda_ctx
     bool timing = false;
     int fuse_split = 1;                   // in-kernel split of k-contiguous operands: 0 never, 1 by shape, 2 always
     bool stream_k = true;                 // cut the tiles of a partial round along K (SUSHI_SPLIT_K=0 disables)
+    bool panel_pipeline = true;           // sharded GEMM: split most of B under the first column panel (SUSHI_PANEL_PIPELINE=0 disables)
     // multi-GPU (one process per GPU: a single communicator bound to one device index)
     ncclComm_t comm = nullptr;
     int comm_dev = -1, nranks = 1, rank = 0;
@@ -329,6 +334,80 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     return SUSHI_CUDA_OK;
 }
 
+// One row block times all of B on the tensor path, as two column panels: panel 0 is sized to whole
+// rounds of the persistent grid (tile columns in multiples of SMs / gcd(SMs, tile rows)) and long
+// enough to cover the split of the rest of B, which runs on a side stream meanwhile.  In the sharded
+// GEMM B is replicated, so its pre-pass is the part of a step that does not shrink with the number
+// of GPUs; this takes most of it off the critical path.  The side stream starts after everything
+// queued on the caller's stream before this call (B may have been produced there) and the second
+// GEMM waits for it.  Returns 1 when the shape does not suit the scheme (the caller then uses
+// run_gemm), 0 on success, a negative error otherwise.
+int run_gemm_two_panels(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t rows, int64_t n, int64_t k, float alpha,
+                        const float* a, int64_t lda, const float* b, int64_t ldb, float beta, float* c, int64_t ldc,
+                        float* const* peer_c, int n_peers)
+{
+    if (rows <= 0 || n <= 0 || k <= 0 || alpha == 0.0f) return 1;
+    const bool want_b = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && rows <= 2048);
+    if (want_b && tb && sushi::tc3x::raw_eligible(b, n, k, ldb, 0, 1)) return 1;       // B needs no pre-pass
+    const int64_t tiles_m = (rows + 255) / 256, tiles_n = (n + 255) / 256;
+    const int64_t unit = d.sm_count / std::gcd((int64_t)d.sm_count, tiles_m);           // tile columns per whole round
+    int64_t cols0 = 0;
+    for (int64_t tc = unit; tc * 2 <= tiles_n; tc += unit)
+    {
+        // GEMM of panel 0 (~235 TFLOP/s) against the split of the rest (12 B per element at ~4.5 TB/s)
+        const int64_t n0 = tc * 256;
+        if (rows * n0 >= 400 * (n - n0)) { cols0 = n0; break; }
+    }
+    if (cols0 == 0 || (n - cols0 + 255) / 256 * tiles_m < d.sm_count) return 1;
+    SC_CUDA(ctx, cudaSetDevice(d.device));
+    if (!d.prep_stream)
+    {
+        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d.prep_stream, cudaStreamNonBlocking));
+        SC_CUDA(ctx, cudaEventCreateWithFlags(&d.prep_fork, cudaEventDisableTiming));
+        SC_CUDA(ctx, cudaEventCreateWithFlags(&d.prep_join, cudaEventDisableTiming));
+    }
+    const bool want_a = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && n <= 2048);
+    const bool fuse_a = want_a && !ta && sushi::tc3x::raw_eligible(a, rows, k, lda, 0, 1);
+    const size_t bytes_b0 = sushi::split_plane_bytes(cols0, k, 1), bytes_b1 = sushi::split_plane_bytes(n - cols0, k, 1);
+    const size_t bytes_a = fuse_a ? 0 : sushi::split_plane_bytes(rows, k, 1);
+    int rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_b0 + bytes_b1 + bytes_a);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    float* planes_b0 = static_cast<float*>(d.workspace);
+    float* planes_b1 = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b0);
+    float* planes_a = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b0 + bytes_b1);
+    // column `col` of op(B): op(B)^T row `col`
+    const float* b1 = tb ? b + cols0 * ldb : b + cols0;
+
+    SC_CUDA(ctx, cudaEventRecord(d.prep_fork, d.stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d.prep_stream, d.prep_fork, 0));
+    SC_CUDA(ctx, sushi::launch_split_tf32(b1, planes_b1, n - cols0, k, ldb, 0, 1, /*k_contig=*/tb != 0, d.sm_count, d.prep_stream));
+    SC_CUDA(ctx, cudaEventRecord(d.prep_join, d.prep_stream));
+
+    if ((rc = timing_mark(ctx, d, 0, fuse_a ? 1 : 2)) != SUSHI_CUDA_OK) return rc;
+    if (!fuse_a) SC_CUDA(ctx, sushi::launch_split_tf32(a, planes_a, rows, k, lda, 0, 1, /*k_contig=*/!ta, d.sm_count, d.stream));
+    SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b0, cols0, k, ldb, 0, 1, /*k_contig=*/tb != 0, d.sm_count, d.stream));
+    sushi::tc3x::OperandSource src_a, src_b;
+    if (fuse_a) { src_a.raw = a; src_a.ld = lda; src_a.stride = 0; } else src_a.planes = planes_a;
+    float* peers[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    for (int i = 0; i < n_peers && i < 7; ++i) peers[i] = peer_c[i];
+    src_b.planes = planes_b0;
+    if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, rows, cols0, k, ldc, 0, 1, alpha, beta, d.status, d.sm_count,
+                                               d.stream, nullptr, 0, n_peers ? peers : nullptr, n_peers));
+    if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
+
+    SC_CUDA(ctx, cudaStreamWaitEvent(d.stream, d.prep_join, 0));
+    for (int i = 0; i < n_peers && i < 7; ++i) peers[i] = peer_c[i] + cols0;
+    src_b.planes = planes_b1;
+    if ((rc = timing_mark(ctx, d, 0, 1)) != SUSHI_CUDA_OK) return rc;
+    if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c + cols0, rows, n - cols0, k, ldc, 0, 1, alpha, beta, d.status,
+                                               d.sm_count, d.stream, nullptr, 0, n_peers ? peers : nullptr, n_peers));
+    if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
+    ctx->launches += (fuse_a ? 0 : 1) + 4;
+    return SUSHI_CUDA_OK;
+}
+
 bool load_nccl(std::string* err)
 {
     std::lock_guard<std::mutex> lock(g_nccl_mutex);
@@ -424,6 +503,7 @@ extern "C" int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx
     sushi_cuda_ctx* ctx = new sushi_cuda_ctx();
     ctx->variant = check_variant_env(SUSHI_GEMM_AUTO);
     if (const char* e = getenv("SUSHI_SPLIT_K")) ctx->stream_k = atoi(e) != 0;
+    if (const char* e = getenv("SUSHI_PANEL_PIPELINE")) ctx->panel_pipeline = atoi(e) != 0;
     if (const char* e = getenv("SUSHI_FUSE_SPLIT")) ctx->fuse_split = atoi(e);
     for (int id : ids)
     {
@@ -479,6 +559,9 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         if (d.status_host) cudaFreeHost(d.status_host);
         for (cudaEvent_t e : d.timing_events) cudaEventDestroy(e);
         if (d.copy_in) { cudaStreamSynchronize(d.copy_in); cudaStreamDestroy(d.copy_in); }
+        if (d.prep_stream) { cudaStreamSynchronize(d.prep_stream); cudaStreamDestroy(d.prep_stream); }
+        if (d.prep_fork) cudaEventDestroy(d.prep_fork);
+        if (d.prep_join) cudaEventDestroy(d.prep_join);
         if (d.copy_out) { cudaStreamSynchronize(d.copy_out); cudaStreamDestroy(d.copy_out); }
         for (cudaEvent_t e : d.pipe_events) if (e) cudaEventDestroy(e);
         if (d.own_stream) cudaStreamDestroy(d.own_stream);
@@ -1325,8 +1408,18 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     if (do_gather && ldc != n)
         return set_error(ctx, SUSHI_CUDA_ERR_UNSUPPORTED, "sgemm_row_sharded: gathering needs ldc == n");
     float* c_block = c_full + first * ldc;
+    const bool tensor_block = ctx->variant == SUSHI_GEMM_TC3X ||
+                              (ctx->variant == SUSHI_GEMM_AUTO && count > 0 && prefer_tc3x(count, n, k, 1, d->sm_count));
     if (!do_gather)
+    {
+        if (tensor_block && ctx->panel_pipeline)
+        {
+            rc = run_gemm_two_panels(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, b, ldb, beta, c_block, ldc,
+                                     nullptr, 0);
+            if (rc <= 0) return rc;
+        }
         return run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1);
+    }
 
     // Fused exchange: one launch over the whole block; the epilogue stores C tiles to the peers.
     const bool tensor_path = ctx->variant == SUSHI_GEMM_TC3X ||
@@ -1343,8 +1436,13 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
         fused.variant = SUSHI_GEMM_TC3X;
         for (int r = 0; r < nranks; ++r)
             if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * ldc;
-        rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
-                      &fused);
+        rc = 1;
+        if (ctx->panel_pipeline)
+            rc = run_gemm_two_panels(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, b, ldb, beta, c_block, ldc,
+                                     fused.peer_c, fused.n_peers);
+        if (rc > 0)
+            rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
+                          &fused);
         if (rc != SUSHI_CUDA_OK) return rc;
         // barrier 2: every rank's kernel (and with it its stores into this rank's buffer) is complete
         SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));

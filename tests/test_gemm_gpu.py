@@ -573,6 +573,38 @@ def test_bounded_wait_expiry_reaches_the_host_and_context_survives(ctx):
         ctx.selftest_bounded_wait(100000)        # limit out of range is rejected, nothing is launched
 
 
+def test_row_block_in_two_column_panels_matches_single_call(ctx):
+    """The sharded entry point multiplies a row block in two column panels (the split of most of B
+    runs on a side stream under the first panel's GEMM).  Same kernels, same per-tile arithmetic:
+    the result must equal the plain call bit for bit, in every transpose, with alpha / beta."""
+    m, n, k = 1024, 18944 + 256, 272          # 4 tile rows -> panels of 37 tile columns; ragged k
+    for ta, tb in [(0, 0), (0, 1), (1, 0), (1, 1)]:
+        a = og.uniform_pm1(700 + ta, m * k)
+        b = og.uniform_pm1(710 + tb, k * n)
+        c0 = og.uniform_pm1(720, m * n)
+        da, db = dev(a), dev(b)
+        lda, ldb = (m if ta else k), (k if tb else n)
+        c1, c2 = dev(c0), dev(c0)
+        ctx.set_gemm_variant(TC3X)
+        before = ctx.launch_count()
+        ctx.sgemm_row_sharded(ta, tb, m, n, k, 1.5, da, lda, db, ldb, 0.5, c1, n, gather=0)
+        sharded_launches = ctx.launch_count() - before
+        ctx.sgemm(ta, tb, m, n, k, 1.5, da, lda, db, ldb, 0.5, c2, n)
+        ctx.sync()
+        ctx.set_gemm_variant(AUTO)
+        if not (tb and m <= 2048):             # B split inside the kernel: nothing to pipeline
+            assert sharded_launches >= 4, (ta, tb, sharded_launches)      # two B splits and two GEMMs at least
+        assert torch.equal(c1, c2), (ta, tb)
+        rows = np.array([0, 255, 256, 1023])
+        got = c1.cpu().numpy().reshape(m, n)[rows]
+        av = a.reshape(k, m).T if ta else a.reshape(m, k)
+        bv = b.reshape(n, k).T if tb else b.reshape(k, n)
+        ref = 1.5 * (av[rows].astype(np.float64) @ bv.astype(np.float64)) + 0.5 * c0.reshape(m, n)[rows]
+        absab = np.abs(av[rows]).astype(np.float64) @ np.abs(bv).astype(np.float64)
+        r, _ = og.tolerance_ratio(got[None], ref[None], absab[None], k, beta=0.5, c_in=c0.reshape(m, n)[rows][None], budget=BUDGET)
+        assert r <= 1.0, (ta, tb, r)
+
+
 def test_launch_counter_counts_kernels(ctx):
     before = ctx.launch_count()
     check(ctx, SIMT, 0, 0, 64, 64, 64, 1.0, 0.0)
