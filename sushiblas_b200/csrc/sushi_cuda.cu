@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "sgemm_simt.cuh"
+#include "sgemm_skinny.cuh"
 #include "split_tf32.cuh"
 #include "sgemm_tc3x.cuh"
 #include "trsm_blocks.cuh"
@@ -91,6 +92,7 @@ struct sushi_cuda_ctx
     bool timing = false;
     int fuse_split = 1;                   // in-kernel split of k-contiguous operands: 0 never, 1 by shape, 2 always
     bool stream_k = true;                 // cut the tiles of a partial round along K (SUSHI_SPLIT_K=0 disables)
+    bool skinny = true;                   // tall-and-skinny kernel for n <= 32 (SUSHI_SKINNY=0 disables)
     bool panel_pipeline = true;           // sharded GEMM: split most of B under the first column panel (SUSHI_PANEL_PIPELINE=0 disables)
     // multi-GPU (one process per GPU: a single communicator bound to one device index)
     ncclComm_t comm = nullptr;
@@ -321,6 +323,21 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         return SUSHI_CUDA_OK;
     }
 
+    // tall-and-skinny products are bound by reading A once: their own kernel (same arithmetic class)
+    if (tri == 0 && ctx->skinny && batch <= 65535 && sushi::skinny_eligible(ta, m, n, k, a, lda, sa))
+    {
+        sushi::SkinnyArgs q;
+        q.a = a; q.b = b; q.c = c; q.m = m; q.n = n; q.k = k; q.lda = lda; q.ldb = ldb; q.ldc = ldc;
+        q.stride_a = sa; q.stride_b = sb; q.stride_c = sc; q.row_blocks = 0; q.alpha = alpha; q.beta = beta;
+        q.trans_b = tb != 0; q.relu = relu ? 1 : 0;
+        int rcs = timing_mark(ctx, d, 0, 0);
+        if (rcs == SUSHI_CUDA_OK) rcs = timing_mark(ctx, d, 1, 0);
+        if (rcs != SUSHI_CUDA_OK) return rcs;
+        SC_CUDA(ctx, sushi::launch_sgemm_skinny(q, batch, d.sm_count, d.stream));
+        if ((rcs = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rcs;
+        ctx->launches++;
+        return SUSHI_CUDA_OK;
+    }
     sushi::SimtGemmArgs g;
     g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
     g.stride_a = sa; g.stride_b = sb; g.stride_c = sc; g.tiles_m = 0; g.tiles_n = 0;
@@ -504,6 +521,7 @@ extern "C" int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx
     ctx->variant = check_variant_env(SUSHI_GEMM_AUTO);
     if (const char* e = getenv("SUSHI_SPLIT_K")) ctx->stream_k = atoi(e) != 0;
     if (const char* e = getenv("SUSHI_PANEL_PIPELINE")) ctx->panel_pipeline = atoi(e) != 0;
+    if (const char* e = getenv("SUSHI_SKINNY")) ctx->skinny = atoi(e) != 0;
     if (const char* e = getenv("SUSHI_FUSE_SPLIT")) ctx->fuse_split = atoi(e);
     for (int id : ids)
     {

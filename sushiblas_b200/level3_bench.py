@@ -1,10 +1,11 @@
-"""Timing of the Level-3 rows next to the fp32 GEMM: fp64 GEMM, TRSM, SYRK.
+"""Timing of the Level-3 rows next to the fp32 GEMM: fp64 GEMM, TRSM, SYRK, and of a deliberately
+bandwidth-bound fp32 GEMM shape (65536 x 16 x 256, served by the FFMA kernel).
 
-    python -m sushiblas_b200.level3_bench [--op dgemm|strsm|ssyrk|all] [--size N] [--steps K] [--warmup W] [--library]
+    python -m sushiblas_b200.level3_bench [--op dgemm|strsm|ssyrk|skinny|all] [--size N] [--steps K] [--warmup W] [--library]
 
 One JSON line per (op, case): CUDA-event time of each call on the launching stream (median and
 best of K calls after W warm-up calls), inputs resident in HBM, L2 flushed between calls by
-writing a 256 MiB buffer.  `--library` adds the time of torch's own routine for the same problem
+writing and re-reading a 256 MiB buffer.  `--library` adds the time of torch's own routine for the same problem
 (cuBLAS) on the same GPU as context; it is not part of the product path.  Needs a CUDA device:
 there is no CPU fallback.
 """
@@ -12,7 +13,17 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
+
+
+def _hbm_peak_gbs():
+    """Measured copy bandwidth of this pool's GPUs when the file is present, else the documented fallback."""
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
 
 
 def _time_calls(torch, stream, fn, reset, flush, steps, warmup):
@@ -32,7 +43,7 @@ def _time_calls(torch, stream, fn, reset, flush, steps, warmup):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["dgemm", "strsm", "ssyrk", "all"])
+    ap.add_argument("--op", default="all", choices=["dgemm", "strsm", "ssyrk", "skinny", "all"])
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -52,7 +63,10 @@ def main(argv=None):
     scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def flush():
+        # write a buffer twice the size of L2, then read it back: the write displaces the operands,
+        # the read leaves L2 full of clean lines, so the timed call does not pay for write-backs
         scrub.fill_(1)
+        scrub.max()
 
     def emit(op, case, flops, med, best, lib_ms, extra=None):
         line = {"op": op, "case": case, "size": n, "ms_median": round(med, 4), "ms_best": round(best, 4),
@@ -94,6 +108,26 @@ def main(argv=None):
             emit("strsm", f"{'left' if left else 'right'}/{'upper' if upper else 'lower'}/{'T' if trans else 'N'}",
                  1.0 * n * n * n, med, best, lib, {"dtype": "f32"})
         del a, b, b0
+
+    if args.op in ("skinny", "all"):
+        # AI = 7.5 flop / byte: far below the ridge of either roofline, so HBM bounds it
+        m_, n_, k_ = 65536, 16, 256
+        a = torch.rand(m_, k_, device="cuda")
+        b = torch.rand(k_, n_, device="cuda")
+        c = torch.zeros(m_, n_, device="cuda")
+        med, best = _time_calls(torch, stream, lambda: ctx.sgemm(0, 0, m_, n_, k_, 1.0, a, k_, b, n_, 0.0, c, n_),
+                                lambda: None, flush, args.steps, args.warmup)
+        lib = None
+        if args.library:
+            lib, _ = _time_calls(torch, stream, lambda: torch.mm(a, b, out=c), lambda: None, flush, args.steps, args.warmup)
+        alg_bytes = 4.0 * (m_ * k_ + k_ * n_ + m_ * n_)
+        peak, src = _hbm_peak_gbs()
+        gbs = alg_bytes / (med * 1e-3) / 1e9
+        emit("sgemm", "65536x16x256 NN", 2.0 * m_ * n_ * k_, med, best, lib,
+             {"dtype": "f32", "size": None, "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                                                         "frac": round(gbs / peak, 4), "peak_source": src,
+                                                         "algorithmic_bytes": alg_bytes}})
+        del a, b, c
 
     if args.op in ("ssyrk", "all"):
         a = torch.rand(n, n, device="cuda")

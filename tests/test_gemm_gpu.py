@@ -573,6 +573,19 @@ def test_bounded_wait_expiry_reaches_the_host_and_context_survives(ctx):
         ctx.selftest_bounded_wait(100000)        # limit out of range is rejected, nothing is launched
 
 
+@pytest.mark.parametrize("tb", [0, 1])
+def test_tall_and_skinny_products(ctx, tb):
+    """n <= 32 with many rows goes to the streaming kernel (A read once, 8-way k split per row):
+    every column count class, ragged k chunks, padded leading dimensions, alpha / beta, batches."""
+    for (m, n, k) in [(4096, 16, 256), (2048, 1, 32), (5000, 5, 100), (3000, 8, 516), (2500, 17, 260), (2049, 32, 1028)]:
+        for (alpha, beta) in [(1.0, 0.0), (1.5, 0.5)]:
+            check(ctx, AUTO, 0, tb, m, n, k, alpha, beta, seed=800 + n + k)
+    check(ctx, AUTO, 0, tb, 4100, 12, 132, -1.0, 1.0, batch=3, pad=(4, 3, 5), seed=850)
+    check(ctx, AUTO, 0, tb, 2048, 16, 64, 1.0, 0.0, seed=851, poison_c=True)     # beta == 0: C is not read
+    # unaligned leading dimension of A: the tiled kernel serves it, same answer class
+    check(ctx, AUTO, 0, tb, 2100, 16, 64, 1.0, 0.5, pad=(1, 0, 0), seed=852)
+
+
 def test_row_block_in_two_column_panels_matches_single_call(ctx):
     """The sharded entry point multiplies a row block in two column panels (the split of most of B
     runs on a side stream under the first panel's GEMM).  Same kernels, same per-tile arithmetic:
