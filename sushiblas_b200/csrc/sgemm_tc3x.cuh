@@ -39,7 +39,10 @@
 // the last slice owns the tile: it acquires the flags, adds the slots and applies alpha/beta.
 // Publishing never waits, an owner only waits for items dealt before its own, and the grid never
 // exceeds the SM count, so the exchange cannot deadlock; the flag wait is bounded like every
-// other wait.
+// other wait.  With so few tiles that S slices of every tile fit the grid at one item per CTA
+// (S = 2, 4, 8, 16), the finish is cooperative instead: every slice publishes, then each CTA waits
+// for the S flags of its tile and adds and stores rows [q, q+1) * 256/S of it -- every CTA reads
+// 256 KB whatever S is, where a single owner would read (S-1) * 256 KB through one SM.
 //
 // Every wait in this kernel is bounded: on expiry the waiter records a code in *status,
 // raises a CTA-wide abort flag, every role leaves its loop, in-flight copies and MMAs are
@@ -74,7 +77,8 @@ enum : int { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA_FULL = 2, ST_TIM
              ST_TIMEOUT_EPILOGUE = 4, ST_TIMEOUT_PARTIAL_FLAG = 5, ST_TIMEOUT_PARTIAL_PUBLISH = 6, ST_TIMEOUT_CONVERT = 7, ST_SELFTEST = 99 };
 
 constexpr int SK_SLOT_FLOATS = BM * BN;               // one raw accumulator tile per published slice
-constexpr int SK_MAX_SPLIT = 4;                       // at most this many K slices per tile
+constexpr int SK_MAX_SPLIT = 4;                       // at most this many K slices per tile (owner scheme)
+constexpr int SK_COOP_MAX_SPLIT = 16;                 // cooperative scheme: S in {2, 4, 8, 16}
 constexpr size_t SK_FLAG_BYTES = 16384;              // flag region at the head of the exchange area
 constexpr int SK_MIN_KB = 8;                          // and each slice is at least this many k-blocks
 
@@ -95,11 +99,12 @@ struct Params
     int64_t dp_tiles;              // tiles [0, dp_tiles) are dealt whole, round-robin over the grid
     int32_t sk_tiles;              // tiles [dp_tiles, dp_tiles + sk_tiles) are cut along K (0: none)
     int32_t sk_split;              // number of K slices per cut tile (>= 2 when sk_tiles > 0)
+    int32_t sk_coop;               // 1: every slice publishes and each CTA finishes its own band of rows of the tile
     int32_t n_peers;               // fused all-gather: finished tiles are also stored to peer_c[0 .. n_peers)
     float* peer_c[7];              // the address of `c` inside each peer GPU's buffer
     int32_t raw_mask;              // bit 0: A arrives raw (split in kernel); bit 1: B arrives raw
-    float* sk_partials;            // [sk_tiles * (sk_split-1)][256*256] raw accumulators of slices 0 .. S-2
-    unsigned int* sk_flags;        // [sk_tiles * (sk_split-1)] epoch of the slot's last publication
+    float* sk_partials;            // [sk_tiles * (sk_split-1)][256*256] raw accumulators of slices 0 .. S-2 (all S when sk_coop)
+    unsigned int* sk_flags;        // one per slot: epoch of the slot's last publication
     unsigned int sk_epoch;         // this launch's epoch (never 0)
 };
 
@@ -108,8 +113,9 @@ struct WorkItem
 {
     int64_t tile;
     int32_t kb0, kb1;
-    int32_t kind;                  // 0 whole tile; 1 slice that publishes a partial; 2 last slice: owner of a cut tile
-    int32_t slot;                  // kind 1: slot to publish; kind 2: slot of slice 0 (slice q at slot + q*sk_tiles)
+    int32_t kind;                  // 0 whole tile; 1 slice that publishes a partial; 2 last slice: owner of a cut tile;
+                                   // 3 slice that publishes and then finishes rows [q, q+1) * 256/S of the tile
+    int32_t slot;                  // kind 1, 3: slot to publish (q*sk_tiles + t); kind 2: slot of slice 0 (slice q at slot + q*sk_tiles)
 };
 
 // idx-th work item of CTA `cta` (identical enumeration in every role); false when exhausted.
@@ -126,7 +132,8 @@ __device__ __forceinline__ bool get_work_item(const Params& p, int32_t cta, int3
     w.tile = p.dp_tiles + t;
     w.kb0 = (int32_t)((int64_t)q * p.num_kb / p.sk_split);
     w.kb1 = (int32_t)((int64_t)(q + 1) * p.num_kb / p.sk_split);
-    if (q == p.sk_split - 1) { w.kind = 2; w.slot = t; }
+    if (p.sk_coop) { w.kind = 3; w.slot = q * p.sk_tiles + t; }
+    else if (q == p.sk_split - 1) { w.kind = 2; w.slot = t; }
     else { w.kind = 1; w.slot = q * p.sk_tiles + t; }
     return true;
 }
@@ -184,6 +191,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// Bounded wait for a slot's publication flag (acquire).  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool flag_wait_bounded(const unsigned int* flag, unsigned int epoch, volatile int* abort_flag,
+                                                  int* status, int code, unsigned long long limit_ns);
+
 // Bounded wait.  Returns false when the CTA is aborting (own expiry or someone else's).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code, unsigned long long limit_ns)
@@ -205,6 +216,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
             }
         }
     }
+}
+
+__device__ __forceinline__ bool flag_wait_bounded(const unsigned int* flag, unsigned int epoch, volatile int* abort_flag,
+                                                  int* status, int code, unsigned long long limit_ns)
+{
+    if (ld_acquire_gpu(flag) == epoch) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (ld_acquire_gpu(flag) != epoch)
+    {
+        if (((++spins) & 0x3F) == 0)
+        {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > limit_ns)
+            {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -637,7 +670,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int64_t col_base = (int64_t)tc.tn * BN;
             const bool vec_ok = ((p.ldc & 3) == 0) && ((p.stride_c & 3) == 0) &&
                                 ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0);
-            const bool partial = (w.kind == 1);
+            const bool partial = (w.kind == 1 || w.kind == 3);
             // slot element of (tile row, tile col): row-major 256 x 256
             float* my_slot = partial ? p.sk_partials + (size_t)w.slot * SK_SLOT_FLOATS : nullptr;
             const int slot_row0 = h * 128 + q * 32;
@@ -836,6 +869,89 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 ++published;
             }
+
+            if (w.kind == 3)
+            {
+                // Cooperative finish: when all S slices of the tile are published, this CTA adds rows
+                // [q, q+1) * 256/S of the S slots (always in slot order, so the sum does not depend on
+                // timing) and applies alpha / beta: every CTA reads 256 KB whatever S is, instead of one
+                // owner reading (S-1) * 256 KB.  All S CTAs of a tile are co-resident (the plan deals at
+                // most one item per CTA), nobody waits before publishing, and the waits are bounded.
+                int okc = 1;
+                const int32_t t_idx = w.slot % p.sk_tiles, q_idx = w.slot / p.sk_tiles;
+                for (int32_t c = 0; c < p.sk_split && okc; ++c)
+                    okc = flag_wait_bounded(p.sk_flags + (c * p.sk_tiles + t_idx), p.sk_epoch, abort_flag, p.status,
+                                            ST_TIMEOUT_PARTIAL_FLAG, WAIT_LIMIT_NS) ? 1 : 0;
+                ok = __all_sync(0xffffffffu, okc) != 0;
+                if (!ok) break;
+                const int band = BM / p.sk_split, rows_per_warp = band / 8;      // S in {2, 4, 8, 16}
+                const float* slot0 = p.sk_partials + (size_t)t_idx * SK_SLOT_FLOATS;
+                const size_t cstride = (size_t)p.sk_tiles * SK_SLOT_FLOATS;
+                for (int i = 0; i < rows_per_warp; ++i)
+                {
+                    const int trow = q_idx * band + ew * rows_per_warp + i;      // row inside the tile
+                    const int64_t grow = (int64_t)tc.tm * BM + trow;
+                    if (grow >= p.m) break;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                    {
+                        const int col4 = lane + 32 * half;
+                        const int64_t gcol = col_base + col4 * 4;
+                        const float* src = slot0 + (size_t)trow * BN + col4 * 4;
+                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int32_t c0 = 0; c0 < p.sk_split; c0 += 8)
+                        {
+                            float4 t4[8];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c)
+                                if (c0 + c < p.sk_split) t4[c] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(c0 + c) * cstride));
+#pragma unroll
+                            for (int c = 0; c < 8; ++c)
+                                if (c0 + c < p.sk_split) { sum.x += t4[c].x; sum.y += t4[c].y; sum.z += t4[c].z; sum.w += t4[c].w; }
+                        }
+                        if (gcol >= p.n) continue;
+                        float* dst = cb + grow * p.ldc + gcol;
+                        const bool tri_all = p.tri == 0 || (p.tri == 1 ? gcol + 3 <= grow : gcol >= grow);
+                        if (vec_ok && gcol + 3 < p.n && tri_all)
+                        {
+                            float4 o;
+                            o.x = p.alpha * sum.x; o.y = p.alpha * sum.y; o.z = p.alpha * sum.z; o.w = p.alpha * sum.w;
+                            if (has_beta)
+                            {
+                                const float4 old = *reinterpret_cast<const float4*>(dst);
+                                o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
+                                o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
+                            }
+                            if (p.relu)
+                            {
+                                o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+                            }
+                            *reinterpret_cast<float4*>(dst) = o;
+                            for (int32_t peer = 0; peer < p.n_peers; ++peer)
+                                *reinterpret_cast<float4*>(p.peer_c[peer] + tc.bi * p.stride_c + grow * p.ldc + gcol) = o;
+                        }
+                        else
+                        {
+                            const float av[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                            {
+                                const bool inside = p.tri == 0 || (p.tri == 1 ? gcol + j <= grow : gcol + j >= grow);
+                                if (gcol + j < p.n && inside)
+                                {
+                                    float o = p.alpha * av[j];
+                                    if (has_beta) o = fmaf(p.beta, dst[j], o);
+                                    o = p.relu ? fmaxf(o, 0.0f) : o;
+                                    dst[j] = o;
+                                    for (int32_t peer = 0; peer < p.n_peers; ++peer)
+                                        p.peer_c[peer][tc.bi * p.stride_c + grow * p.ldc + gcol + j] = o;
+                                }
+                            }
+                        }
+                    }
+                }
+                if (p.n_peers > 0) __threadfence_system();
+            }
         }
     }
 
@@ -899,14 +1015,27 @@ inline bool make_plane_map(CUtensorMap* map, const float* planes, int64_t rows_p
 }
 
 // Split-K tail plan for `tiles` tiles on `sm_count` SMs (see the header comment).
-struct TailPlan { int64_t dp_tiles; int32_t sk_tiles, sk_split; int64_t grid; };
+struct TailPlan { int64_t dp_tiles; int32_t sk_tiles, sk_split; int64_t grid; int32_t coop; };
 
 inline TailPlan plan_tail(int64_t tiles, int64_t num_kb, int sm_count, bool allow_split)
 {
-    TailPlan t{tiles, 0, 1, tiles < sm_count ? tiles : sm_count};
+    TailPlan t{tiles, 0, 1, tiles < sm_count ? tiles : sm_count, 0};
     // With at least one tile per SM the tail is not cut: measured on B200 (power-capped clocks,
     // fix-up traffic) the gain of a balanced last round does not cover the exchange.
     if (!allow_split || tiles <= 0 || tiles >= sm_count) return t;
+    // Few tiles: cut K in S = 2, 4, 8 or 16 slices with one slice per CTA (all co-resident) and let
+    // every CTA finish its own band of rows.  The exchange then costs a fixed ~7 us (256 KB written
+    // and 256 KB read per CTA) whatever S is, so the largest S that fits the grid wins as long as a
+    // slice keeps a few k-blocks: slice main loop 0.9 us per k-block against the fixed cost.
+    {
+        int s = 1;
+        while (s * 2 <= SK_COOP_MAX_SPLIT && tiles * (s * 2) <= sm_count && num_kb / (s * 2) >= SK_MIN_KB) s *= 2;
+        if (s >= 2 && (double)num_kb * 0.9 * (1.0 - 1.0 / s) > 8.0)
+        {
+            t.dp_tiles = 0; t.sk_tiles = (int32_t)tiles; t.sk_split = s; t.grid = tiles * s; t.coop = 1;
+            return t;
+        }
+    }
     // Cost in units of one whole-tile main loop: rounds/S plus the fix-up, which is a fixed
     // time per published slice (slot write + owner's read) and so weighs 7/num_kb of a tile.
     int best_s = 1;
@@ -928,7 +1057,7 @@ inline TailPlan plan_tail(int64_t tiles, int64_t num_kb, int sm_count, bool allo
 // The flag region must be zero-filled when the area is allocated.
 inline size_t sk_area_bytes(const TailPlan& t)
 {
-    const size_t slots = (size_t)t.sk_tiles * (size_t)(t.sk_split - 1);
+    const size_t slots = (size_t)t.sk_tiles * (size_t)(t.coop ? t.sk_split : t.sk_split - 1);
     return slots ? SK_FLAG_BYTES + slots * (SK_SLOT_FLOATS * sizeof(float)) : 0;
 }
 
@@ -1013,7 +1142,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.alpha = alpha; p.beta = beta; p.status = status; p.relu = relu ? 1 : 0; p.tri = tri;
     p.lean_epilogue = lean_epilogue_enabled() ? 1 : 0;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
-    p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split;
+    p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split; p.sk_coop = plan.coop;
     p.sk_flags = static_cast<unsigned int*>(sk_area);
     p.sk_partials = sk_area ? reinterpret_cast<float*>(static_cast<char*>(sk_area) + SK_FLAG_BYTES) : nullptr;
     p.sk_epoch = sk_epoch;

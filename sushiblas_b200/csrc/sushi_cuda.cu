@@ -175,15 +175,25 @@ int validate_gemm(sushi_cuda_ctx* ctx, int64_t m, int64_t n, int64_t k, const vo
 
 // Kernel choice for SUSHI_GEMM_AUTO: the tensor-core path pays a pre-pass and works in
 // 256 x 256 tiles, so it needs enough k to amortise the split and enough tiles to occupy SMs.
-bool prefer_tc3x(int64_t m, int64_t n, int64_t k, int64_t batch, int sm_count)
+bool prefer_tc3x(int64_t m, int64_t n, int64_t k, int64_t batch, int sm_count, bool allow_split = true)
 {
     if (k < 128 || m < 128 || n < 128) return false;
-    const double tiles = (double)((m + 255) / 256) * (double)((n + 255) / 256) * (double)batch;
-    const double waves = tiles <= sm_count ? 1.0 : (double)((int64_t)(tiles + sm_count - 1) / sm_count);
-    // tensor path: 1536 clk per 16-k block per tile (+ pre-pass ~ 12 B per operand element at 5 TB/s)
-    const double t_tc = waves * ((double)((k + 15) / 16) * 1536.0 / 1.5e9) +
-                        12.0 * (double)batch * (double)k * (double)(m + n) / 5.0e12 + 6e-6;
-    const double t_simt = 2.0 * (double)m * (double)n * (double)k * (double)batch / 25.0e12 + 3e-6;
+    const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256) * batch;
+    const int64_t num_kb = (k + 15) / 16;
+    // tensor path: ~1 us per 16-k block of a 256 x 256 tile; few tiles are cut along K (plan_tail), which
+    // adds a fixed exchange; pre-pass ~ 12 B per operand element at 5 TB/s; launches and epilogue ~ 12 us
+    const sushi::tc3x::TailPlan plan = sushi::tc3x::plan_tail(tiles, num_kb, sm_count, allow_split);
+    const int64_t items = plan.sk_split > 1 ? tiles * plan.sk_split : tiles;
+    const double rounds = (double)((items + sm_count - 1) / sm_count);
+    const double kb_item = (double)((num_kb + plan.sk_split - 1) / plan.sk_split);
+    const double t_tc = rounds * kb_item * 1.02e-6 + (plan.sk_split > 1 ? 8e-6 : 0.0) +
+                        12.0 * (double)batch * (double)k * (double)(m + n) / 5.0e12 + 12e-6;
+    // FFMA path (measured): 128 x 128 tiles at ~0.2 TFLOP/s per SM when they fill the GPU, else 64 x 64 tiles at ~0.1
+    const int64_t big = ((m + 127) / 128) * ((n + 127) / 128) * batch;
+    const int64_t edge = big >= sm_count ? 128 : 64;
+    const int64_t simt_tiles = ((m + edge - 1) / edge) * ((n + edge - 1) / edge) * batch;
+    const double t_simt = (double)((simt_tiles + sm_count - 1) / sm_count) * (2.0 * edge * edge * (double)k) /
+                          (edge == 128 ? 0.2e12 : 0.1e12) + 3e-6;
     return t_tc < t_simt;
 }
 
@@ -249,7 +259,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     }
     int variant = (reuse && reuse->variant >= 0) ? reuse->variant : ctx->variant;
     if (variant == SUSHI_GEMM_AUTO)
-        variant = prefer_tc3x(m, n, k, batch, d.sm_count) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+        variant = prefer_tc3x(m, n, k, batch, d.sm_count, ctx->stream_k) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
     if (reuse) reuse->variant = variant;
 
     if (variant == SUSHI_GEMM_TC3X)

@@ -203,7 +203,10 @@ def test_tc3x_split_k_tail_integer_exact(ctx):
     rng = np.random.default_rng(99)
     for (batch, m, n, k, ta, tb, alpha, beta) in [(1, 1024, 768, 512, 0, 0, 1.0, 0.0), (1, 512, 512, 2048, 1, 0, 2.0, 1.0),
                                                    (3, 512, 256, 384, 0, 1, 1.0, -1.0), (1, 2048, 2048, 1024, 0, 0, 1.0, 0.0),
-                                                   (1, 300, 700, 1000, 1, 1, -1.0, 1.0)]:
+                                                   (1, 300, 700, 1000, 1, 1, -1.0, 1.0),
+                                                   # one tile cut 16 ways, every CTA finishing 16 of its rows; ragged single tile
+                                                   (1, 256, 256, 4096, 0, 0, 1.0, 1.0), (1, 200, 250, 2100, 0, 1, 2.0, -1.0),
+                                                   (1, 1024, 1024, 1024, 0, 0, 1.0, 0.0), (2, 512, 768, 2048, 1, 0, 1.0, 1.0)]:
         ar, ac = (k, m) if ta else (m, k)
         br, bc = (n, k) if tb else (k, n)
         a = rng.integers(-3, 4, size=(batch, ar, ac)).astype(np.float32)
@@ -218,6 +221,18 @@ def test_tc3x_split_k_tail_integer_exact(ctx):
     # repeated launches reuse the exchange area with a new epoch each time
     for _ in range(5):
         check(ctx, TC3X, 0, 0, 1024, 1024, 640, 1.5, 0.5)
+    # the ReLU epilogue on a cut tile
+    m, n, k = 512, 512, 3000
+    a = rng.integers(-3, 4, size=(m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(k, n)).astype(np.float32)
+    c = rng.integers(-8, 9, size=(m, n)).astype(np.float32)
+    dc = dev(c)
+    ctx.set_gemm_variant(TC3X)
+    ctx.sgemm_strided_batched_ex(0, 0, m, n, k, 1.0, dev(a), k, 0, dev(b), n, 0, 1.0, dc, n, 0, 1, epilogue=1)
+    ctx.sync()
+    ctx.set_gemm_variant(AUTO)
+    want = np.maximum(a.astype(np.int64) @ b.astype(np.int64) + c, 0).astype(np.float32)
+    assert np.array_equal(dc.cpu().numpy(), want)
 
 
 def test_tc3x_in_kernel_split_paths(ctx):
