@@ -25,6 +25,12 @@
 // TMA swizzle is preserved), fence the generic-proxy writes towards the async proxy and arrive on
 // a per-stage "converted" barrier that the MMA warp then waits on instead of the TMA barrier.
 // This removes 12 B/element of pre-pass traffic and halves that operand's read traffic.
+// An operand stored the other way round (A transposed, B not transposed: the row index of the tile
+// is contiguous) is taken raw as well: its tile arrives as eight dense boxes of 32 rows x 16 k, box
+// g in the 2 KB of the lo slot that converter warp g rewrites, and that warp transposes while it
+// splits -- a lane reads the 16 k values of one row (conflict-free) and writes the row's 64 bytes of
+// hi and lo at the positions TMA's SWIZZLE_64B would have used.  The read-before-write hazard
+// stays inside one warp, so no cross-warp synchronisation is added.
 //
 // Why 256 x 256: with both planes of both operands streamed per k-block, a CTA moves
 // 8*(BM+BN) bytes per 3*BM*BN tensor-core MACs; 256 x 256 keeps that at ~43 B/clk/SM of L2
@@ -102,7 +108,9 @@ struct Params
     int32_t sk_coop;               // 1: every slice publishes and each CTA finishes its own band of rows of the tile
     int32_t n_peers;               // fused all-gather: finished tiles are also stored to peer_c[0 .. n_peers)
     float* peer_c[7];              // the address of `c` inside each peer GPU's buffer
-    int32_t raw_mask;              // bit 0: A arrives raw (split in kernel); bit 1: B arrives raw
+    int32_t raw_mask;              // bit 0: A arrives raw (split in kernel); bit 1: B arrives raw;
+                                   // bit 2 / 3: that raw operand is row-contiguous (element (row, kk) at kk*ld + row)
+                                   // and is also transposed by the converters
     float* sk_partials;            // [sk_tiles * (sk_split-1)][256*256] raw accumulators of slices 0 .. S-2 (all S when sk_coop)
     unsigned int* sk_flags;        // one per slot: epoch of the slot's last publication
     unsigned int sk_epoch;         // this launch's epoch (never 0)
@@ -442,6 +450,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t acc_full = smem_u32(bars + 6), acc_empty0 = smem_u32(bars + 7);
     const uint32_t drain = smem_u32(bars + 9), partial_done = smem_u32(bars + 10), conv0 = smem_u32(bars + 11);
     const bool a_raw = (p.raw_mask & 1) != 0, b_raw = (p.raw_mask & 2) != 0;
+    const bool a_mn = (p.raw_mask & 4) != 0, b_mn = (p.raw_mask & 8) != 0;       // raw and row-contiguous
 
     if (threadIdx.x == 0)
     {
@@ -493,9 +502,24 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         const uint32_t dst = smem_u32(stage_base + s * STAGE_BYTES);
                         const uint32_t bar = full0 + 8 * s;
                         mbar_arrive_expect_tx(bar, (a_raw ? PLANE_BYTES : OPERAND_BYTES) + (b_raw ? PLANE_BYTES : OPERAND_BYTES));
-                        if (a_raw) tma_load_3d(dst, &raw_a, bar, kb * BK, tc.tm * BM, (int32_t)tc.bi);
+                        if (a_mn)
+                        {
+                            // eight boxes of 32 rows x 16 k, box g into the 2 KB of the lo slot that converter warp g rewrites
+#pragma unroll
+                            for (int g = 0; g < EPI_WARPS; ++g)
+                                tma_load_3d(dst + PLANE_BYTES + g * (PLANE_BYTES / EPI_WARPS), &raw_a, bar, tc.tm * BM + 32 * g, kb * BK,
+                                            (int32_t)tc.bi);
+                        }
+                        else if (a_raw) tma_load_3d(dst, &raw_a, bar, kb * BK, tc.tm * BM, (int32_t)tc.bi);
                         else tma_load_4d(dst, &map_a, bar, 0, tc.tm * BM, kb, (int32_t)(tc.bi * 2));
-                        if (b_raw) tma_load_3d(dst + OPERAND_BYTES, &raw_b, bar, kb * BK, tc.tn * BN, (int32_t)tc.bi);
+                        if (b_mn)
+                        {
+#pragma unroll
+                            for (int g = 0; g < EPI_WARPS; ++g)
+                                tma_load_3d(dst + OPERAND_BYTES + PLANE_BYTES + g * (PLANE_BYTES / EPI_WARPS), &raw_b, bar,
+                                            tc.tn * BN + 32 * g, kb * BK, (int32_t)tc.bi);
+                        }
+                        else if (b_raw) tma_load_3d(dst + OPERAND_BYTES, &raw_b, bar, kb * BK, tc.tn * BN, (int32_t)tc.bi);
                         else tma_load_4d(dst + OPERAND_BYTES, &map_b, bar, 0, tc.tn * BN, kb, (int32_t)(tc.bi * 2));
                     }
                 }
@@ -617,6 +641,31 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         if (!((p.raw_mask >> op) & 1)) continue;
                         float4* hi = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES);
                         float4* lo = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES + PLANE_BYTES);
+                        if ((p.raw_mask >> (op + 2)) & 1)
+                        {
+                            // Row-contiguous operand: this warp's 32 rows arrived as [16 k][32 rows] in the 2 KB of
+                            // the lo slot that hold these rows' lo values afterwards, so reading before writing is
+                            // a matter of this warp alone.  A lane takes one row: 16 conflict-free loads, then the
+                            // row's 64 bytes of hi and of lo in the MMA's K-major layout (16-byte chunk c of row r
+                            // at position c ^ ((r >> 1) & 3): SWIZZLE_64B).
+                            const float* raw = reinterpret_cast<const float*>(lo) + ew * (32 * BK);
+                            float x[BK];
+#pragma unroll
+                            for (int kk = 0; kk < BK; ++kk) x[kk] = raw[kk * 32 + lane];
+                            __syncwarp();
+                            const int r = ew * 32 + lane;
+#pragma unroll
+                            for (int c = 0; c < BK / 4; ++c)
+                            {
+                                float4 h4, l4;
+                                split_tf32_1(x[4 * c + 0], h4.x, l4.x); split_tf32_1(x[4 * c + 1], h4.y, l4.y);
+                                split_tf32_1(x[4 * c + 2], h4.z, l4.z); split_tf32_1(x[4 * c + 3], h4.w, l4.w);
+                                const int pos = r * (BK / 4) + (c ^ ((r >> 1) & 3));
+                                hi[pos] = h4;
+                                lo[pos] = l4;
+                            }
+                            continue;
+                        }
 #pragma unroll
                         for (int j = 0; j < PLANE_BYTES / 16 / (EPI_WARPS * 32); ++j)
                         {
@@ -1092,6 +1141,22 @@ inline bool make_raw_map(CUtensorMap* map, const float* base, int64_t rows, int6
     return r == CUDA_SUCCESS;
 }
 
+// Raw row-contiguous operand (element (row, kk) at base[kk*ld + row]): boxes of 32 rows x 16 k, dense.
+inline bool make_raw_mn_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int64_t stride,
+                            int64_t batch)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t gdim[3] = {(cuuint64_t)rows, (cuuint64_t)k, (cuuint64_t)batch};
+    cuuint64_t gstr[2] = {(cuuint64_t)ld * 4, (cuuint64_t)(batch > 1 ? stride : k * ld) * 4};
+    cuuint32_t box[3] = {32u, (cuuint32_t)BK, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // True when a k-contiguous operand can be fetched raw by TMA: 16-byte aligned base, leading
 // dimension and batch stride multiples of 4 floats, extents within the tensor-map limits.
 inline bool raw_eligible(const float* base, int64_t rows, int64_t k, int64_t ld, int64_t stride, int64_t batch)
@@ -1107,8 +1172,9 @@ inline bool raw_eligible(const float* base, int64_t rows, int64_t k, int64_t ld,
 struct OperandSource
 {
     const float* planes = nullptr;     // pre-split hi/lo planes, or
-    const float* raw = nullptr;        // raw operand: element (row, kk) at raw[bi*stride + row*ld + kk]
+    const float* raw = nullptr;        // raw operand: element (row, kk) at raw[bi*stride + row*ld + kk],
     int64_t ld = 0, stride = 0;
+    bool row_contig = false;           // ... or, when set, at raw[bi*stride + kk*ld + row]
 };
 
 // a / b: op(A) (rows = m) and op(B)^T (rows = n).
@@ -1130,10 +1196,12 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     if (n_peers < 0 || n_peers > 7) return cudaErrorInvalidValue;
     p.n_peers = n_peers;
     for (int i = 0; i < 7; ++i) p.peer_c[i] = (i < n_peers) ? peer_c[i] : nullptr;
-    p.raw_mask = (a.raw ? 1 : 0) | (b.raw ? 2 : 0);
-    if (a.raw) { if (!make_raw_map(&raw_a, a.raw, m, k, a.ld, a.stride, batch)) return cudaErrorInvalidValue; map_a = raw_a; }
+    p.raw_mask = (a.raw ? 1 : 0) | (b.raw ? 2 : 0) | (a.raw && a.row_contig ? 4 : 0) | (b.raw && b.row_contig ? 8 : 0);
+    if (a.raw && a.row_contig) { if (!make_raw_mn_map(&raw_a, a.raw, m, k, a.ld, a.stride, batch)) return cudaErrorInvalidValue; map_a = raw_a; }
+    else if (a.raw) { if (!make_raw_map(&raw_a, a.raw, m, k, a.ld, a.stride, batch)) return cudaErrorInvalidValue; map_a = raw_a; }
     else { if (!make_plane_map(&map_a, a.planes, m_pad, num_kb, batch)) return cudaErrorInvalidValue; raw_a = map_a; }
-    if (b.raw) { if (!make_raw_map(&raw_b, b.raw, n, k, b.ld, b.stride, batch)) return cudaErrorInvalidValue; map_b = raw_b; }
+    if (b.raw && b.row_contig) { if (!make_raw_mn_map(&raw_b, b.raw, n, k, b.ld, b.stride, batch)) return cudaErrorInvalidValue; map_b = raw_b; }
+    else if (b.raw) { if (!make_raw_map(&raw_b, b.raw, n, k, b.ld, b.stride, batch)) return cudaErrorInvalidValue; map_b = raw_b; }
     else { if (!make_plane_map(&map_b, b.planes, n_pad, num_kb, batch)) return cudaErrorInvalidValue; raw_b = map_b; }
     p.c = c; p.m = m; p.n = n; p.ldc = ldc; p.stride_c = stride_c;
     p.num_kb = (int32_t)num_kb;

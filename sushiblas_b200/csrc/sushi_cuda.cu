@@ -270,10 +270,13 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         // uses the operand.  Measured break-even on B200: the operand is reused by about eleven
         // 256-wide tiles, so A is split in-kernel when n <= 2048 and B when m <= 2048
         // (SUSHI_FUSE_SPLIT=0: never, =2: whenever eligible).
-        const bool want_a = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && n <= 2048);
-        const bool want_b = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && m <= 2048);
-        const bool fuse_a = want_a && !ta && sushi::tc3x::raw_eligible(a, m, k, lda, sa, batch);
-        const bool fuse_b = want_b && tb && sushi::tc3x::raw_eligible(b, n, k, ldb, sb, batch);
+        const bool want_a = ctx->fuse_split == 2 || (ctx->fuse_split != 0 && n <= 2048);
+        const bool want_b = ctx->fuse_split == 2 || (ctx->fuse_split != 0 && m <= 2048);
+        // either storage order of an operand can be taken raw: k-contiguous tiles are split in place, row-contiguous
+        // ones (A^T, or B not transposed) are transposed by the converters on the way (SUSHI_FUSE_SPLIT=3: only k-contiguous)
+        const bool mn_ok = ctx->fuse_split != 3;
+        const bool fuse_a = want_a && (!ta || mn_ok) && sushi::tc3x::raw_eligible(a, m, k, lda, sa, batch);
+        const bool fuse_b = want_b && (tb || mn_ok) && sushi::tc3x::raw_eligible(b, n, k, ldb, sb, batch);
         // workspace: [planes of op(B)^T][planes of op(A)] -- B first so that slabs of A of any
         // size can follow without moving it
         const int64_t a_rows = (reuse && reuse->max_rows > m) ? reuse->max_rows : m;
@@ -321,8 +324,8 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
             }
         }
         sushi::tc3x::OperandSource src_a, src_b;
-        if (fuse_a) { src_a.raw = a; src_a.ld = lda; src_a.stride = sa; } else src_a.planes = planes_a;
-        if (fuse_b) { src_b.raw = b; src_b.ld = ldb; src_b.stride = sb; }
+        if (fuse_a) { src_a.raw = a; src_a.ld = lda; src_a.stride = sa; src_a.row_contig = ta != 0; } else src_a.planes = planes_a;
+        if (fuse_b) { src_b.raw = b; src_b.ld = ldb; src_b.stride = sb; src_b.row_contig = tb == 0; }
         else src_b.planes = (same_operand && !fuse_a) ? planes_a : planes_b;
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,

@@ -239,11 +239,22 @@ def test_tc3x_in_kernel_split_paths(ctx):
     """Operands whose k index is contiguous are fetched raw by TMA and split inside the kernel
     (NT: both operands, NN: A, TT: B); unaligned leading dimensions fall back to the pre-pass.
     Ragged M, N, K rely on TMA zero fill."""
-    for (ta, tb) in [(0, 1), (0, 0), (1, 1)]:
+    for (ta, tb) in [(0, 1), (0, 0), (1, 1), (1, 0)]:
         check(ctx, TC3X, ta, tb, 300, 260, 100, 1.5, 0.5)                 # ragged everything, aligned ld
         check(ctx, TC3X, ta, tb, 1024, 512, 1000, 1.0, 0.0, pad=(4, 8, 0))  # padded but aligned ld
         check(ctx, TC3X, ta, tb, 257, 129, 77, 1.0, 1.0, pad=(1, 3, 0))     # ld % 4 != 0: pre-pass fallback
         check(ctx, TC3X, ta, tb, 512, 256, 333, 1.0, 0.0, batch=5)
+    # row-contiguous operands are transposed by the converters: integer-exact in every storage order, ragged tiles
+    rng = np.random.default_rng(6)
+    for (ta, tb) in [(1, 0), (0, 0), (1, 1)]:
+        m, n, k = 1000, 520, 328
+        a = rng.integers(-3, 4, size=(k, m) if ta else (m, k)).astype(np.float32)
+        b = rng.integers(-3, 4, size=(n, k) if tb else (k, n)).astype(np.float32)
+        opa = (a.T if ta else a).astype(np.int64)
+        opb = (b.T if tb else b).astype(np.int64)
+        got = run_gemm(ctx, TC3X, ta, tb, m, n, k, 1.0, a.ravel(), a.shape[1], 0, b.ravel(), b.shape[1], 0, 0.0,
+                       np.zeros(m * n, np.float32), n, 0, 1).reshape(m, n)
+        assert np.array_equal(got, (opa @ opb).astype(np.float32)), (ta, tb)
     # integer-exact on the fully in-kernel path (NT) with split-K on top
     rng = np.random.default_rng(5)
     m, n, k = 1024, 768, 520
@@ -638,9 +649,13 @@ def test_launch_counter_counts_kernels(ctx):
     check(ctx, SIMT, 0, 0, 64, 64, 64, 1.0, 0.0)
     mid = ctx.launch_count()
     assert mid - before == 1
-    # tensor-core path: one pre-pass launch per operand that is not split inside the GEMM kernel
-    # (k-contiguous operands of small problems are): TN = 2 pre-passes, NN = 1 (B), NT = none
-    for (ta, tb, launches) in [(1, 0, 3), (0, 0, 2), (0, 1, 1)]:
+    # tensor-core path: one pre-pass launch per operand that is not split inside the GEMM kernel.  Aligned
+    # operands of small problems are split in the kernel in either storage order: one launch in every transpose
+    for (ta, tb) in [(1, 0), (0, 0), (0, 1), (1, 1)]:
         start = ctx.launch_count()
         check(ctx, TC3X, ta, tb, 256, 256, 64, 1.0, 0.0)
-        assert ctx.launch_count() - start == launches, (ta, tb)
+        assert ctx.launch_count() - start == 1, (ta, tb)
+    # an operand whose leading dimension is not a multiple of 4 floats goes through the pre-pass: A here
+    start = ctx.launch_count()
+    check(ctx, TC3X, 1, 0, 256, 256, 64, 1.0, 0.0, pad=(1, 0, 0))
+    assert ctx.launch_count() - start == 2
