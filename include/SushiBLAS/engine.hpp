@@ -1,7 +1,7 @@
 // engine.hpp -- entry object of the library (reference: include/SushiBLAS/engine.hpp:61-194,
 // src/engine.cpp:35-69): holds the runtime context, the deferred task graph, the default
 // layout and the RNG seed; hands out tensors and the op facades.  Provided: blas() (Level 3:
-// GEMM, SYRK, TRSM), nonlinear() (ReLU, fusable into a GEMM) and io() (.npy / raw files); the
+// GEMM, SYRK, TRSM), nonlinear() (the activations, fusable into a GEMM) and io() (.npy / raw files); the
 // other op families of the reference are outside the GEMM path.
 #pragma once
 
@@ -161,6 +161,7 @@ namespace SushiBLAS
             q.b = db; q.ldb = g.ldb; q.stride_b = g.stride_b;
             q.beta = g.beta; q.c = dc; q.ldc = g.ldc; q.stride_c = g.stride_c; q.batch = g.batch;
             q.epilogue = slot->activation;
+            q.act_param = slot->param;
             return SUSHI_CUDA_OK;
         };
         // stage the output back (host-resident C only); `dc` is recomputed, nothing is shared with prepare
@@ -178,9 +179,9 @@ namespace SushiBLAS
             int rc = prepare(rt, q);
             if (rc != SUSHI_CUDA_OK) return rc;
             SB_LOG_INFO("CUDA GEMM [Row-Major]: {}x[{}x{}x{}]", g.batch, g.m, g.n, g.k);
-            rc = sushi_cuda_sgemm_strided_batched_ex(rt.native_handle(), 0, q.trans_a, q.trans_b, q.m, q.n, q.k, q.alpha,
-                                                     q.a, q.lda, q.stride_a, q.b, q.ldb, q.stride_b, q.beta, q.c, q.ldc,
-                                                     q.stride_c, q.batch, q.epilogue);
+            rc = sushi_cuda_sgemm_strided_batched_act(rt.native_handle(), 0, q.trans_a, q.trans_b, q.m, q.n, q.k, q.alpha,
+                                                      q.a, q.lda, q.stride_a, q.b, q.ldb, q.stride_b, q.beta, q.c, q.ldc,
+                                                      q.stride_c, q.batch, q.epilogue, q.act_param);
             return rc == SUSHI_CUDA_OK ? finish(rt) : rc;
         };
         // small problems may be batched with their neighbours into one grouped launch at execute()
@@ -449,24 +450,25 @@ namespace SushiBLAS
         return SushiRuntime::Execution::Event();
     }
 
-    // ---------------------------------------------------------------- NonLinearOps::relu
-    inline SushiRuntime::Execution::Event NonLinearOps::relu(Tensor& t)
+    // ---------------------------------------------------------------- NonLinearOps
+    inline SushiRuntime::Execution::Event NonLinearOps::forward(Tensor& t, const char* name, SushiRuntime::Graph::OpID op,
+                                                                int activation, float param)
     {
-        using namespace SushiRuntime::Graph::Literals;
-        SB_THROW_IF(t.dtype != Core::DataType::FLOAT32, "Unsupported data type for ReLU (the CUDA backend serves FLOAT32 only).");
+        SB_THROW_IF(t.dtype != Core::DataType::FLOAT32, "Unsupported data type for {} (the CUDA backend serves FLOAT32 only).", name);
         SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
         float* ptr = t.data_as<float>();
         const int64_t count = t.num_elements;
-        if (engine_.get_graph().try_fuse_activation(ptr, count, SUSHI_EPILOGUE_RELU)) return SushiRuntime::Execution::Event();
+        if (engine_.get_graph().try_fuse_activation(ptr, count, activation, param)) return SushiRuntime::Execution::Event();
 
         SushiRuntime::Graph::TaskMetadata meta;
-        meta.name = "math.nonlinear.relu";
+        meta.name = name;
         meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
-        meta.op_id = "math.nonlinear.relu"_op;
+        meta.op_id = op;
+        meta.set_param(0, param);
         auto storage = t.storage;
         const bool host = storage->host_resident();
         engine_.get_graph().add_task(meta, {storage->data_ptr}, {storage->data_ptr},
-            [storage, ptr, count, host](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            [storage, ptr, count, host, activation, param](SushiRuntime::Execution::RuntimeContext& rt) -> int
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
                 char* base = static_cast<char*>(storage->allocator->device_view(storage->data_ptr));
@@ -475,12 +477,89 @@ namespace SushiBLAS
                 const std::size_t bytes = static_cast<std::size_t>(count) * sizeof(float);
                 int rc = SUSHI_CUDA_OK;
                 if (host) rc = sushi_cuda_memcpy_h2d(ctx, 0, dptr, ptr, bytes);
-                if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_relu(ctx, 0, dptr, count);
+                if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_activation(ctx, 0, activation, param, dptr, count);
                 if (rc == SUSHI_CUDA_OK && host) rc = sushi_cuda_memcpy_d2h(ctx, 0, ptr, dptr, bytes);
                 return rc;
             });
         return SushiRuntime::Execution::Event();
     }
+
+    inline SushiRuntime::Execution::Event NonLinearOps::backward(const Tensor& dy, const Tensor& saved, Tensor& dx, const char* name,
+                                                                 SushiRuntime::Graph::OpID op, int activation, float param)
+    {
+        SB_THROW_IF(dy.dtype != saved.dtype || dy.dtype != dx.dtype, "Data type mismatch in {}.", name);
+        SB_THROW_IF(dy.dtype != Core::DataType::FLOAT32, "Unsupported data type for {} (the CUDA backend serves FLOAT32 only).", name);
+        SB_THROW_IF(dy.num_elements != saved.num_elements || dy.num_elements != dx.num_elements, "Size mismatch in {}.", name);
+        SB_THROW_IF(!dy.is_contiguous() || !saved.is_contiguous() || !dx.is_contiguous(), "Tensor must be contiguous for this operation");
+        struct Operand { SushiRuntime::sushi_ptr<Storage> storage; float* ptr; bool host; };
+        const Operand od{dy.storage, dy.data_as<float>(), dy.storage->host_resident()};
+        const Operand os{saved.storage, saved.data_as<float>(), saved.storage->host_resident()};
+        const Operand ox{dx.storage, dx.data_as<float>(), dx.storage->host_resident()};
+        const int64_t count = dy.num_elements;
+
+        SushiRuntime::Graph::TaskMetadata meta;
+        meta.name = name;
+        meta.task_type = SushiRuntime::Graph::TaskType::MATH_OP;
+        meta.op_id = op;
+        meta.set_param(0, param);
+        engine_.get_graph().add_task(meta, {dy.storage->data_ptr, saved.storage->data_ptr}, {dx.storage->data_ptr},
+            [od, os, ox, count, activation, param](SushiRuntime::Execution::RuntimeContext& rt) -> int
+            {
+                sushi_cuda_ctx* ctx = rt.native_handle();
+                const std::size_t bytes = static_cast<std::size_t>(count) * sizeof(float);
+                auto on_device = [ctx, bytes](const Operand& o, bool upload, float** out) -> int
+                {
+                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
+                    if (!base) return SUSHI_CUDA_ERR_OOM;
+                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
+                    if (o.host && upload && bytes > 0) return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, bytes);
+                    return SUSHI_CUDA_OK;
+                };
+                float *d_dy = nullptr, *d_s = nullptr, *d_dx = nullptr;
+                int rc = on_device(od, true, &d_dy);
+                if (rc == SUSHI_CUDA_OK) rc = on_device(os, true, &d_s);
+                if (rc == SUSHI_CUDA_OK) rc = on_device(ox, false, &d_dx);
+                if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_activation_backward(ctx, 0, activation, param, d_dy, d_s, d_dx, count);
+                if (rc == SUSHI_CUDA_OK && ox.host && bytes > 0) rc = sushi_cuda_memcpy_d2h(ctx, 0, ox.ptr, d_dx, bytes);
+                return rc;
+            });
+        return SushiRuntime::Execution::Event();
+    }
+
+#define SUSHI_NONLINEAR_OP(fn, dotted, kind)                                                                                   \
+    inline SushiRuntime::Execution::Event NonLinearOps::fn(Tensor& t)                                                          \
+    {                                                                                                                          \
+        using namespace SushiRuntime::Graph::Literals;                                                                         \
+        return forward(t, "math.nonlinear." dotted, "math.nonlinear." dotted ""_op, kind, 0.0f);                               \
+    }                                                                                                                          \
+    inline SushiRuntime::Execution::Event NonLinearOps::fn##_backward(const Tensor& dy, const Tensor& s, Tensor& dx)           \
+    {                                                                                                                          \
+        using namespace SushiRuntime::Graph::Literals;                                                                         \
+        return backward(dy, s, dx, "math.nonlinear." dotted "_backward", "math.nonlinear." dotted "_backward"_op, kind, 0.0f); \
+    }
+#define SUSHI_NONLINEAR_OP_PARAM(fn, dotted, kind)                                                                             \
+    inline SushiRuntime::Execution::Event NonLinearOps::fn(Tensor& t, float alpha)                                             \
+    {                                                                                                                          \
+        using namespace SushiRuntime::Graph::Literals;                                                                         \
+        return forward(t, "math.nonlinear." dotted, "math.nonlinear." dotted ""_op, kind, alpha);                              \
+    }                                                                                                                          \
+    inline SushiRuntime::Execution::Event NonLinearOps::fn##_backward(const Tensor& dy, const Tensor& s, Tensor& dx,           \
+                                                                      float alpha)                                             \
+    {                                                                                                                          \
+        using namespace SushiRuntime::Graph::Literals;                                                                         \
+        return backward(dy, s, dx, "math.nonlinear." dotted "_backward", "math.nonlinear." dotted "_backward"_op, kind, alpha);\
+    }
+    SUSHI_NONLINEAR_OP(relu, "relu", SUSHI_ACT_RELU)
+    SUSHI_NONLINEAR_OP(sigmoid, "sigmoid", SUSHI_ACT_SIGMOID)
+    SUSHI_NONLINEAR_OP(tanh, "tanh", SUSHI_ACT_TANH)
+    SUSHI_NONLINEAR_OP(silu, "silu", SUSHI_ACT_SILU)
+    SUSHI_NONLINEAR_OP(gelu, "gelu", SUSHI_ACT_GELU)
+    SUSHI_NONLINEAR_OP(softplus, "softplus", SUSHI_ACT_SOFTPLUS)
+    SUSHI_NONLINEAR_OP_PARAM(leaky_relu, "leaky_relu", SUSHI_ACT_LEAKY_RELU)
+    SUSHI_NONLINEAR_OP_PARAM(elu, "elu", SUSHI_ACT_ELU)
+#undef SUSHI_NONLINEAR_OP
+#undef SUSHI_NONLINEAR_OP_PARAM
+
     // ---------------------------------------------------------------- IO
     inline void IO::write_payload(std::ofstream& ofs, const Tensor& t)
     {

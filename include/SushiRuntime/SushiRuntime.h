@@ -439,7 +439,8 @@ namespace SushiRuntime
         /// the graph so that a later element-wise task can be folded into the producer.
         struct EpilogueSlot
         {
-            int activation = 0;        ///< sushi_cuda_epilogue value
+            int activation = 0;        ///< sushi_cuda_activation_kind value
+            float param = 0.0f;        ///< its parameter (leaky_relu slope, elu alpha)
         };
 
         /// What a producer task writes, for record-time fusion ("TaskMetadata ... for fusers",
@@ -480,12 +481,13 @@ namespace SushiRuntime
                 /// Folds an in-place activation over `count` elements at `ptr` into the task recorded
                 /// just before it, if that task produces exactly this range and has no activation yet.
                 /// Returns true when folded (the caller then records no task of its own).
-                bool try_fuse_activation(void* ptr, std::int64_t count, int activation)
+                bool try_fuse_activation(void* ptr, std::int64_t count, int activation, float param = 0.0f)
                 {
                     if (!fusion_enabled_ || tasks_.empty()) return false;
                     FusionInfo& f = tasks_.back().producer;
                     if (!f.slot || f.out_ptr != ptr || f.out_count != count || f.slot->activation != 0) return false;
                     f.slot->activation = activation;
+                    f.slot->param = param;
                     ++fused_;
                     return true;
                 }

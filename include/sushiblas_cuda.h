@@ -205,7 +205,8 @@ typedef struct sushi_cuda_gemm_desc
     float beta;
     float* c; int64_t ldc, stride_c;
     int64_t batch;
-    int32_t epilogue;          /* sushi_cuda_epilogue */
+    int32_t epilogue;          /* sushi_cuda_epilogue or sushi_cuda_activation_kind */
+    float act_param;           /* parameter of the activation (leaky_relu, elu) */
 } sushi_cuda_gemm_desc;
 SUSHI_CUDA_API int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sushi_cuda_gemm_desc* problems,
                                             int64_t count);
@@ -213,6 +214,40 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const 
 /* In-place ReLU on `count` contiguous floats (replaces the element-wise kernel of
  * src/ops/math/nonlinear/relu.cpp:36-40 for FLOAT32).                                         */
 SUSHI_CUDA_API int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count);
+
+/* The activations of the reference's non-linear family, FLOAT32 (the .cpp files of src/ops/math/nonlinear;
+ * element-wise driver nonlinear_internal.hpp:50-92).  Values 0 and 1 coincide with
+ * sushi_cuda_epilogue.  `act_param` is leaky_relu's slope (reference default 0.01) or elu's alpha
+ * (default 1.0); ignored by the others.  gelu is the tanh form the reference uses
+ * (gelu.cpp:38-44).                                                                            */
+typedef enum sushi_cuda_activation_kind
+{
+    SUSHI_ACT_NONE = 0,
+    SUSHI_ACT_RELU = 1,
+    SUSHI_ACT_LEAKY_RELU = 2,
+    SUSHI_ACT_SIGMOID = 3,
+    SUSHI_ACT_TANH = 4,
+    SUSHI_ACT_ELU = 5,
+    SUSHI_ACT_SILU = 6,
+    SUSHI_ACT_GELU = 7,
+    SUSHI_ACT_SOFTPLUS = 8
+} sushi_cuda_activation_kind;
+
+/* x <- f(x) in place on `count` contiguous floats (the forward lambdas of the files above).   */
+SUSHI_CUDA_API int sushi_cuda_activation(sushi_cuda_ctx* ctx, int dev, int activation, float act_param, float* x,
+                                         int64_t count);
+/* dx <- dy * f'(.), the backward lambdas of the same files: `saved` is the forward INPUT x, except
+ * for sigmoid and tanh, which take the forward OUTPUT y (sigmoid.cpp, tanh.cpp).              */
+SUSHI_CUDA_API int sushi_cuda_activation_backward(sushi_cuda_ctx* ctx, int dev, int activation, float act_param,
+                                                  const float* dy, const float* saved, float* dx, int64_t count);
+/* GEMM with any of these activations applied to alpha*op(A)*op(B) + beta*C in the epilogue (one
+ * pass over C instead of two).                                                                 */
+SUSHI_CUDA_API int sushi_cuda_sgemm_strided_batched_act(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                        int64_t m, int64_t n, int64_t k, float alpha,
+                                                        const float* a, int64_t lda, int64_t stride_a,
+                                                        const float* b, int64_t ldb, int64_t stride_b,
+                                                        float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                        int64_t batch, int activation, float act_param);
 
 /* Same operation on HOST buffers (the SHARED / HOST strategies of the reference, whose
  * tensors callers fill and read on the host: tests/test_common.hpp:36-58): stages A, B

@@ -28,7 +28,7 @@ class GemmDesc(ctypes.Structure):
                 ("a", _vp), ("lda", _i64), ("stride_a", _i64),
                 ("b", _vp), ("ldb", _i64), ("stride_b", _i64),
                 ("beta", _f32), ("c", _vp), ("ldc", _i64), ("stride_c", _i64),
-                ("batch", _i64), ("epilogue", ctypes.c_int32)]
+                ("batch", _i64), ("epilogue", ctypes.c_int32), ("act_param", _f32)]
 
 
 # name -> (restype, argtypes); mirrors include/sushiblas_cuda.h one to one
@@ -61,6 +61,10 @@ SIGNATURES = {
     "sushi_cuda_sgemm_strided_batched_ex": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                                    _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
     "sushi_cuda_relu": (_int, [_vp, _int, _vp, _i64]),
+    "sushi_cuda_activation": (_int, [_vp, _int, _int, _f32, _vp, _i64]),
+    "sushi_cuda_activation_backward": (_int, [_vp, _int, _int, _f32, _vp, _vp, _vp, _i64]),
+    "sushi_cuda_sgemm_strided_batched_act": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _i64,
+                                                    _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int, _f32]),
     "sushi_cuda_ssyrk": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _f32, _vp, _i64]),
     "sushi_cuda_ssyrk_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _f32, _vp, _i64, _i64, _f32,
                                                 _vp, _i64, _i64, _i64]),
@@ -304,11 +308,24 @@ class SushiCuda:
             d.a, d.lda, d.stride_a = _addr(q["a"]), q["lda"], q.get("stride_a", 0)
             d.b, d.ldb, d.stride_b = _addr(q["b"]), q["ldb"], q.get("stride_b", 0)
             d.c, d.ldc, d.stride_c = _addr(q["c"]), q["ldc"], q.get("stride_c", 0)
-            d.batch, d.epilogue = q.get("batch", 1), q.get("epilogue", 0)
+            d.batch, d.epilogue, d.act_param = q.get("batch", 1), q.get("epilogue", 0), q.get("act_param", 0.0)
         self._check(self.lib.sushi_cuda_sgemm_grouped(self._ctx, dev, arr, len(problems)))
 
     def relu(self, x, count: int, dev: int = 0):
         self._check(self.lib.sushi_cuda_relu(self._ctx, dev, _addr(x), count))
+
+    def activation(self, kind: int, x, count: int, param: float = 0.0, dev: int = 0):
+        self._check(self.lib.sushi_cuda_activation(self._ctx, dev, int(kind), param, _addr(x), count))
+
+    def activation_backward(self, kind: int, dy, saved, dx, count: int, param: float = 0.0, dev: int = 0):
+        self._check(self.lib.sushi_cuda_activation_backward(self._ctx, dev, int(kind), param, _addr(dy), _addr(saved),
+                                                            _addr(dx), count))
+
+    def sgemm_strided_batched_act(self, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,
+                                  beta, c, ldc, stride_c, batch, activation: int, act_param: float = 0.0, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_strided_batched_act(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a), lda, stride_a,
+            _addr(b), ldb, stride_b, beta, _addr(c), ldc, stride_c, batch, int(activation), act_param))
 
     # -- GEMM (host pointers, staged)
     def sgemm_strided_batched_host(self, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,

@@ -13,6 +13,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+#include "activation.cuh"
 
 namespace sushi {
 
@@ -24,7 +25,8 @@ struct SimtGemmArgs
     int64_t stride_a, stride_b, stride_c;
     int64_t tiles_m, tiles_n;
     float alpha, beta;
-    int relu;            // epilogue activation: max(alpha*acc + beta*C, 0)
+    int act;             // epilogue activation (ACT_* of activation.cuh) applied to alpha*acc + beta*C
+    float act_param;     // its parameter (leaky_relu, elu)
     int tri;             // 0: full C; 1: only row >= col is written (lower triangle); 2: only row <= col (upper)
 };
 
@@ -158,9 +160,10 @@ __device__ __forceinline__ void simt_gemm_tile(const SimtGemmArgs& p, int64_t tm
                     o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
                     o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
                 }
-                if (p.relu)
+                if (p.act)
                 {
-                    o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+                    o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
+                    o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
                 }
                 *reinterpret_cast<float4*>(dst) = o;
             }
@@ -174,7 +177,7 @@ __device__ __forceinline__ void simt_gemm_tile(const SimtGemmArgs& p, int64_t tm
                     {
                         float o = p.alpha * acc[i][g * 4 + j];
                         if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
-                        dst[j] = p.relu ? fmaxf(o, 0.0f) : o;
+                        dst[j] = apply_act(o, p.act, p.act_param);
                     }
                 }
             }
@@ -234,9 +237,9 @@ sgemm_grouped_simt_kernel(const GroupedGemm* __restrict__ problems, int count)
 }
 
 // C <- beta * C (k == 0 or alpha == 0): no operand is read.  One thread per element.
-// relu != 0 additionally clamps at zero (beta == 1 with relu is the standalone in-place ReLU).
+// act != 0 additionally applies that activation.
 __global__ void scale_c_kernel(float* c, int64_t m, int64_t n, int64_t ldc, int64_t stride_c,
-                               int64_t batch, float beta, int relu = 0)
+                               int64_t batch, float beta, int act = 0, float act_param = 0.0f)
 {
     const int64_t total = m * n * batch;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -247,7 +250,7 @@ __global__ void scale_c_kernel(float* c, int64_t m, int64_t n, int64_t ldc, int6
         const int64_t bi = i / (n * m);
         float* dst = c + bi * stride_c + row * ldc + col;
         float v = (beta == 0.0f) ? 0.0f : beta * (*dst);
-        *dst = relu ? fmaxf(v, 0.0f) : v;
+        *dst = apply_act(v, act, act_param);
     }
 }
 

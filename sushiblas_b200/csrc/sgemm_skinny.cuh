@@ -21,6 +21,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+#include "activation.cuh"
 
 namespace sushi {
 
@@ -32,7 +33,8 @@ struct SkinnyArgs
     int64_t stride_a, stride_b, stride_c;
     int64_t row_blocks;          // ceil(m / rows per CTA)
     float alpha, beta;
-    int trans_b, relu;
+    int trans_b, act;            // act: epilogue activation (ACT_* of activation.cuh)
+    float act_param;
 };
 
 constexpr int SKINNY_THREADS = 256;
@@ -218,17 +220,17 @@ sgemm_skinny_kernel(const SkinnyArgs p)
                             const float2 old = *reinterpret_cast<const float2*>(dst);
                             o0 = fmaf(p.beta, old.x, o0); o1 = fmaf(p.beta, old.y, o1);
                         }
-                        if (p.relu) { o0 = fmaxf(o0, 0.0f); o1 = fmaxf(o1, 0.0f); }
+                        if (p.act) { o0 = apply_act(o0, p.act, p.act_param); o1 = apply_act(o1, p.act, p.act_param); }
                         *reinterpret_cast<float2*>(dst) = make_float2(o0, o1);
                     }
                     else
                     {
                         if (p.beta != 0.0f) o0 = fmaf(p.beta, dst[0], o0);
-                        dst[0] = p.relu ? fmaxf(o0, 0.0f) : o0;
+                        dst[0] = apply_act(o0, p.act, p.act_param);
                         if (col + 1 < p.n)
                         {
                             if (p.beta != 0.0f) o1 = fmaf(p.beta, dst[1], o1);
-                            dst[1] = p.relu ? fmaxf(o1, 0.0f) : o1;
+                            dst[1] = apply_act(o1, p.act, p.act_param);
                         }
                     }
                 }

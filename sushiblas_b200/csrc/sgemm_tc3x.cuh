@@ -58,6 +58,7 @@
 #include <cstdlib>
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include "activation.cuh"
 
 namespace sushi {
 namespace tc3x {
@@ -97,7 +98,8 @@ struct Params
     int32_t tiles_m, tiles_n;
     int64_t total_tiles;           // tiles_m * tiles_n * batch
     float alpha, beta;
-    int32_t relu;                  // epilogue activation: max(alpha*acc + beta*C, 0)
+    int32_t act;                   // epilogue activation (ACT_* of activation.cuh) applied to alpha*acc + beta*C
+    float act_param;               // its parameter (leaky_relu, elu)
     int32_t lean_epilogue;         // 1: interior work items use the check-free epilogue path
     int32_t tri;                   // 0: full C; 1: only row >= col is written (lower triangle); 2: only row <= col
     int* status;
@@ -725,7 +727,9 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int slot_row0 = h * 128 + q * 32;
 
             // work items that lie wholly inside their destination take the lean path
-            const bool inside_c = p.lean_epilogue && vec_ok && p.tri == 0 && row_base + 32 <= p.m && col_base + BN <= p.n;
+            // (activations other than ReLU take the general path)
+            const bool inside_c = p.lean_epilogue && vec_ok && p.tri == 0 && p.act <= ACT_RELU && row_base + 32 <= p.m &&
+                                  col_base + BN <= p.n;
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256);
             const size_t slot_pos = (size_t)(slot_row0 + rsub) * BN + c4 * 4;       // this lane inside a 256 x 256 slot
             if (partial && p.lean_epilogue)
@@ -741,12 +745,12 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const size_t cstride = (size_t)p.sk_tiles * SK_SLOT_FLOATS;
                 if (has_beta)
                 {
-                    if (p.relu) epilogue_fast<true, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    if (p.act) epilogue_fast<true, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
                     else epilogue_fast<true, false>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
                 }
                 else
                 {
-                    if (p.relu) epilogue_fast<false, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    if (p.act) epilogue_fast<false, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
                     else epilogue_fast<false, false>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
                 }
             }
@@ -838,9 +842,10 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                     o.x = fmaf(p.beta, old[i].x, o.x); o.y = fmaf(p.beta, old[i].y, o.y);
                                     o.z = fmaf(p.beta, old[i].z, o.z); o.w = fmaf(p.beta, old[i].w, o.w);
                                 }
-                                if (p.relu)
+                                if (p.act)
                                 {
-                                    o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+                                    o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
+                                    o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
                                 }
                                 *reinterpret_cast<float4*>(dst) = o;
                             }
@@ -855,7 +860,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                     {
                                         float o = p.alpha * av[j];
                                         if (has_beta) o = fmaf(p.beta, dst[j], o);
-                                        dst[j] = p.relu ? fmaxf(o, 0.0f) : o;
+                                        dst[j] = apply_act(o, p.act, p.act_param);
                                     }
                                 }
                             }
@@ -971,9 +976,10 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
                                 o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
                             }
-                            if (p.relu)
+                            if (p.act)
                             {
-                                o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+                                o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
+                                o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
                             }
                             *reinterpret_cast<float4*>(dst) = o;
                             for (int32_t peer = 0; peer < p.n_peers; ++peer)
@@ -990,7 +996,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 {
                                     float o = p.alpha * av[j];
                                     if (has_beta) o = fmaf(p.beta, dst[j], o);
-                                    o = p.relu ? fmaxf(o, 0.0f) : o;
+                                    o = apply_act(o, p.act, p.act_param);
                                     dst[j] = o;
                                     for (int32_t peer = 0; peer < p.n_peers; ++peer)
                                         p.peer_c[peer][tc.bi * p.stride_c + grow * p.ldc + gcol + j] = o;
@@ -1184,7 +1190,8 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
                                      float alpha, float beta, int* status, int sm_count, cudaStream_t st,
                                      void* sk_area = nullptr, unsigned int sk_epoch = 0,
-                                     float* const* peer_c = nullptr, int n_peers = 0, bool relu = false, int tri = 0)
+                                     float* const* peer_c = nullptr, int n_peers = 0, int act = 0, int tri = 0,
+                                     float act_param = 0.0f)
 {
     // per-device attribute; cheap enough to set on every launch
     cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -1207,7 +1214,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.num_kb = (int32_t)num_kb;
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
-    p.alpha = alpha; p.beta = beta; p.status = status; p.relu = relu ? 1 : 0; p.tri = tri;
+    p.alpha = alpha; p.beta = beta; p.status = status; p.act = act; p.act_param = act_param; p.tri = tri;
     p.lean_epilogue = lean_epilogue_enabled() ? 1 : 0;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
     p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split; p.sk_coop = plan.coop;

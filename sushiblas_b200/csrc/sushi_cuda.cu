@@ -234,7 +234,8 @@ struct SlabReuse
     int64_t max_rows = 0;      // largest slab (sizes the A planes once)
     float* peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int n_peers = 0;           // fused all-gather: the GEMM epilogue also stores C to these addresses
-    bool relu = false;         // epilogue activation
+    int act = 0;               // epilogue activation (sushi_cuda_activation_kind)
+    float act_param = 0.0f;    // its parameter
     int tri = 0;               // triangular output (SYRK): 1 lower, 2 upper
 };
 
@@ -244,15 +245,16 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
 {
     if (m == 0 || n == 0 || batch == 0) return SUSHI_CUDA_OK;
     SC_CUDA(ctx, cudaSetDevice(d.device));
-    const bool relu = reuse && reuse->relu;
+    const int act = reuse ? reuse->act : 0;
+    const float act_param = reuse ? reuse->act_param : 0.0f;
     const int tri = reuse ? reuse->tri : 0;
     if ((k == 0 || alpha == 0.0f) && tri == 0)
     {
-        if (beta == 1.0f && !relu) return SUSHI_CUDA_OK;
+        if (beta == 1.0f && !act) return SUSHI_CUDA_OK;
         const int64_t total = m * n * batch;
         int64_t blocks = (total + 255) / 256;
         if (blocks > (int64_t)d.sm_count * 16) blocks = (int64_t)d.sm_count * 16;
-        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d.stream>>>(c, m, n, ldc, sc, batch, beta, relu ? 1 : 0);
+        sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d.stream>>>(c, m, n, ldc, sc, batch, beta, act, act_param);
         ctx->launches++;
         SC_CUDA(ctx, cudaGetLastError());
         return SUSHI_CUDA_OK;
@@ -330,7 +332,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,
                                                    d.status, d.sm_count, d.stream, sk_area, d.sk_epoch,
-                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, relu, tri));
+                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, act, tri, act_param));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
         ctx->launches += 1 + prepass_launches;
         return SUSHI_CUDA_OK;
@@ -342,7 +344,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         sushi::SkinnyArgs q;
         q.a = a; q.b = b; q.c = c; q.m = m; q.n = n; q.k = k; q.lda = lda; q.ldb = ldb; q.ldc = ldc;
         q.stride_a = sa; q.stride_b = sb; q.stride_c = sc; q.row_blocks = 0; q.alpha = alpha; q.beta = beta;
-        q.trans_b = tb != 0; q.relu = relu ? 1 : 0;
+        q.trans_b = tb != 0; q.act = act; q.act_param = act_param;
         int rcs = timing_mark(ctx, d, 0, 0);
         if (rcs == SUSHI_CUDA_OK) rcs = timing_mark(ctx, d, 1, 0);
         if (rcs != SUSHI_CUDA_OK) return rcs;
@@ -354,7 +356,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     sushi::SimtGemmArgs g;
     g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
     g.stride_a = sa; g.stride_b = sb; g.stride_c = sc; g.tiles_m = 0; g.tiles_n = 0;
-    g.alpha = alpha; g.beta = beta; g.relu = relu ? 1 : 0; g.tri = tri;
+    g.alpha = alpha; g.beta = beta; g.act = act; g.act_param = act_param; g.tri = tri;
     int rc = timing_mark(ctx, d, 0, 0);
     if (rc == SUSHI_CUDA_OK) rc = timing_mark(ctx, d, 1, 0);
     if (rc != SUSHI_CUDA_OK) return rc;
@@ -836,10 +838,25 @@ extern "C" int sushi_cuda_sgemm_strided_batched_ex(sushi_cuda_ctx* ctx, int dev,
     if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_ex: bad context or device index");
     if (epilogue != SUSHI_EPILOGUE_NONE && epilogue != SUSHI_EPILOGUE_RELU)
         return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_ex: unknown epilogue");
+    return sushi_cuda_sgemm_strided_batched_act(ctx, dev, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b,
+                                                beta, c, ldc, stride_c, batch, epilogue, 0.0f);
+}
+
+extern "C" int sushi_cuda_sgemm_strided_batched_act(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                    int64_t m, int64_t n, int64_t k, float alpha,
+                                                    const float* a, int64_t lda, int64_t stride_a,
+                                                    const float* b, int64_t ldb, int64_t stride_b,
+                                                    float beta, float* c, int64_t ldc, int64_t stride_c,
+                                                    int64_t batch, int activation, float act_param)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_act: bad context or device index");
+    if (activation < 0 || activation >= sushi::ACT_COUNT)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_act: unknown activation");
     int rc = validate_gemm(ctx, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, stride_a, stride_b, stride_c, batch);
     if (rc != SUSHI_CUDA_OK) return rc;
     SlabReuse opts;
-    opts.relu = (epilogue == SUSHI_EPILOGUE_RELU);
+    opts.act = activation; opts.act_param = act_param;
     return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a, lda, stride_a, b, ldb, stride_b, beta, c, ldc,
                     stride_c, batch, &opts);
 }
@@ -861,7 +878,7 @@ extern "C" int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sush
         int rc = validate_gemm(ctx, q.m, q.n, q.k, q.a, q.lda, q.b, q.ldb, q.c, q.ldc, q.trans_a, q.trans_b, q.stride_a,
                                q.stride_b, q.stride_c, q.batch);
         if (rc != SUSHI_CUDA_OK) return rc;
-        if (q.epilogue != SUSHI_EPILOGUE_NONE && q.epilogue != SUSHI_EPILOGUE_RELU)
+        if (q.epilogue < 0 || q.epilogue >= sushi::ACT_COUNT)
             return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_grouped: unknown epilogue");
         if (q.m == 0 || q.n == 0 || q.batch == 0) continue;
         const bool tensor = ctx->variant == SUSHI_GEMM_TC3X ||
@@ -872,7 +889,7 @@ extern "C" int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sush
         g.g.lda = q.lda; g.g.ldb = q.ldb; g.g.ldc = q.ldc;
         g.g.stride_a = q.stride_a; g.g.stride_b = q.stride_b; g.g.stride_c = q.stride_c;
         g.g.tiles_m = (q.m + 63) / 64; g.g.tiles_n = (q.n + 63) / 64;
-        g.g.alpha = q.alpha; g.g.beta = q.beta; g.g.relu = q.epilogue == SUSHI_EPILOGUE_RELU; g.g.tri = 0;
+        g.g.alpha = q.alpha; g.g.beta = q.beta; g.g.act = q.epilogue; g.g.act_param = q.act_param; g.g.tri = 0;
         g.trans_a = q.trans_a != 0; g.trans_b = q.trans_b != 0;
         g.first_tile = tiles;
         tiles += g.g.tiles_m * g.g.tiles_n * q.batch;
@@ -895,7 +912,7 @@ extern "C" int sushi_cuda_sgemm_grouped(sushi_cuda_ctx* ctx, int dev, const sush
     {
         const sushi_cuda_gemm_desc& q = problems[i];
         SlabReuse opts;
-        opts.relu = q.epilogue == SUSHI_EPILOGUE_RELU;
+        opts.act = q.epilogue; opts.act_param = q.act_param;
         int rc = run_gemm(ctx, *d, q.trans_a, q.trans_b, q.m, q.n, q.k, q.alpha, q.a, q.lda, q.stride_a, q.b, q.ldb,
                           q.stride_b, q.beta, q.c, q.ldc, q.stride_c, q.batch, &opts);
         if (rc != SUSHI_CUDA_OK) return rc;
@@ -1096,18 +1113,43 @@ extern "C" int sushi_cuda_strsm(sushi_cuda_ctx* ctx, int dev, int left, int uppe
     return sushi_cuda_strsm_strided_batched(ctx, dev, left, upper, trans, unit_diag, m, n, alpha, a, lda, 0, b, ldb, 0, 1);
 }
 
-extern "C" int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count)
+extern "C" int sushi_cuda_activation(sushi_cuda_ctx* ctx, int dev, int activation, float act_param, float* x, int64_t count)
 {
     DeviceState* d = get_dev(ctx, dev);
-    if (!d || count < 0 || (count > 0 && !x)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "relu: bad argument");
-    if (count == 0) return SUSHI_CUDA_OK;
+    if (!d || count < 0 || (count > 0 && !x)) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "activation: bad argument");
+    if (activation < 0 || activation >= sushi::ACT_COUNT)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "activation: unknown activation");
+    if (count == 0 || activation == sushi::ACT_NONE) return SUSHI_CUDA_OK;
     SC_CUDA(ctx, cudaSetDevice(d->device));
-    int64_t blocks = (count + 255) / 256;
-    if (blocks > (int64_t)d->sm_count * 32) blocks = (int64_t)d->sm_count * 32;
-    sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(x, 1, count, count, 0, 1, 1.0f, 1);
+    int64_t blocks = (count / 4 + 255) / 256 + 1;
+    if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
+    sushi::activation_forward_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(x, count, activation, act_param);
     ctx->launches++;
     SC_CUDA(ctx, cudaGetLastError());
     return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_activation_backward(sushi_cuda_ctx* ctx, int dev, int activation, float act_param, const float* dy,
+                                              const float* saved, float* dx, int64_t count)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || count < 0 || (count > 0 && (!dy || !saved || !dx)))
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "activation_backward: bad argument");
+    if (activation <= sushi::ACT_NONE || activation >= sushi::ACT_COUNT)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "activation_backward: unknown activation");
+    if (count == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    int64_t blocks = (count / 4 + 255) / 256 + 1;
+    if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
+    sushi::activation_backward_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(dy, saved, dx, count, activation, act_param);
+    ctx->launches++;
+    SC_CUDA(ctx, cudaGetLastError());
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_relu(sushi_cuda_ctx* ctx, int dev, float* x, int64_t count)
+{
+    return sushi_cuda_activation(ctx, dev, sushi::ACT_RELU, 0.0f, x, count);
 }
 
 extern "C" int sushi_cuda_sgemm(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,

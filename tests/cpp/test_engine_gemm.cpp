@@ -482,6 +482,50 @@ TEST_CASE(ExampleFlowWithWaitAll)
     EXPECT_NEAR(C.data_as<float>()[12345], 512.0f, 1e-3);
 }
 
+TEST_CASE(ActivationFamilyKnownAnswers)
+{
+    // Forward / Backward of tests/math/nonlinear/test_{leaky_relu,sigmoid,tanh,elu,silu,gelu,softplus}.cpp
+    sb::Engine engine(runtime());
+    auto t = engine.create_tensor({4});
+    auto dy = engine.create_tensor({4}), x = engine.create_tensor({4}), dx = engine.create_tensor({4});
+    auto fwd = [&](std::vector<float> in, std::vector<float> want, auto&& op) {
+        fill_tensor(t, in); op(); engine.execute().wait(); verify_tensor(t, want);
+    };
+    auto bwd = [&](std::vector<float> g, std::vector<float> saved, std::vector<float> want, auto&& op) {
+        fill_tensor(dy, g); fill_tensor(x, saved); fill_tensor(dx, {0, 0, 0, 0}); op(); engine.execute().wait(); verify_tensor(dx, want);
+    };
+    fwd({-2.0f, -0.5f, 0.0f, 3.5f}, {-0.02f, -0.005f, 0.0f, 3.5f}, [&] { engine.nonlinear().leaky_relu(t, 0.01f); });
+    fwd({0.0f, 1.0f, -1.0f, 2.0f}, {0.5f, 0.731058f, 0.268941f, 0.880797f}, [&] { engine.nonlinear().sigmoid(t); });
+    fwd({0.0f, 1.0f, -1.0f, 2.0f}, {0.0f, 0.761594f, -0.761594f, 0.964028f}, [&] { engine.nonlinear().tanh(t); });
+    fwd({-1.0f, 0.0f, 1.0f, 2.0f}, {-0.632121f, 0.0f, 1.0f, 2.0f}, [&] { engine.nonlinear().elu(t, 1.0f); });
+    fwd({-1.0f, 0.0f, 1.0f, 2.0f}, {-0.268941f, 0.0f, 0.731059f, 1.761594f}, [&] { engine.nonlinear().silu(t); });
+    fwd({-1.0f, 0.0f, 1.0f, 2.0f}, {-0.158865f, 0.0f, 0.841135f, 1.954598f}, [&] { engine.nonlinear().gelu(t); });
+    fwd({-1.0f, 0.0f, 1.0f, 2.0f}, {0.313262f, 0.693147f, 1.313262f, 2.126928f}, [&] { engine.nonlinear().softplus(t); });
+    bwd({1, 2, 3, 4}, {-1.0f, 0.0f, 1.0f, 2.0f}, {0.0f, 0.0f, 3.0f, 4.0f}, [&] { engine.nonlinear().relu_backward(dy, x, dx); });
+    bwd({1, 2, 3, 4}, {-1.0f, -0.5f, 1.0f, 2.0f}, {0.01f, 0.02f, 3.0f, 4.0f}, [&] { engine.nonlinear().leaky_relu_backward(dy, x, dx, 0.01f); });
+    bwd({1, 1, 1, 1}, {0.5f, 0.731058f, 0.268941f, 0.880797f}, {0.25f, 0.196612f, 0.196612f, 0.104994f},
+        [&] { engine.nonlinear().sigmoid_backward(dy, x, dx); });
+    bwd({1, 1, 1, 1}, {0.0f, 0.761594f, -0.761594f, 0.964028f}, {1.0f, 0.419974f, 0.419974f, 0.070651f},
+        [&] { engine.nonlinear().tanh_backward(dy, x, dx); });
+    bwd({1, 1, 1, 1}, {-1.0f, 0.0f, 1.0f, 2.0f}, {0.367879f, 1.0f, 1.0f, 1.0f}, [&] { engine.nonlinear().elu_backward(dy, x, dx, 1.0f); });
+    bwd({1, 1, 1, 1}, {-1.0f, 0.0f, 1.0f, 2.0f}, {0.072329f, 0.5f, 0.927671f, 1.090784f}, [&] { engine.nonlinear().silu_backward(dy, x, dx); });
+    bwd({1, 1, 1, 1}, {-1.0f, 0.0f, 1.0f, 2.0f}, {-0.082937f, 0.5f, 1.082937f, 1.086099f}, [&] { engine.nonlinear().gelu_backward(dy, x, dx); });
+    bwd({1, 1, 1, 1}, {-1.0f, 0.0f, 1.0f, 2.0f}, {0.268941f, 0.5f, 0.731059f, 0.880797f}, [&] { engine.nonlinear().softplus_backward(dy, x, dx); });
+
+    // an activation recorded right after the GEMM that wrote the tensor is folded into the GEMM's epilogue
+    auto A = engine.create_tensor({64, 48}), B = engine.create_tensor({48, 40}), C = engine.create_tensor({64, 40});
+    auto a = random_vec(64 * 48, 71), b = random_vec(48 * 40, 72);
+    fill_tensor(A, a); fill_tensor(B, b);
+    engine.blas().gemm(A, B, C);
+    engine.nonlinear().sigmoid(C);
+    EXPECT_EQ(engine.get_graph().pending(), size_t(1));
+    engine.execute().wait();
+    auto ref = host_gemm(false, false, 64, 40, 48, 1.0f, a, b, 0.0f, a);
+    for (size_t i = 0; i < ref.size(); ++i) EXPECT_NEAR(C.data_as<float>()[i], 1.0 / (1.0 + std::exp(-double(ref[i]))), 2e-5);
+    auto D64 = engine.create_tensor({4}, sb::Core::DataType::FLOAT64);
+    EXPECT_THROWS(engine.nonlinear().gelu(D64), "FLOAT32 only");
+}
+
 TEST_CASE(ErrorsAreRuntimeErrors)
 {
     sb::Engine engine(runtime());

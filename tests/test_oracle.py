@@ -245,3 +245,21 @@ def test_dgemm_oracle_known_answers_and_numpy_agreement():
     ref_rm, _ = og.dgemm_f80_c(0, 0, m, n, k, 1.0, A, k, 0, B, n, 0, 0.0, np.zeros(m * n), n, 0, 1)
     assert np.array_equal(ref_cm.reshape(n, m).T, ref_rm.reshape(m, n))
     assert og.tolerance_ratio_f64(np.array([np.nan]), np.array([0.0], np.longdouble), np.array([1.0]), 1) == float("inf")
+
+
+# ------------------------------------------------------------------ activation restatements
+def test_activation_oracle_reproduces_the_reference_known_answers():
+    from oracle import ref_activations as oa
+    for kind, a, x, want in oa.REFERENCE_FORWARD:
+        assert np.allclose(oa.forward(kind, x, a), want, rtol=0, atol=1e-4), oa.NAMES[kind]   # tests/test_common.hpp:48
+    for kind, a, dy, s, want in oa.REFERENCE_BACKWARD:
+        assert np.allclose(oa.backward(kind, dy, s, a), want, rtol=0, atol=1e-4), oa.NAMES[kind]
+    # the backward forms are the derivatives of the forward forms (central differences)
+    x = np.linspace(-3.0, 3.0, 25) + 0.013
+    for kind, a in [(oa.LEAKY_RELU, 0.1), (oa.ELU, 0.7), (oa.SILU, 0.0), (oa.GELU, 0.0), (oa.SOFTPLUS, 0.0)]:
+        num = (oa.forward(kind, x + 1e-6, a) - oa.forward(kind, x - 1e-6, a)) / 2e-6
+        assert np.allclose(oa.backward(kind, np.ones_like(x), x, a), num, rtol=1e-6, atol=1e-7), oa.NAMES[kind]
+    for kind in (oa.SIGMOID, oa.TANH):
+        y = oa.forward(kind, x)
+        num = (oa.forward(kind, x + 1e-6) - oa.forward(kind, x - 1e-6)) / 2e-6
+        assert np.allclose(oa.backward(kind, np.ones_like(x), y), num, rtol=1e-6, atol=1e-7), oa.NAMES[kind]
