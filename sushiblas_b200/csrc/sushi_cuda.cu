@@ -180,20 +180,29 @@ bool prefer_tc3x(int64_t m, int64_t n, int64_t k, int64_t batch, int sm_count, b
     if (k < 128 || m < 128 || n < 128) return false;
     const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256) * batch;
     const int64_t num_kb = (k + 15) / 16;
-    // tensor path: ~1 us per 16-k block of a 256 x 256 tile; few tiles are cut along K (plan_tail), which
-    // adds a fixed exchange; pre-pass ~ 12 B per operand element at 5 TB/s; launches and epilogue ~ 12 us
+    // Tensor path, measured on B200: ~1 us per 16-k block of a 256 x 256 tile on top of ~27 us of fixed cost per
+    // launch (prologue, pipeline fill, epilogue, teardown); few tiles are cut along K (plan_tail), which adds
+    // the exchange; an operand wider than 2048 in the other dimension goes through the pre-pass (a launch of
+    // ~6 us plus 12 B per element at ~5 TB/s), narrower ones are split inside the kernel.
     const sushi::tc3x::TailPlan plan = sushi::tc3x::plan_tail(tiles, num_kb, sm_count, allow_split);
     const int64_t items = plan.sk_split > 1 ? tiles * plan.sk_split : tiles;
     const double rounds = (double)((items + sm_count - 1) / sm_count);
     const double kb_item = (double)((num_kb + plan.sk_split - 1) / plan.sk_split);
-    const double t_tc = rounds * kb_item * 1.02e-6 + (plan.sk_split > 1 ? 8e-6 : 0.0) +
-                        12.0 * (double)batch * (double)k * (double)(m + n) / 5.0e12 + 12e-6;
-    // FFMA path (measured): 128 x 128 tiles at ~0.2 TFLOP/s per SM when they fill the GPU, else 64 x 64 tiles at ~0.1
+    double t_tc = rounds * kb_item * 1.02e-6 + 27e-6 + (plan.sk_split > 1 ? 6e-6 : 0.0);
+    if (n > 2048) t_tc += 6e-6 + 12.0 * (double)batch * (double)k * (double)m / 5.0e12;
+    if (m > 2048) t_tc += 6e-6 + 12.0 * (double)batch * (double)k * (double)n / 5.0e12;
+    // FFMA path, measured: 128 x 128 tiles at ~0.17 TFLOP/s per SM once they fill the GPU; otherwise 64 x 64 tiles,
+    // ~0.1 TFLOP/s for a lone CTA and ~0.125 per SM with several resident; ~5 us to launch
     const int64_t big = ((m + 127) / 128) * ((n + 127) / 128) * batch;
-    const int64_t edge = big >= sm_count ? 128 : 64;
-    const int64_t simt_tiles = ((m + edge - 1) / edge) * ((n + edge - 1) / edge) * batch;
-    const double t_simt = (double)((simt_tiles + sm_count - 1) / sm_count) * (2.0 * edge * edge * (double)k) /
-                          (edge == 128 ? 0.2e12 : 0.1e12) + 3e-6;
+    double t_simt;
+    if (big >= sm_count)
+        t_simt = (double)big / sm_count * (2.0 * 128 * 128 * (double)k) / 0.17e12 + 5e-6;
+    else
+    {
+        const int64_t small = ((m + 63) / 64) * ((n + 63) / 64) * batch;
+        const double per_sm = (double)small / sm_count;
+        t_simt = (per_sm <= 1.0 ? 1.0 / 0.1e12 : per_sm / 0.125e12) * (2.0 * 64 * 64 * (double)k) + 5e-6;
+    }
     return t_tc < t_simt;
 }
 

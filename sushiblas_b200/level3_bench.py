@@ -1,7 +1,7 @@
 """Timing of the Level-3 rows next to the fp32 GEMM: fp64 GEMM, TRSM, SYRK, and of a deliberately
 bandwidth-bound fp32 GEMM shape (65536 x 16 x 256, served by the FFMA kernel).
 
-    python -m sushiblas_b200.level3_bench [--op dgemm|strsm|ssyrk|skinny|all] [--size N] [--steps K] [--warmup W] [--library]
+    python -m sushiblas_b200.level3_bench [--op dgemm|strsm|ssyrk|skinny|activation|all] [--size N] [--steps K] [--warmup W] [--library]
 
 One JSON line per (op, case): CUDA-event time of each call on the launching stream (median and
 best of K calls after W warm-up calls), inputs resident in HBM, L2 flushed between calls by
@@ -43,7 +43,7 @@ def _time_calls(torch, stream, fn, reset, flush, steps, warmup):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["dgemm", "strsm", "ssyrk", "skinny", "all"])
+    ap.add_argument("--op", default="all", choices=["dgemm", "strsm", "ssyrk", "skinny", "activation", "all"])
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -128,6 +128,31 @@ def main(argv=None):
                                                          "frac": round(gbs / peak, 4), "peak_source": src,
                                                          "algorithmic_bytes": alg_bytes}})
         del a, b, c
+
+    if args.op in ("activation", "all"):
+        # element-wise, in place: 4 B read + 4 B written per element; 1 GiB of floats
+        count = 1 << 28
+        x = torch.rand(count, device="cuda") * 4 - 2
+        dy = torch.rand(count, device="cuda")
+        dx = torch.empty(count, device="cuda")
+        peak, src = _hbm_peak_gbs()
+        for kind, label in [(1, "relu"), (7, "gelu"), (3, "sigmoid")]:
+            med, best = _time_calls(torch, stream, lambda: ctx.activation(kind, x, count, 0.0), lambda: None, flush,
+                                    args.steps, args.warmup)
+            gbs = 8.0 * count / (med * 1e-3) / 1e9
+            emit("activation", label, 0.0, med, best, None,
+                 {"dtype": "f32", "size": count, "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                                                               "frac": round(gbs / peak, 4), "peak_source": src,
+                                                               "algorithmic_bytes": 8.0 * count}})
+            x.uniform_(-2, 2)
+        med, best = _time_calls(torch, stream, lambda: ctx.activation_backward(7, dy, x, dx, count, 0.0), lambda: None, flush,
+                                args.steps, args.warmup)
+        gbs = 12.0 * count / (med * 1e-3) / 1e9
+        emit("activation_backward", "gelu", 0.0, med, best, None,
+             {"dtype": "f32", "size": count, "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                                                           "frac": round(gbs / peak, 4), "peak_source": src,
+                                                           "algorithmic_bytes": 12.0 * count}})
+        del x, dy, dx
 
     if args.op in ("ssyrk", "all"):
         a = torch.rand(n, n, device="cuda")
