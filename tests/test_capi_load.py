@@ -80,3 +80,29 @@ def test_missing_library_is_an_error_not_a_fallback(tmp_path):
     code = ("import sys; import sushiblas_b200, sushiblas_b200.capi; "
             "bad = [m for m in sys.modules if m == 'oracle' or m.startswith('oracle.')]; sys.exit(1 if bad else 0)")
     assert subprocess.run([sys.executable, "-c", code], cwd=ROOT).returncode == 0
+
+
+def test_header_is_plain_c(tmp_path):
+    """The drop-in boundary must be consumable from C (cgo / JNI / ctypes generators read it as C):
+    the header compiles as C99 on its own and its structs have the layout the Python binding assumes."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "abi_check.c"
+    src.write_text(
+        '#include <stddef.h>\n#include <stdio.h>\n#include "sushiblas_cuda.h"\n'
+        "int main(void) {\n"
+        '  printf("%zu %zu %zu %zu\\n", sizeof(sushi_cuda_gemm_desc), offsetof(sushi_cuda_gemm_desc, alpha),\n'
+        "         offsetof(sushi_cuda_gemm_desc, epilogue), offsetof(sushi_cuda_gemm_desc, act_param));\n"
+        "  return (SUSHI_ACT_SOFTPLUS == 8 && (int)SUSHI_EPILOGUE_RELU == (int)SUSHI_ACT_RELU) ? 0 : 1;\n}\n")
+    exe = tmp_path / "abi_check"
+    subprocess.check_call([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0
+    import ctypes
+    from sushiblas_b200.capi import GemmDesc
+    size, off_alpha, off_epi, off_param = (int(v) for v in out.stdout.split())
+    assert size == ctypes.sizeof(GemmDesc)
+    assert off_alpha == GemmDesc.alpha.offset and off_epi == GemmDesc.epilogue.offset and off_param == GemmDesc.act_param.offset
