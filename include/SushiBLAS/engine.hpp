@@ -561,95 +561,110 @@ namespace SushiBLAS
 #undef SUSHI_NONLINEAR_OP_PARAM
 
     // ---------------------------------------------------------------- IO
-    inline void IO::write_payload(std::ofstream& ofs, const Tensor& t)
+    // The file formats themselves live in detail:: functions that take no Engine, so that they can be
+    // exercised with host-resident tensors on a machine without a GPU; IO adds the flush of pending work.
+    namespace detail
     {
-        SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
-        SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
-        const std::size_t bytes = static_cast<std::size_t>(t.num_elements) * detail::io_bytes_per_element(t.dtype);
-        if (bytes == 0) return;
-        if (t.storage->host_resident())
-            ofs.write(static_cast<const char*>(t.data()), static_cast<std::streamsize>(bytes));
-        else
+        inline void write_payload(std::ofstream& ofs, const Tensor& t)
         {
-            std::vector<char> buf(bytes);
-            t.to_host(buf.data());
-            ofs.write(buf.data(), static_cast<std::streamsize>(bytes));
+            SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
+            SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
+            const std::size_t bytes = static_cast<std::size_t>(t.num_elements) * io_bytes_per_element(t.dtype);
+            if (bytes == 0) return;
+            if (t.storage->host_resident())
+                ofs.write(static_cast<const char*>(t.data()), static_cast<std::streamsize>(bytes));
+            else
+            {
+                std::vector<char> buf(bytes);
+                t.to_host(buf.data());
+                ofs.write(buf.data(), static_cast<std::streamsize>(bytes));
+            }
+            SB_THROW_IF(!ofs.good(), "Failed while writing {} bytes of tensor data", bytes);
         }
-        SB_THROW_IF(!ofs.good(), "Failed while writing {} bytes of tensor data", bytes);
-    }
 
-    inline void IO::read_payload(std::ifstream& ifs, Tensor& t, const std::string& path)
-    {
-        SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
-        SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
-        const std::size_t bytes = static_cast<std::size_t>(t.num_elements) * detail::io_bytes_per_element(t.dtype);
-        if (bytes == 0) return;
-        if (t.storage->host_resident())
+        inline void read_payload(std::ifstream& ifs, Tensor& t, const std::string& path)
         {
-            ifs.read(static_cast<char*>(t.data()), static_cast<std::streamsize>(bytes));
-            SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != bytes, "File is shorter than the tensor ({} bytes): {}", bytes, path);
-            // the device mirror of a host-resident tensor is refreshed by the next operation that reads it
+            SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
+            SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
+            const std::size_t bytes = static_cast<std::size_t>(t.num_elements) * io_bytes_per_element(t.dtype);
+            if (bytes == 0) return;
+            if (t.storage->host_resident())
+            {
+                ifs.read(static_cast<char*>(t.data()), static_cast<std::streamsize>(bytes));
+                SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != bytes, "File is shorter than the tensor ({} bytes): {}", bytes, path);
+                // the device mirror of a host-resident tensor is refreshed by the next operation that reads it
+            }
+            else
+            {
+                std::vector<char> buf(bytes);
+                ifs.read(buf.data(), static_cast<std::streamsize>(bytes));
+                SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != bytes, "File is shorter than the tensor ({} bytes): {}", bytes, path);
+                t.from_host(buf.data());
+            }
         }
-        else
+
+        inline void save_npy_file(const Tensor& t, const std::string& path)
         {
-            std::vector<char> buf(bytes);
-            ifs.read(buf.data(), static_cast<std::streamsize>(bytes));
-            SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != bytes, "File is shorter than the tensor ({} bytes): {}", bytes, path);
-            t.from_host(buf.data());
+            SB_THROW_IF(npy_descr(t.dtype)[0] == '\0', "Unsupported data type for .npy export.");
+            std::ofstream ofs(path, std::ios::binary);
+            SB_THROW_IF(!ofs.is_open(), "Failed to open file: {}", path);
+            const std::string dict = npy_header_dict(t.dtype, t.layout, t.shape.data(), t.rank);
+            SB_THROW_IF(dict.size() > 65535, "Tensor shape does not fit a version 1.0 .npy header");
+            const unsigned char preamble[10] = {0x93, 'N', 'U', 'M', 'P', 'Y', 1, 0,
+                                                static_cast<unsigned char>(dict.size() & 0xff),
+                                                static_cast<unsigned char>(dict.size() >> 8)};
+            ofs.write(reinterpret_cast<const char*>(preamble), 10);
+            ofs.write(dict.data(), static_cast<std::streamsize>(dict.size()));
+            write_payload(ofs, t);
         }
-    }
+
+        inline void load_npy_file(Tensor& t, const std::string& path)
+        {
+            std::ifstream ifs(path, std::ios::binary);
+            SB_THROW_IF(!ifs.is_open(), "Failed to open file for reading: {}", path);
+            unsigned char pre[8] = {0};
+            ifs.read(reinterpret_cast<char*>(pre), 8);
+            SB_THROW_IF(ifs.gcount() != 8 || std::memcmp(pre, "\x93NUMPY", 6) != 0, "Invalid .npy file magic.");
+            const int major = pre[6];
+            SB_THROW_IF(major < 1 || major > 3, "Unsupported .npy format version {}.{}", major, int(pre[7]));
+            unsigned char len_bytes[4] = {0};
+            const int len_size = (major == 1) ? 2 : 4;
+            ifs.read(reinterpret_cast<char*>(len_bytes), len_size);
+            SB_THROW_IF(ifs.gcount() != len_size, "Truncated .npy header: {}", path);
+            const std::size_t header_len = std::size_t(len_bytes[0]) | (std::size_t(len_bytes[1]) << 8) |
+                                           (std::size_t(len_bytes[2]) << 16) | (std::size_t(len_bytes[3]) << 24);
+            std::string header(header_len, ' ');
+            ifs.read(header.data(), static_cast<std::streamsize>(header_len));
+            SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != header_len, "Truncated .npy header: {}", path);
+            const NpyInfo info = parse_npy_header(header);
+
+            std::string want = npy_descr(t.dtype);
+            std::string have = info.descr;
+            if (!have.empty() && (have[0] == '=' || have[0] == '|')) have[0] = '<';     // native order on this host is little-endian
+            SB_THROW_IF(have != want, "Data type mismatch in .npy header: file has '{}', tensor needs '{}'.", info.descr, want);
+            SB_THROW_IF(static_cast<int32_t>(info.shape.size()) != t.rank, "Rank mismatch in .npy header: file has {}, tensor has {}.",
+                        info.shape.size(), t.rank);
+            for (int i = 0; i < t.rank; ++i)
+                SB_THROW_IF(info.shape[static_cast<std::size_t>(i)] != t.shape[i], "Shape dimension {} mismatch in .npy header.", i);
+            int wide_dims = 0;
+            for (int i = 0; i < t.rank; ++i) wide_dims += t.shape[i] > 1;
+            SB_THROW_IF(wide_dims > 1 && info.fortran_order != (t.layout == Core::Layout::COLUMN_MAJOR),
+                        "Memory order mismatch in .npy header: fortran_order is {}.", info.fortran_order ? "True" : "False");
+            read_payload(ifs, t, path);
+        }
+    } // namespace detail
 
     inline void IO::save_npy(const Tensor& t, const std::string& path)
     {
-        SB_THROW_IF(detail::npy_descr(t.dtype)[0] == '\0', "Unsupported data type for .npy export.");
         engine_.execute().wait();
-        std::ofstream ofs(path, std::ios::binary);
-        SB_THROW_IF(!ofs.is_open(), "Failed to open file: {}", path);
-        const std::string dict = detail::npy_header_dict(t.dtype, t.layout, t.shape.data(), t.rank);
-        SB_THROW_IF(dict.size() > 65535, "Tensor shape does not fit a version 1.0 .npy header");
-        const unsigned char preamble[10] = {0x93, 'N', 'U', 'M', 'P', 'Y', 1, 0,
-                                            static_cast<unsigned char>(dict.size() & 0xff),
-                                            static_cast<unsigned char>(dict.size() >> 8)};
-        ofs.write(reinterpret_cast<const char*>(preamble), 10);
-        ofs.write(dict.data(), static_cast<std::streamsize>(dict.size()));
-        write_payload(ofs, t);
+        detail::save_npy_file(t, path);
         SB_LOG_INFO("Exported NumPy file: {}", path);
     }
 
     inline void IO::load_npy(Tensor& t, const std::string& path)
     {
         engine_.execute().wait();
-        std::ifstream ifs(path, std::ios::binary);
-        SB_THROW_IF(!ifs.is_open(), "Failed to open file for reading: {}", path);
-        unsigned char pre[8] = {0};
-        ifs.read(reinterpret_cast<char*>(pre), 8);
-        SB_THROW_IF(ifs.gcount() != 8 || std::memcmp(pre, "\x93NUMPY", 6) != 0, "Invalid .npy file magic.");
-        const int major = pre[6];
-        SB_THROW_IF(major < 1 || major > 3, "Unsupported .npy format version {}.{}", major, int(pre[7]));
-        unsigned char len_bytes[4] = {0};
-        const int len_size = (major == 1) ? 2 : 4;
-        ifs.read(reinterpret_cast<char*>(len_bytes), len_size);
-        SB_THROW_IF(ifs.gcount() != len_size, "Truncated .npy header: {}", path);
-        const std::size_t header_len = std::size_t(len_bytes[0]) | (std::size_t(len_bytes[1]) << 8) |
-                                       (std::size_t(len_bytes[2]) << 16) | (std::size_t(len_bytes[3]) << 24);
-        std::string header(header_len, ' ');
-        ifs.read(header.data(), static_cast<std::streamsize>(header_len));
-        SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != header_len, "Truncated .npy header: {}", path);
-        const detail::NpyInfo info = detail::parse_npy_header(header);
-
-        std::string want = detail::npy_descr(t.dtype);
-        std::string have = info.descr;
-        if (!have.empty() && (have[0] == '=' || have[0] == '|')) have[0] = '<';     // native order on this host is little-endian
-        SB_THROW_IF(have != want, "Data type mismatch in .npy header: file has '{}', tensor needs '{}'.", info.descr, want);
-        SB_THROW_IF(static_cast<int32_t>(info.shape.size()) != t.rank, "Rank mismatch in .npy header: file has {}, tensor has {}.",
-                    info.shape.size(), t.rank);
-        for (int i = 0; i < t.rank; ++i)
-            SB_THROW_IF(info.shape[static_cast<std::size_t>(i)] != t.shape[i], "Shape dimension {} mismatch in .npy header.", i);
-        int wide_dims = 0;
-        for (int i = 0; i < t.rank; ++i) wide_dims += t.shape[i] > 1;
-        SB_THROW_IF(wide_dims > 1 && info.fortran_order != (t.layout == Core::Layout::COLUMN_MAJOR),
-                    "Memory order mismatch in .npy header: fortran_order is {}.", info.fortran_order ? "True" : "False");
-        read_payload(ifs, t, path);
+        detail::load_npy_file(t, path);
         SB_LOG_INFO("Loaded NumPy file: {}", path);
     }
 
@@ -658,7 +673,7 @@ namespace SushiBLAS
         engine_.execute().wait();
         std::ofstream ofs(path, std::ios::binary);
         SB_THROW_IF(!ofs.is_open(), "Failed to open file: {}", path);
-        write_payload(ofs, t);
+        detail::write_payload(ofs, t);
     }
 
     inline void IO::load_bin(Tensor& t, const std::string& path)
@@ -666,7 +681,7 @@ namespace SushiBLAS
         engine_.execute().wait();
         std::ifstream ifs(path, std::ios::binary);
         SB_THROW_IF(!ifs.is_open(), "Failed to open file: {}", path);
-        read_payload(ifs, t, path);
+        detail::read_payload(ifs, t, path);
     }
 
 } // namespace SushiBLAS

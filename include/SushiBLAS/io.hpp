@@ -133,8 +133,6 @@ namespace SushiBLAS
             inline void load_bin(Tensor& t, const std::string& path);
 
         private:
-            inline void write_payload(std::ofstream& ofs, const Tensor& t);
-            inline void read_payload(std::ifstream& ifs, Tensor& t, const std::string& path);
             Engine& engine_;
     };
 } // namespace SushiBLAS

@@ -5,6 +5,9 @@
 // RuntimeContext without a device.
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
+#include <iterator>
+#include <vector>
 #include <SushiBLAS/SushiBLAS.h>
 #include "check.hpp"
 
@@ -180,6 +183,37 @@ TEST_CASE(npy_header_is_what_numpy_writes_and_parses_back)
     EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'fortran_order': 0, 'shape': (3,)}"), "neither True nor False");
     EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (3, x)}"), "bad character");
     EXPECT_THROWS(sb::detail::parse_npy_header("{'descr': '<f4', 'fortran_order': False, 'shape': (3, 4"), "unterminated shape");
+}
+
+TEST_CASE(npy_files_round_trip_on_the_host)
+{
+    // the file routines behind IO::save_npy / load_npy with host-resident tensors: no device involved
+    const char* dir = std::getenv("SUSHI_TEST_TMPDIR");
+    const std::string base = std::string(dir ? dir : "/tmp") + "/host_logic_";
+    auto al = sr::make_sushi<MallocAllocator>();
+    auto t = make(al, {3, 5});
+    for (int i = 0; i < 15; ++i) t.data_as<float>()[i] = 0.25f * float(i) - 1.0f;
+    sb::detail::save_npy_file(t, base + "rowmajor.npy");
+    auto back = make(al, {3, 5});
+    sb::detail::load_npy_file(back, base + "rowmajor.npy");
+    for (int i = 0; i < 15; ++i) EXPECT_EQ(back.data_as<float>()[i], t.data_as<float>()[i]);
+    // the file is 10 bytes of preamble, a header that ends on a 64-byte boundary, then the raw elements
+    {
+        std::ifstream f(base + "rowmajor.npy", std::ios::binary);
+        std::vector<char> bytes((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+        EXPECT_EQ(bytes.size(), size_t(128 + 15 * 4));
+        EXPECT_TRUE(std::memcmp(bytes.data(), "\x93NUMPY\x01\x00\x76\x00", 10) == 0);
+        EXPECT_TRUE(std::memcmp(bytes.data() + 128, t.data(), 60) == 0);
+    }
+    auto col = make(al, {3, 5}, sb::Core::Layout::COLUMN_MAJOR);
+    for (int i = 0; i < 15; ++i) col.data_as<float>()[i] = float(i);
+    sb::detail::save_npy_file(col, base + "fortran.npy");
+    EXPECT_THROWS(sb::detail::load_npy_file(back, base + "fortran.npy"), "Memory order mismatch");
+    auto wrong = make(al, {5, 3});
+    EXPECT_THROWS(sb::detail::load_npy_file(wrong, base + "rowmajor.npy"), "Shape dimension 0 mismatch");
+    EXPECT_THROWS(sb::detail::load_npy_file(back, base + "missing.npy"), "Failed to open file for reading");
+    auto view = t.transpose(0, 1);
+    EXPECT_THROWS(sb::detail::save_npy_file(view, base + "view.npy"), "contiguous");
 }
 
 TEST_CASE(runtime_context_fails_loudly_without_a_device)

@@ -21,9 +21,17 @@ def _run(exe):
     return p.stdout
 
 
-def test_cpp_host_logic(binaries):
-    out = _run(binaries["test_host_logic"])
-    assert "gemm_parameter_derivation" in out
+def test_cpp_host_logic(binaries, tmp_path):
+    env = dict(os.environ, SUSHI_TEST_TMPDIR=str(tmp_path))
+    p = subprocess.run([binaries["test_host_logic"]], capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0 and " 0 failed" in p.stdout, p.stdout + p.stderr
+    assert "gemm_parameter_derivation" in p.stdout
+    # the .npy files the C++ side wrote from host-resident tensors open in numpy with the right order and values
+    a = np.load(tmp_path / "host_logic_rowmajor.npy")
+    assert a.dtype == np.float32 and a.shape == (3, 5) and not np.isfortran(a)
+    assert np.array_equal(a.ravel(), 0.25 * np.arange(15, dtype=np.float32) - 1.0)
+    f = np.load(tmp_path / "host_logic_fortran.npy")
+    assert np.isfortran(f) and np.array_equal(f.ravel(order="F"), np.arange(15, dtype=np.float32))
 
 
 @pytest.mark.gpu
