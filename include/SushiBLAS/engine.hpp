@@ -652,7 +652,64 @@ namespace SushiBLAS
                         "Memory order mismatch in .npy header: fortran_order is {}.", info.fortran_order ? "True" : "False");
             read_payload(ifs, t, path);
         }
+        // Native ".sushi" container (src/io.cpp:40-109): the reference dumps a struct
+        //   { char magic[6] = "SUSHI"; uint32 version = 1; int32 rank; int64 shape[6]; int32 dtype; int32 layout; }
+        // as the compiler lays it out on x86-64 -- magic at 0, version at 8, rank at 12, shape at 16, dtype at 64,
+        // layout at 68, 72 bytes in all -- followed by the raw elements.  Written here field by field at those
+        // offsets (padding and unused extents zero); the loader checks what the reference checks: magic, rank
+        // and the first `rank` extents.
+        constexpr std::size_t SUSHI_HEADER_BYTES = 72;
+
+        inline void save_sushi_file(const Tensor& t, const std::string& path)
+        {
+            unsigned char h[SUSHI_HEADER_BYTES] = {0};
+            std::memcpy(h, "SUSHI", 6);
+            const std::uint32_t version = 1;
+            const std::int32_t rank = t.rank, dtype = static_cast<std::int32_t>(t.dtype), layout = static_cast<std::int32_t>(t.layout);
+            std::memcpy(h + 8, &version, 4);
+            std::memcpy(h + 12, &rank, 4);
+            for (int i = 0; i < t.rank; ++i) std::memcpy(h + 16 + 8 * i, &t.shape[i], 8);
+            std::memcpy(h + 64, &dtype, 4);
+            std::memcpy(h + 68, &layout, 4);
+            std::ofstream ofs(path, std::ios::binary);
+            SB_THROW_IF(!ofs.is_open(), "Failed to open file for writing: {}", path);
+            ofs.write(reinterpret_cast<const char*>(h), SUSHI_HEADER_BYTES);
+            write_payload(ofs, t);
+        }
+
+        inline void load_sushi_file(Tensor& t, const std::string& path)
+        {
+            std::ifstream ifs(path, std::ios::binary);
+            SB_THROW_IF(!ifs.is_open(), "Failed to open file for reading: {}", path);
+            unsigned char h[SUSHI_HEADER_BYTES] = {0};
+            ifs.read(reinterpret_cast<char*>(h), SUSHI_HEADER_BYTES);
+            SB_THROW_IF(static_cast<std::size_t>(ifs.gcount()) != SUSHI_HEADER_BYTES || std::memcmp(h, "SUSHI", 5) != 0,
+                        "Invalid .sushi file magic.");
+            std::int32_t rank = 0;
+            std::memcpy(&rank, h + 12, 4);
+            SB_THROW_IF(rank != t.rank, "Rank mismatch in .sushi file.");
+            for (int i = 0; i < t.rank; ++i)
+            {
+                std::int64_t extent = 0;
+                std::memcpy(&extent, h + 16 + 8 * i, 8);
+                SB_THROW_IF(extent != t.shape[i], "Dimension mismatch at index {}", i);
+            }
+            read_payload(ifs, t, path);
+        }
     } // namespace detail
+
+    inline void IO::save(const Tensor& t, const std::string& path)
+    {
+        engine_.execute().wait();
+        detail::save_sushi_file(t, path);
+        SB_LOG_INFO("Saved native SushiBLAS file: {}", path);
+    }
+
+    inline void IO::load(Tensor& t, const std::string& path)
+    {
+        engine_.execute().wait();
+        detail::load_sushi_file(t, path);
+    }
 
     inline void IO::save_npy(const Tensor& t, const std::string& path)
     {

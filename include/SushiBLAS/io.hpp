@@ -1,5 +1,5 @@
-// io.hpp -- tensor persistence in NumPy's .npy format and as raw bytes (reference:
-// include/SushiBLAS/io.hpp:47-125, src/io.cpp:111-240).  Same entry points and the same
+// io.hpp -- tensor persistence in the native ".sushi" container, in NumPy's .npy format and as raw bytes
+// (reference: include/SushiBLAS/io.hpp:47-125, src/io.cpp:40-240; print / to_string are not provided).  Same entry points and the same
 // staging convention: pending work is flushed first (execute().wait()), a DEVICE tensor goes
 // through a host buffer (src/io.cpp:73-78, 187-193), SHARED / HOST tensors are written from
 // their host image.  The .npy writer emits format version 1.0 with the dictionary padded so
@@ -123,6 +123,10 @@ namespace SushiBLAS
         public:
             explicit IO(Engine& e) : engine_(e) {}
 
+            /// Native ".sushi" container: a 72-byte header (magic, version, rank, extents, dtype, layout) and
+            /// the raw elements (src/io.cpp:40-109).
+            inline void save(const Tensor& t, const std::string& path);
+            inline void load(Tensor& t, const std::string& path);
             /// Writes `t` as a NumPy .npy file that numpy.load() opens (src/io.cpp:136-196).
             /// Flushes the engine's pending tasks first.  The tensor must be contiguous.
             inline void save_npy(const Tensor& t, const std::string& path);

@@ -214,6 +214,29 @@ TEST_CASE(npy_files_round_trip_on_the_host)
     EXPECT_THROWS(sb::detail::load_npy_file(back, base + "missing.npy"), "Failed to open file for reading");
     auto view = t.transpose(0, 1);
     EXPECT_THROWS(sb::detail::save_npy_file(view, base + "view.npy"), "contiguous");
+
+    // native container (src/io.cpp:40-109): 72-byte header at the offsets of the reference's struct, then the elements
+    sb::detail::save_sushi_file(t, base + "native.sushi");
+    {
+        std::ifstream f(base + "native.sushi", std::ios::binary);
+        std::vector<unsigned char> bytes((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+        EXPECT_EQ(bytes.size(), size_t(72 + 60));
+        EXPECT_TRUE(std::memcmp(bytes.data(), "SUSHI\0", 6) == 0);
+        int32_t version, rank, dtype, layout; int64_t d0, d1;
+        std::memcpy(&version, &bytes[8], 4); std::memcpy(&rank, &bytes[12], 4);
+        std::memcpy(&d0, &bytes[16], 8); std::memcpy(&d1, &bytes[24], 8);
+        std::memcpy(&dtype, &bytes[64], 4); std::memcpy(&layout, &bytes[68], 4);
+        EXPECT_EQ(version, 1); EXPECT_EQ(rank, 2); EXPECT_EQ(d0, 3); EXPECT_EQ(d1, 5);
+        EXPECT_EQ(dtype, int32_t(sb::Core::DataType::FLOAT32)); EXPECT_EQ(layout, int32_t(sb::Core::Layout::ROW_MAJOR));
+        EXPECT_TRUE(std::memcmp(&bytes[72], t.data(), 60) == 0);
+    }
+    auto again = make(al, {3, 5});
+    sb::detail::load_sushi_file(again, base + "native.sushi");
+    for (int i = 0; i < 15; ++i) EXPECT_EQ(again.data_as<float>()[i], t.data_as<float>()[i]);
+    EXPECT_THROWS(sb::detail::load_sushi_file(wrong, base + "native.sushi"), "Dimension mismatch at index 0");
+    auto rank1 = make(al, {15});
+    EXPECT_THROWS(sb::detail::load_sushi_file(rank1, base + "native.sushi"), "Rank mismatch");
+    EXPECT_THROWS(sb::detail::load_sushi_file(again, base + "rowmajor.npy"), "Invalid .sushi file magic");
 }
 
 TEST_CASE(runtime_context_fails_loudly_without_a_device)
