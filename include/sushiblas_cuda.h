@@ -176,7 +176,7 @@ SUSHI_CUDA_API int sushi_cuda_dgemm_strided_batched(sushi_cuda_ctx* ctx, int dev
  *     left != 0:  op(A) * X = alpha * B,  A is m x m        left == 0:  X * op(A) = alpha * B,  A is n x n
  * A is upper (upper != 0) or lower triangular; only that triangle is read, and its diagonal is
  * taken as 1 when unit_diag != 0.  Replaces oneapi::mkl::blas::row_major::trsm / trsm_batch (call
- * sites src/ops/blas/level3/trsm.cpp:61-79).  Recursive blocked substitution: ranges of 256-wide
+ * sites src/ops/blas/level3/trsm.cpp:61-79).  Recursive blocked substitution: ranges of 512-wide
  * blocks of the triangular dimension are halved, each halving costing one GEMM update on the
  * regular GEMM kernels, and single blocks are applied through their explicit inverses (a small
  * substitution kernel plus two batched GEMMs), so large solves run on the tensor cores.

@@ -961,13 +961,13 @@ extern "C" int sushi_cuda_ssyrk(sushi_cuda_ctx* ctx, int dev, int upper, int tra
 namespace {
 
 // One triangular solve, row-major:  left: op(A) X = alpha B (A m x m);  right: X op(A) = alpha B (A n x n);
-// X overwrites B.  Recursive blocked substitution over 256-wide blocks of the triangular dimension:
+// X overwrites B.  Recursive blocked substitution over 512-wide blocks of the triangular dimension:
 // a range of blocks is cut in two, the first half is solved, its contribution is removed from the
 // second half with ONE GEMM (alpha = -1, beta = 1, in place; at the top level half of all the
 // flops), then the second half is solved.  A single block is applied through its explicit inverse
-// (a GEMM into a temporary, copied back).  The 256 x 256 inverses come from the substitution
-// kernel on the 128 x 128 diagonal sub-blocks, completed by inv21 = -inv22 * T21 * inv11 (lower;
-// inv12 = -inv11 * T12 * inv22 for upper) as two batched GEMMs.
+// (a GEMM into a temporary, copied back).  The 512 x 512 inverses come from the substitution
+// kernel on the 128 x 128 diagonal sub-blocks, assembled level by level (128 -> 256 -> 512) with
+// inv21 = -inv22 * T21 * inv11 (lower; inv12 = -inv11 * T12 * inv22 for upper) as batched GEMMs.
 int run_trsm(sushi_cuda_ctx* ctx, DeviceState& d, int left, int upper, int trans, int unit_diag, int64_t m, int64_t n,
              float alpha, const float* a, int64_t lda, float* b, int64_t ldb)
 {
@@ -987,9 +987,10 @@ int run_trsm(sushi_cuda_ctx* ctx, DeviceState& d, int left, int upper, int trans
     };
     if (alpha == 0.0f) return scale_b(0.0f);                    // BLAS convention: B <- 0 without reading A
 
-    // workspace: the inverses, the 128 x 128 products T21 * inv11, one block row / column of temporaries
+    // workspace: the inverses, one 256 x 256 product T21 * inv11 per block, one block row / column of temporaries
+    constexpr int64_t WB = NB / 2;
     const size_t inv_bytes = (size_t)nblk * NB * NB * sizeof(float);
-    const size_t w_bytes = (size_t)nblk * HB * HB * sizeof(float);
+    const size_t w_bytes = (size_t)nblk * WB * WB * sizeof(float);
     const size_t tmp_bytes = (size_t)NB * (size_t)(left ? n : m) * sizeof(float);
     int rc = grow(ctx, d, &d.trsm_buf, &d.trsm_bytes, inv_bytes + w_bytes + tmp_bytes);
     if (rc != SUSHI_CUDA_OK) return rc;
@@ -1003,33 +1004,42 @@ int run_trsm(sushi_cuda_ctx* ctx, DeviceState& d, int left, int upper, int trans
     SC_CUDA(ctx, sushi::launch_trtri_diag_blocks(t, d.stream));
     ctx->launches++;
 
-    // complete the 256 x 256 inverses: `count` blocks starting at block q0 whose second sub-block has r2 rows
-    auto complete = [&](int64_t q0, int64_t count, int64_t r2) -> int {
+    // Inverse of a diagonal block of order 2L from the inverses of its halves of order L:
+    //   lower:  inv21 = -inv22 * T21 * inv11        upper:  inv12 = -inv11 * T12 * inv22
+    // for `count` consecutive 512-blocks starting at q0, the 2L block sitting `off` rows into each of them and
+    // its second half holding r2 <= L rows of the matrix (the rest of that half is identity padding).
+    auto pair_up = [&](int64_t L, int64_t off, int64_t q0, int64_t count, int64_t r2) -> int {
         if (count <= 0 || r2 <= 0) return SUSHI_CUDA_OK;
-        const int64_t p0 = q0 * NB;
-        float* blk = inv + q0 * NB * NB;
-        float* wq = w + q0 * HB * HB;
-        const int64_t sa = NB * (lda + 1), si = NB * NB, sw = HB * HB;
+        const int64_t p0 = q0 * NB + off;
+        float* i11 = inv + q0 * NB * NB + off * (NB + 1);
+        float* i22 = i11 + L * (NB + 1);
+        float* wq = w + q0 * WB * WB;
+        const int64_t sa = NB * (lda + 1), si = NB * NB, sw = WB * WB;
         int r;
         if (eff_lower)
         {
-            // T21 = op(A)[p0+128 .., p0 ..] (r2 x 128);  W = T21 * inv11;  inv21 = -inv22 * W
-            const float* t21 = trans ? a + p0 * lda + p0 + HB : a + (p0 + HB) * lda + p0;
-            r = run_gemm(ctx, d, trans, 0, r2, HB, HB, 1.0f, t21, lda, sa, blk, NB, si, 0.0f, wq, HB, sw, count);
+            // T21 = op(A)[p0 + L .., p0 ..] (r2 x L);  W = T21 * inv11;  inv21 = -inv22 * W
+            const float* t21 = trans ? a + p0 * lda + p0 + L : a + (p0 + L) * lda + p0;
+            r = run_gemm(ctx, d, trans, 0, r2, L, L, 1.0f, t21, lda, sa, i11, NB, si, 0.0f, wq, L, sw, count);
             if (r != SUSHI_CUDA_OK) return r;
-            return run_gemm(ctx, d, 0, 0, r2, HB, r2, -1.0f, blk + HB * NB + HB, NB, si, wq, HB, sw, 0.0f, blk + HB * NB, NB, si, count);
+            return run_gemm(ctx, d, 0, 0, r2, L, r2, -1.0f, i22, NB, si, wq, L, sw, 0.0f, i11 + L * NB, NB, si, count);
         }
-        // T12 = op(A)[p0 .., p0+128 ..] (128 x r2);  W = T12 * inv22;  inv12 = -inv11 * W
-        const float* t12 = trans ? a + (p0 + HB) * lda + p0 : a + p0 * lda + p0 + HB;
-        r = run_gemm(ctx, d, trans, 0, HB, r2, r2, 1.0f, t12, lda, sa, blk + HB * NB + HB, NB, si, 0.0f, wq, HB, sw, count);
+        // T12 = op(A)[p0 .., p0 + L ..] (L x r2);  W = T12 * inv22;  inv12 = -inv11 * W
+        const float* t12 = trans ? a + (p0 + L) * lda + p0 : a + p0 * lda + p0 + L;
+        r = run_gemm(ctx, d, trans, 0, L, r2, r2, 1.0f, t12, lda, sa, i22, NB, si, 0.0f, wq, L, sw, count);
         if (r != SUSHI_CUDA_OK) return r;
-        return run_gemm(ctx, d, 0, 0, HB, r2, HB, -1.0f, blk, NB, si, wq, HB, sw, 0.0f, blk + HB, NB, si, count);
+        return run_gemm(ctx, d, 0, 0, L, r2, L, -1.0f, i11, NB, si, wq, L, sw, 0.0f, i11 + L, NB, si, count);
     };
-    const int64_t full = dim / NB;                               // blocks with both sub-blocks complete
-    rc = complete(0, full, HB);
-    if (rc != SUSHI_CUDA_OK) return rc;
-    if (full < nblk && dim - full * NB > HB) rc = complete(full, 1, dim - full * NB - HB);
-    if (rc != SUSHI_CUDA_OK) return rc;
+    for (int64_t L = HB; L < NB; L *= 2)
+        for (int64_t off = 0; off < NB; off += 2 * L)
+        {
+            // 512-blocks whose 2L block at `off` lies wholly inside the matrix run as one batched call,
+            // the (at most one) partial one after them on its own
+            const int64_t full = dim >= off + 2 * L ? (dim - off - 2 * L) / NB + 1 : 0;
+            if ((rc = pair_up(L, off, 0, full, L)) != SUSHI_CUDA_OK) return rc;
+            const int64_t p0 = full * NB + off;
+            if (p0 + L < dim && (rc = pair_up(L, off, full, 1, dim - p0 - L)) != SUSHI_CUDA_OK) return rc;
+        }
 
     if (alpha != 1.0f) { rc = scale_b(alpha); if (rc != SUSHI_CUDA_OK) return rc; }
 

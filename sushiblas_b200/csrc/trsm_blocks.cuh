@@ -2,13 +2,13 @@
 //
 // TRSM (reference: src/ops/blas/level3/trsm.cpp:85-202, forwarding to oneMKL trsm[_batch] at
 // trsm.cpp:61-79) is run as a recursive blocked substitution: the off-diagonal work is GEMM
-// updates on the regular GEMM kernels, and each 256 x 256 diagonal block of op(A) is applied
+// updates on the regular GEMM kernels, and each 512 x 512 diagonal block of op(A) is applied
 // through its explicit inverse.  This kernel inverts the 128 x 128 diagonal sub-blocks (the host
-// then completes each 256 block with two small GEMMs).  One CTA per sub-block, thread j owns
-// column j of the inverse and runs the substitution for it out of shared memory (reads of T are
-// broadcasts, writes of the column are conflict-free).  Sub-block d is written at
-// inv + (d / 2) * 256 * 256 + (d % 2) * (128 * 256 + 128) with leading dimension 256, i.e. onto
-// the diagonal of its 256 x 256 block; rows and columns beyond the matrix become identity.
+// then assembles the 256 and 512 blocks from their halves with batched GEMMs).  One CTA per
+// sub-block, thread j owns column j of the inverse and runs the substitution for it out of shared
+// memory (reads of T are broadcasts, writes of the column are conflict-free).  Sub-block d is
+// written at inv + (d / 4) * 512 * 512 + (d % 4) * (128 * 512 + 128) with leading dimension 512,
+// i.e. onto the diagonal of its 512 x 512 block; rows and columns beyond the matrix become identity.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -16,12 +16,13 @@
 namespace sushi {
 
 constexpr int TRSM_NB = 128;       // order of the sub-blocks inverted by substitution
-constexpr int TRSM_BASE = 256;     // order of the diagonal blocks applied as explicit inverses
+constexpr int TRSM_BASE = 512;     // order of the diagonal blocks applied as explicit inverses
+constexpr int TRSM_SUBS = TRSM_BASE / TRSM_NB;
 
 struct TrtriArgs
 {
     const float* a;        // triangular matrix (dim x dim, leading dimension lda)
-    float* inv;            // out: [ceil(dim / 256)][256][256]; this kernel fills the two 128 x 128 diagonal sub-blocks
+    float* inv;            // out: [ceil(dim / 512)][512][512]; this kernel fills the four 128 x 128 diagonal sub-blocks
     int64_t dim, lda;
     int trans;             // op(A) = A^T
     int eff_lower;         // op(A) is lower triangular
@@ -73,8 +74,8 @@ trtri_diag_blocks_kernel(const TrtriArgs p)
         }
     }
     __syncthreads();
-    float* out = p.inv + (int64_t)(blockIdx.x / 2) * TRSM_BASE * TRSM_BASE +
-                 (int64_t)(blockIdx.x % 2) * (TRSM_NB * TRSM_BASE + TRSM_NB);
+    float* out = p.inv + (int64_t)(blockIdx.x / TRSM_SUBS) * TRSM_BASE * TRSM_BASE +
+                 (int64_t)(blockIdx.x % TRSM_SUBS) * (TRSM_NB * TRSM_BASE + TRSM_NB);
     for (int i = 0; i < TRSM_NB; ++i) out[i * TRSM_BASE + j] = X[i][j];
 }
 
@@ -82,7 +83,7 @@ inline size_t trtri_smem_bytes() { return sizeof(float) * (TRSM_NB * (TRSM_NB + 
 
 inline cudaError_t launch_trtri_diag_blocks(const TrtriArgs& p, cudaStream_t st)
 {
-    const int64_t blocks = 2 * ((p.dim + TRSM_BASE - 1) / TRSM_BASE);
+    const int64_t blocks = TRSM_SUBS * ((p.dim + TRSM_BASE - 1) / TRSM_BASE);
     if (blocks <= 0) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(trtri_diag_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)trtri_smem_bytes());
