@@ -359,10 +359,12 @@ __device__ __forceinline__ TileCoord decode_tile(int64_t t, int32_t tiles_m, int
 // destination (C, or the slot of a published K slice with ldc = BN, alpha = 1).
 // `contrib` (owner of a cut tile): the same position inside the first published slot; n_contrib
 // slots, contrib_stride floats apart, are added before alpha/beta.
-template <bool HAS_BETA, bool RELU>
+// ACT: 0 none, 1 ReLU, 2 any activation of activation.cuh (chosen at run time by `act`).
+template <bool HAS_BETA, int ACT>
 __device__ __forceinline__ void epilogue_fast(uint32_t taddr0, float4* stg, float* __restrict__ dst, int64_t ldc,
                                               float alpha, float beta, int lane,
-                                              const float* contrib = nullptr, int n_contrib = 0, size_t contrib_stride = 0)
+                                              const float* contrib = nullptr, int n_contrib = 0, size_t contrib_stride = 0,
+                                              int act = 0, float act_param = 0.0f)
 {
     const int rsub = lane >> 3, c4 = lane & 7;
     const int64_t row_step = 4 * ldc;
@@ -419,9 +421,14 @@ __device__ __forceinline__ void epilogue_fast(uint32_t taddr0, float4* stg, floa
                 o.x = fmaf(beta, old[i].x, o.x); o.y = fmaf(beta, old[i].y, o.y);
                 o.z = fmaf(beta, old[i].z, o.z); o.w = fmaf(beta, old[i].w, o.w);
             }
-            if (RELU)
+            if (ACT == 1)
             {
                 o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f);
+            }
+            if (ACT == 2)
+            {
+                o.x = apply_act(o.x, act, act_param); o.y = apply_act(o.y, act, act_param);
+                o.z = apply_act(o.z, act, act_param); o.w = apply_act(o.w, act, act_param);
             }
             *reinterpret_cast<float4*>(out + i * row_step) = o;
         }
@@ -727,15 +734,13 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int slot_row0 = h * 128 + q * 32;
 
             // work items that lie wholly inside their destination take the lean path
-            // (activations other than ReLU take the general path)
-            const bool inside_c = p.lean_epilogue && vec_ok && p.tri == 0 && p.act <= ACT_RELU && row_base + 32 <= p.m &&
-                                  col_base + BN <= p.n;
+            const bool inside_c = p.lean_epilogue && vec_ok && p.tri == 0 && row_base + 32 <= p.m && col_base + BN <= p.n;
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256);
             const size_t slot_pos = (size_t)(slot_row0 + rsub) * BN + c4 * 4;       // this lane inside a 256 x 256 slot
             if (partial && p.lean_epilogue)
             {
                 // raw accumulators into this slice's slot (alpha = 1, no beta, dense 256-wide rows)
-                epilogue_fast<false, false>(taddr0, stg, my_slot + slot_pos, BN, 1.0f, 0.0f, lane);
+                epilogue_fast<false, 0>(taddr0, stg, my_slot + slot_pos, BN, 1.0f, 0.0f, lane);
             }
             else if (inside_c)
             {
@@ -745,13 +750,17 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const size_t cstride = (size_t)p.sk_tiles * SK_SLOT_FLOATS;
                 if (has_beta)
                 {
-                    if (p.act) epilogue_fast<true, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
-                    else epilogue_fast<true, false>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    if (p.act > ACT_RELU)
+                        epilogue_fast<true, 2>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride, p.act, p.act_param);
+                    else if (p.act) epilogue_fast<true, 1>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    else epilogue_fast<true, 0>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
                 }
                 else
                 {
-                    if (p.act) epilogue_fast<false, true>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
-                    else epilogue_fast<false, false>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    if (p.act > ACT_RELU)
+                        epilogue_fast<false, 2>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride, p.act, p.act_param);
+                    else if (p.act) epilogue_fast<false, 1>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
+                    else epilogue_fast<false, 0>(taddr0, stg, dst, p.ldc, p.alpha, p.beta, lane, contrib, n_contrib, cstride);
                 }
             }
             else if (partial || row_base < p.m)
