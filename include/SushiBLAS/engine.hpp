@@ -6,6 +6,11 @@
 #pragma once
 
 #include <atomic>
+#include <cmath>
+#include <sstream>
+#include <iomanip>
+#include <functional>
+#include <cstdio>
 #include <cstdint>
 #include <initializer_list>
 #include <vector>
@@ -697,6 +702,88 @@ namespace SushiBLAS
             read_payload(ifs, t, path);
         }
     } // namespace detail
+
+    namespace detail
+    {
+        // Text form of a tensor (src/io.cpp:242-359): "Tensor(shape=[..], dtype=f32):" and the nested rows with
+        // `precision` fixed decimals; a dimension longer than 2 * edge_items shows its first and last edge_items
+        // entries around "...".  Elements are addressed through the tensor's strides, so views print as they index.
+        inline std::string format_tensor(const Tensor& t, int precision, int edge_items)
+        {
+            SB_THROW_IF(!t.storage, "Accessing data of a tensor with no storage");
+            const bool cplx = t.dtype == Core::DataType::COMPLEX32 || t.dtype == Core::DataType::COMPLEX64;
+            const bool wide = t.dtype == Core::DataType::FLOAT64 || t.dtype == Core::DataType::COMPLEX64;
+            SB_THROW_IF(t.dtype == Core::DataType::HALF, "Unsupported data type for printing.");
+            // elements spanned from data(): 1 + sum (extent - 1) * stride
+            std::int64_t span = t.num_elements > 0 ? 1 : 0;
+            for (int i = 0; i < t.rank && span > 0; ++i) span += (t.shape[i] - 1) * t.strides[i];
+            const std::size_t elem = io_bytes_per_element(t.dtype);
+            std::vector<char> host(static_cast<std::size_t>(span) * elem);
+            if (span > 0)
+            {
+                if (t.storage->host_resident()) std::memcpy(host.data(), t.data(), host.size());
+                else
+                {
+                    SB_THROW_IF(!t.is_contiguous(), "Tensor must be contiguous for this operation");
+                    t.to_host(host.data());
+                }
+            }
+            auto value = [&](std::int64_t idx) -> std::string
+            {
+                double re = 0.0, im = 0.0;
+                if (wide) { const double* p = reinterpret_cast<const double*>(host.data()) + idx * (cplx ? 2 : 1); re = p[0]; if (cplx) im = p[1]; }
+                else { const float* p = reinterpret_cast<const float*>(host.data()) + idx * (cplx ? 2 : 1); re = p[0]; if (cplx) im = p[1]; }
+                std::ostringstream v;
+                v << std::fixed << std::setprecision(precision);
+                // the reference converts to float before printing
+                if (std::abs(static_cast<float>(im)) < 1e-9) v << static_cast<float>(re);
+                else v << "(" << static_cast<float>(re) << (im >= 0 ? "+" : "") << static_cast<float>(im) << "j)";
+                return v.str();
+            };
+            std::ostringstream os;
+            os << "Tensor(shape=[";
+            for (int i = 0; i < t.rank; ++i) os << t.shape[i] << (i == t.rank - 1 ? "" : ", ");
+            os << "], dtype=" << (t.dtype == Core::DataType::FLOAT32 ? "f32" : t.dtype == Core::DataType::FLOAT64 ? "f64"
+                                  : t.dtype == Core::DataType::COMPLEX32 ? "c32" : "c64") << "):\n";
+            std::function<void(int, std::int64_t)> emit = [&](int dim, std::int64_t offset)
+            {
+                const std::int64_t extent = t.shape[dim], stride = t.strides[dim];
+                const bool last = dim == t.rank - 1;
+                const std::string indent(static_cast<std::size_t>(dim) + 1, ' ');
+                os << "[";
+                for (std::int64_t i = 0; i < extent; ++i)
+                {
+                    if (extent > 2 * edge_items && i == edge_items)
+                    {
+                        if (last) os << "... "; else os << "\n" << indent << "...\n" << indent;
+                        i = extent - edge_items - 1;        // resumes at extent - edge_items
+                        continue;
+                    }
+                    if (last) os << value(offset + i * stride) << (i == extent - 1 ? "" : ", ");
+                    else
+                    {
+                        emit(dim + 1, offset + i * stride);
+                        if (i < extent - 1) os << ",\n" << indent;
+                    }
+                }
+                os << "]";
+                if (dim == 0 && !last) os << "\n";
+            };
+            if (t.rank > 0) emit(0, 0);
+            return os.str();
+        }
+    } // namespace detail
+
+    inline std::string IO::to_string(const Tensor& t, int precision, int edge_items)
+    {
+        engine_.execute().wait();
+        return detail::format_tensor(t, precision, edge_items);
+    }
+
+    inline void IO::print(const Tensor& t, int precision, int edge_items)
+    {
+        std::fputs(to_string(t, precision, edge_items).c_str(), stdout);
+    }
 
     inline void IO::save(const Tensor& t, const std::string& path)
     {

@@ -1,5 +1,5 @@
 // io.hpp -- tensor persistence in the native ".sushi" container, in NumPy's .npy format and as raw bytes
-// (reference: include/SushiBLAS/io.hpp:47-125, src/io.cpp:40-240; print / to_string are not provided).  Same entry points and the same
+// and as text (reference: include/SushiBLAS/io.hpp:47-125, src/io.cpp:40-359).  Same entry points and the same
 // staging convention: pending work is flushed first (execute().wait()), a DEVICE tensor goes
 // through a host buffer (src/io.cpp:73-78, 187-193), SHARED / HOST tensors are written from
 // their host image.  The .npy writer emits format version 1.0 with the dictionary padded so
@@ -135,6 +135,9 @@ namespace SushiBLAS
             /// Raw element bytes without a header (src/io.cpp:111-134); also serves DEVICE tensors.
             inline void save_bin(const Tensor& t, const std::string& path);
             inline void load_bin(Tensor& t, const std::string& path);
+            /// Text form as numpy-style nested rows (src/io.cpp:242-359); print() writes it to stdout.
+            inline std::string to_string(const Tensor& t, int precision = 4, int edge_items = 3);
+            inline void print(const Tensor& t, int precision = 4, int edge_items = 3);
 
         private:
             Engine& engine_;

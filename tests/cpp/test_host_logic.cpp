@@ -239,6 +239,26 @@ TEST_CASE(npy_files_round_trip_on_the_host)
     EXPECT_THROWS(sb::detail::load_sushi_file(again, base + "rowmajor.npy"), "Invalid .sushi file magic");
 }
 
+TEST_CASE(tensor_text_form)
+{
+    // src/io.cpp:242-359: header line, nested rows, fixed decimals, "..." past 2 * edge_items entries
+    auto al = sr::make_sushi<MallocAllocator>();
+    auto t = make(al, {2, 3});
+    for (int i = 0; i < 6; ++i) t.data_as<float>()[i] = float(i);
+    EXPECT_EQ(sb::detail::format_tensor(t, 1, 3), std::string("Tensor(shape=[2, 3], dtype=f32):\n[[0.0, 1.0, 2.0],\n [3.0, 4.0, 5.0]]\n"));
+    // a transposed view prints through its strides
+    EXPECT_EQ(sb::detail::format_tensor(t.transpose(0, 1), 0, 3),
+              std::string("Tensor(shape=[3, 2], dtype=f32):\n[[0, 3],\n [1, 4],\n [2, 5]]\n"));
+    auto v = make(al, {8});
+    for (int i = 0; i < 8; ++i) v.data_as<float>()[i] = float(i) * 0.5f;
+    EXPECT_EQ(sb::detail::format_tensor(v, 2, 3), std::string("Tensor(shape=[8], dtype=f32):\n[0.00, 0.50, 1.00, ... 2.50, 3.00, 3.50]"));
+    EXPECT_EQ(sb::detail::format_tensor(v, 1, 4), std::string("Tensor(shape=[8], dtype=f32):\n[0.0, 0.5, 1.0, 1.5, 2.0, 2.5, 3.0, 3.5]"));
+    auto tall = make(al, {8, 1});
+    for (int i = 0; i < 8; ++i) tall.data_as<float>()[i] = float(i);
+    EXPECT_EQ(sb::detail::format_tensor(tall, 0, 3),
+              std::string("Tensor(shape=[8, 1], dtype=f32):\n[[0],\n [1],\n [2],\n \n ...\n [5],\n [6],\n [7]]\n"));
+}
+
 TEST_CASE(runtime_context_fails_loudly_without_a_device)
 {
     int count = 0;
