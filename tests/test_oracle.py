@@ -263,3 +263,33 @@ def test_activation_oracle_reproduces_the_reference_known_answers():
         y = oa.forward(kind, x)
         num = (oa.forward(kind, x + 1e-6) - oa.forward(kind, x - 1e-6)) / 2e-6
         assert np.allclose(oa.backward(kind, np.ones_like(x), y), num, rtol=1e-6, atol=1e-7), oa.NAMES[kind]
+
+
+def test_mkl_trsm_and_syrk_lie_within_the_bounds_of_the_oracle():
+    """The reference forwards TRSM / SYRK to oneMKL; MKL's own fp32 routines (through torch CPU) must sit inside
+    the tolerances the GPU tests use against the fp64 restatements -- so those tolerances admit the reference."""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(21)
+    m, n = 96, 40
+    for left in (1, 0):
+        for upper in (0, 1):
+            for trans in (0, 1):
+                dim = m if left else n
+                a = (rng.uniform(-1, 1, (dim, dim)) * (2.0 / dim)).astype(np.float32)
+                a[np.arange(dim), np.arange(dim)] = rng.uniform(3, 5, dim).astype(np.float32)
+                b = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+                tri = np.triu(a) if upper else np.tril(a)
+                op = tri.T if trans else tri
+                x = torch.linalg.solve_triangular(torch.from_numpy(np.ascontiguousarray(op)), torch.from_numpy(0.5 * b),
+                                                  upper=bool(upper) != bool(trans), left=bool(left)).numpy()
+                xref, t = og.trsm_f64_np(left, upper, trans, 0, m, n, 0.5, a, dim, 0, b, n, 0, 1)
+                assert og.trsm_residual_ratio(left, t[0], x, 0.5, b, dim) <= 1.0, (left, upper, trans)
+                assert np.max(np.abs(x - xref[0])) <= 32.0 * dim * 2.0 ** -24 * np.max(np.abs(xref[0]))
+    nn, k = 64, 150
+    a = rng.uniform(-1, 1, (nn, k)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (nn, nn)).astype(np.float32)
+    got = (1.5 * torch.from_numpy(a) @ torch.from_numpy(a).T + 0.5 * torch.from_numpy(c0)).numpy()
+    ref, absaa, mask = og.syrk_f64_np(0, 0, nn, k, 1.5, a, k, 0, 0.5, c0, nn, 0, 1)
+    r, _ = og.tolerance_ratio(np.where(mask, got, 0.0)[None], np.where(mask[None], ref, 0.0), absaa, k, beta=0.5,
+                              c_in=np.where(mask, c0, 0.0)[None], budget=0.5)
+    assert r <= 1.0
