@@ -382,11 +382,19 @@ __global__ void scale_c_f64_kernel(double* c, int64_t m, int64_t n, int64_t ldc,
     }
 }
 
-// The 128-tile when it yields at least one wave of CTAs, else the 64-tile.
+// Tile choice by estimated time: whole rounds of 148 CTAs at the measured full-rate throughput of each tile
+// (128 x 128: 33.5 TFLOP/s, 64 x 64: 30.4 on B200); a 128-tile does four times the work of a 64-tile.  The small
+// tile wins when the large one would leave most of a round idle (1024^3: 64 tiles; 2048^3: 1.73 rounds).
 inline cudaError_t launch_dgemm(const DgemmArgs& a, bool ta, bool tb, int64_t batch, int sm_count, cudaStream_t st)
 {
-    const int64_t big = ((a.m + 127) / 128) * ((a.n + 127) / 128) * batch;
-    if (big >= sm_count) return launch_dgemm_tile<128>(a, ta, tb, batch, st);
+    static const int forced = [] { const char* e = std::getenv("SUSHI_DGEMM_TILE"); return e ? std::atoi(e) : 0; }();
+    if (forced == 64) return launch_dgemm_tile<64>(a, ta, tb, batch, st);
+    if (forced == 128) return launch_dgemm_tile<128>(a, ta, tb, batch, st);
+    const int64_t t128 = ((a.m + 127) / 128) * ((a.n + 127) / 128) * batch;
+    const int64_t t64 = ((a.m + 63) / 64) * ((a.n + 63) / 64) * batch;
+    const double cost128 = (double)((t128 + sm_count - 1) / sm_count) * 4.0 / 33.5;
+    const double cost64 = (double)((t64 + sm_count - 1) / sm_count) / 30.4;
+    if (cost128 <= cost64) return launch_dgemm_tile<128>(a, ta, tb, batch, st);
     return launch_dgemm_tile<64>(a, ta, tb, batch, st);
 }
 
