@@ -277,7 +277,9 @@ SUSHI_CUDA_API int sushi_cuda_reserve_workspace(sushi_cuda_ctx* ctx, int dev, si
  * library image (every GPU that loads the library holds it until the process exits).
  *
  *  - Runs on the CURRENT device, on `cuda_stream` (a cudaStream_t as void*; NULL = default
- *    stream), asynchronously; always the tensor-core 3xTF32 kernel.
+ *    stream), asynchronously; the tensor-core 3xTF32 kernel for k >= 4, the exact-fp32 FFMA kernel
+ *    (no scratch) below that, where a 3xTF32 product could miss the K-scaled tolerance.  A stream
+ *    that belongs to another device is refused (SUSHI_CUDA_ERR_INVALID_ARG).
  *  - Limit: 8 * (pad256(m) + pad256(n)) * pad16(k) bytes must fit the scratch (pad = round up);
  *    e.g. 1024 x 1024 x 2048 fits, 2048^3 does not.  Larger problems return
  *    SUSHI_CUDA_ERR_UNSUPPORTED with the sizes in sushi_cuda_last_error(NULL).
@@ -287,7 +289,10 @@ SUSHI_CUDA_API int sushi_cuda_reserve_workspace(sushi_cuda_ctx* ctx, int dev, si
  *    (different streams, no ordering between them) race and give wrong results; order them.
  *    Nothing is assumed about the array's previous contents.
  *  - `status_dev` (optional, device memory, 4 bytes): set to 0 by the call and to a non-zero
- *    code by the kernel if one of its bounded waits expired (C is then incomplete).          */
+ *    code by the kernel if one of its bounded waits expired (C is then incomplete).  With
+ *    status_dev == NULL the word is one per device, shared by every call and zeroed by each, so
+ *    a later or overlapping call can clear a code before the host reads it: callers that need
+ *    failure detection pass their own word.                                                 */
 #define SUSHI_CUDA_STATIC_SCRATCH_BYTES (32u << 20)
 SUSHI_CUDA_API int sushi_cuda_sgemm_static_scratch(void* cuda_stream, int trans_a, int trans_b,
                                                    int64_t m, int64_t n, int64_t k, float alpha,
@@ -331,8 +336,19 @@ SUSHI_CUDA_API int sushi_cuda_comm_set_peer_buffers(sushi_cuda_ctx* ctx, int dev
  * gather == 2: fused exchange -- one GEMM launch over the whole block whose epilogue warps copy
  * every finished 256 x 256 tile of C into the peers' buffers with plain NVLink stores while the
  * next tile is being multiplied, followed by a 4-byte NCCL all-reduce as the cross-rank barrier.
- * Needs sushi_cuda_comm_set_peer_buffers with c_full as this rank's entry, ldc == n, n % 4 == 0;
- * otherwise the call falls back to gather == 1.                                            */
+ * Taken when ldc == n, n % 4 == 0, the tensor path suits every rank's block
+ * (sushi_cuda_row_sharded_exchange) and peer buffers are registered (on every rank alike); otherwise
+ * the call runs gather == 1.  With buffers registered, c_full must be this rank's registered entry,
+ * 16-byte aligned and large enough: a mismatch is SUSHI_CUDA_ERR_INVALID_ARG, never a silent
+ * change of path.  Ranks whose block is empty still take part in the two barriers.             */
+/* Which exchange sushi_cuda_sgemm_row_sharded runs for a problem: 0 none, 1 NCCL slabs, 2 peer stores fused
+ * into the GEMM epilogue.  Pure host arithmetic over quantities every rank shares (no rank, no pointer): the
+ * ranks of an uneven partition -- short or empty trailing blocks -- therefore always issue the same
+ * collectives.  `variant` is the kernel-family setting (sushi_cuda_gemm_variant), which the ranks must set
+ * alike, as they must register peer buffers alike; `sm_count` the SM count of the (homogeneous) GPUs.     */
+SUSHI_CUDA_API int sushi_cuda_row_sharded_exchange(int64_t m, int64_t n, int64_t k, int nranks, int variant, int sm_count,
+                                                   int gather, int* exchange);
+
 SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                                 int64_t m, int64_t n, int64_t k, float alpha,
                                                 const float* a_local, int64_t lda,

@@ -387,9 +387,6 @@ __global__ void scale_c_f64_kernel(double* c, int64_t m, int64_t n, int64_t ldc,
 // tile wins when the large one would leave most of a round idle (1024^3: 64 tiles; 2048^3: 1.73 rounds).
 inline cudaError_t launch_dgemm(const DgemmArgs& a, bool ta, bool tb, int64_t batch, int sm_count, cudaStream_t st)
 {
-    static const int forced = [] { const char* e = std::getenv("SUSHI_DGEMM_TILE"); return e ? std::atoi(e) : 0; }();
-    if (forced == 64) return launch_dgemm_tile<64>(a, ta, tb, batch, st);
-    if (forced == 128) return launch_dgemm_tile<128>(a, ta, tb, batch, st);
     const int64_t t128 = ((a.m + 127) / 128) * ((a.n + 127) / 128) * batch;
     const int64_t t64 = ((a.m + 63) / 64) * ((a.n + 63) / 64) * batch;
     const double cost128 = (double)((t128 + sm_count - 1) / sm_count) * 4.0 / 33.5;

@@ -1131,13 +1131,6 @@ inline void tile_counts(int64_t m, int64_t n, int64_t k, int64_t batch, int64_t*
     *num_kb = (k + BK - 1) / BK;
 }
 
-// Development switch: SUSHI_LEAN_EPILOGUE=0 routes every work item through the general epilogue.
-inline bool lean_epilogue_enabled()
-{
-    static const bool on = [] { const char* e = getenv("SUSHI_LEAN_EPILOGUE"); return !(e && e[0] == '0'); }();
-    return on;
-}
-
 // planes_a / planes_b as written by launch_split_tf32 for op(A) (rows = m) and op(B)^T (rows = n).
 // Tensor map over a user operand whose k index is contiguous: element (row, kk) at
 // base[bi*stride + row*ld + kk]; box = {16 k, 256 rows, 1}; outside rows/k reads as zero.
@@ -1224,7 +1217,7 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
     p.alpha = alpha; p.beta = beta; p.status = status; p.act = act; p.act_param = act_param; p.tri = tri;
-    p.lean_epilogue = lean_epilogue_enabled() ? 1 : 0;
+    p.lean_epilogue = 1;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);
     p.dp_tiles = plan.dp_tiles; p.sk_tiles = plan.sk_tiles; p.sk_split = plan.sk_split; p.sk_coop = plan.coop;
     p.sk_flags = static_cast<unsigned int*>(sk_area);

@@ -90,10 +90,6 @@ struct sushi_cuda_ctx
     int variant = SUSHI_GEMM_AUTO;
     std::atomic<int64_t> launches{0};
     bool timing = false;
-    int fuse_split = 1;                   // in-kernel split of k-contiguous operands: 0 never, 1 by shape, 2 always
-    bool stream_k = true;                 // cut the tiles of a partial round along K (SUSHI_SPLIT_K=0 disables)
-    bool skinny = true;                   // tall-and-skinny kernel for n <= 32 (SUSHI_SKINNY=0 disables)
-    bool panel_pipeline = true;           // sharded GEMM: split most of B under the first column panel (SUSHI_PANEL_PIPELINE=0 disables)
     // multi-GPU (one process per GPU: a single communicator bound to one device index)
     ncclComm_t comm = nullptr;
     int comm_dev = -1, nranks = 1, rank = 0;
@@ -270,7 +266,10 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     }
     int variant = (reuse && reuse->variant >= 0) ? reuse->variant : ctx->variant;
     if (variant == SUSHI_GEMM_AUTO)
-        variant = prefer_tc3x(m, n, k, batch, d.sm_count, ctx->stream_k) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+        variant = prefer_tc3x(m, n, k, batch, d.sm_count) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+    // A 3xTF32 product carries up to ~12 * 2^-24 |a b| of error whatever K is, which for K < 4 can exceed
+    // the K-scaled tolerance: such products always take the exact-fp32 FFMA kernel.
+    if (variant == SUSHI_GEMM_TC3X && k < 4) variant = SUSHI_GEMM_SIMT;
     if (reuse) reuse->variant = variant;
 
     if (variant == SUSHI_GEMM_TC3X)
@@ -280,14 +279,12 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         // costs ~10 % of the kernel's tensor rate (shared-memory bandwidth) for every tile that
         // uses the operand.  Measured break-even on B200: the operand is reused by about eleven
         // 256-wide tiles, so A is split in-kernel when n <= 2048 and B when m <= 2048
-        // (SUSHI_FUSE_SPLIT=0: never, =2: whenever eligible).
-        const bool want_a = ctx->fuse_split == 2 || (ctx->fuse_split != 0 && n <= 2048);
-        const bool want_b = ctx->fuse_split == 2 || (ctx->fuse_split != 0 && m <= 2048);
+        const bool want_a = n <= 2048;
+        const bool want_b = m <= 2048;
         // either storage order of an operand can be taken raw: k-contiguous tiles are split in place, row-contiguous
-        // ones (A^T, or B not transposed) are transposed by the converters on the way (SUSHI_FUSE_SPLIT=3: only k-contiguous)
-        const bool mn_ok = ctx->fuse_split != 3;
-        const bool fuse_a = want_a && (!ta || mn_ok) && sushi::tc3x::raw_eligible(a, m, k, lda, sa, batch);
-        const bool fuse_b = want_b && (tb || mn_ok) && sushi::tc3x::raw_eligible(b, n, k, ldb, sb, batch);
+        // ones (A^T, or B not transposed) are transposed by the converters on the way
+        const bool fuse_a = want_a && sushi::tc3x::raw_eligible(a, m, k, lda, sa, batch);
+        const bool fuse_b = want_b && sushi::tc3x::raw_eligible(b, n, k, ldb, sb, batch);
         // workspace: [planes of op(B)^T][planes of op(A)] -- B first so that slabs of A of any
         // size can follow without moving it
         const int64_t a_rows = (reuse && reuse->max_rows > m) ? reuse->max_rows : m;
@@ -312,7 +309,6 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
             SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b, n, k, ldb, sb, batch, /*k_contig=*/tb != 0, d.sm_count, d.stream));
         if (reuse) reuse->b_planes_ready = true;
         void* sk_area = nullptr;
-        if (ctx->stream_k)
         {
             int64_t tiles = 0, num_kb = 0;
             sushi::tc3x::tile_counts(m, n, k, batch, &tiles, &num_kb);
@@ -348,7 +344,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     }
 
     // tall-and-skinny products are bound by reading A once: their own kernel (same arithmetic class)
-    if (tri == 0 && ctx->skinny && batch <= 65535 && sushi::skinny_eligible(ta, m, n, k, a, lda, sa))
+    if (tri == 0 && batch <= 65535 && sushi::skinny_eligible(ta, m, n, k, a, lda, sa))
     {
         sushi::SkinnyArgs q;
         q.a = a; q.b = b; q.c = c; q.m = m; q.n = n; q.k = k; q.lda = lda; q.ldb = ldb; q.ldc = ldc;
@@ -388,7 +384,7 @@ int run_gemm_two_panels(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int
                         float* const* peer_c, int n_peers)
 {
     if (rows <= 0 || n <= 0 || k <= 0 || alpha == 0.0f) return 1;
-    const bool want_b = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && rows <= 2048);
+    const bool want_b = rows <= 2048;
     if (want_b && tb && sushi::tc3x::raw_eligible(b, n, k, ldb, 0, 1)) return 1;       // B needs no pre-pass
     const int64_t tiles_m = (rows + 255) / 256, tiles_n = (n + 255) / 256;
     const int64_t unit = d.sm_count / std::gcd((int64_t)d.sm_count, tiles_m);           // tile columns per whole round
@@ -407,7 +403,7 @@ int run_gemm_two_panels(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int
         SC_CUDA(ctx, cudaEventCreateWithFlags(&d.prep_fork, cudaEventDisableTiming));
         SC_CUDA(ctx, cudaEventCreateWithFlags(&d.prep_join, cudaEventDisableTiming));
     }
-    const bool want_a = ctx->fuse_split == 2 || (ctx->fuse_split == 1 && n <= 2048);
+    const bool want_a = n <= 2048;
     const bool fuse_a = want_a && !ta && sushi::tc3x::raw_eligible(a, rows, k, lda, 0, 1);
     const size_t bytes_b0 = sushi::split_plane_bytes(cols0, k, 1), bytes_b1 = sushi::split_plane_bytes(n - cols0, k, 1);
     const size_t bytes_a = fuse_a ? 0 : sushi::split_plane_bytes(rows, k, 1);
@@ -543,10 +539,6 @@ extern "C" int sushi_cuda_init(const int* devices, int n_devices, sushi_cuda_ctx
     }
     sushi_cuda_ctx* ctx = new sushi_cuda_ctx();
     ctx->variant = check_variant_env(SUSHI_GEMM_AUTO);
-    if (const char* e = getenv("SUSHI_SPLIT_K")) ctx->stream_k = atoi(e) != 0;
-    if (const char* e = getenv("SUSHI_PANEL_PIPELINE")) ctx->panel_pipeline = atoi(e) != 0;
-    if (const char* e = getenv("SUSHI_SKINNY")) ctx->skinny = atoi(e) != 0;
-    if (const char* e = getenv("SUSHI_FUSE_SPLIT")) ctx->fuse_split = atoi(e);
     for (int id : ids)
     {
         if (id < 0 || id >= count)
@@ -1480,6 +1472,27 @@ extern "C" int sushi_cuda_comm_set_peer_buffers(sushi_cuda_ctx* ctx, int dev, vo
     return SUSHI_CUDA_OK;
 }
 
+extern "C" int sushi_cuda_row_sharded_exchange(int64_t m, int64_t n, int64_t k, int nranks, int variant, int sm_count,
+                                               int gather, int* exchange)
+{
+    if (!exchange || m < 0 || n < 0 || k < 0 || nranks < 1 || sm_count < 1)
+        return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "row_sharded_exchange: bad argument");
+    *exchange = 0;
+    if (gather == 0 || nranks == 1) return SUSHI_CUDA_OK;
+    *exchange = 1;
+    if (gather != 2 || (n & 3) != 0 || m == 0) return SUSHI_CUDA_OK;
+    // the peer stores live in the tensor-path kernel: it must suit both block sizes that occur, the full block
+    // ceil(m / nranks) and the shorter block of the last rank that owns rows
+    const int64_t block = (m + nranks - 1) / nranks;
+    const int64_t nonempty = (m + block - 1) / block;
+    const int64_t last_rows = m - (nonempty - 1) * block;
+    auto tensor_for = [&](int64_t rows) {
+        return rows > 0 && k >= 4 && (variant == SUSHI_GEMM_TC3X || (variant == SUSHI_GEMM_AUTO && prefer_tc3x(rows, n, k, 1, sm_count)));
+    };
+    if (tensor_for(block) && tensor_for(last_rows)) *exchange = 2;
+    return SUSHI_CUDA_OK;
+}
+
 extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                             int64_t m, int64_t n, int64_t k, float alpha,
                                             const float* a_local, int64_t lda,
@@ -1500,11 +1513,18 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     if (do_gather && ldc != n)
         return set_error(ctx, SUSHI_CUDA_ERR_UNSUPPORTED, "sgemm_row_sharded: gathering needs ldc == n");
     float* c_block = c_full + first * ldc;
-    const bool tensor_block = ctx->variant == SUSHI_GEMM_TC3X ||
-                              (ctx->variant == SUSHI_GEMM_AUTO && count > 0 && prefer_tc3x(count, n, k, 1, d->sm_count));
+    // Which exchange runs -- and with it which collectives every rank issues -- is decided from quantities all
+    // ranks share, never from this rank's own block (sushi_cuda_row_sharded_exchange).
+    const int64_t block = (m + nranks - 1) / nranks;
+    auto tensor_for = [&](int64_t rows) {
+        return rows > 0 && k >= 4 && (ctx->variant == SUSHI_GEMM_TC3X ||
+                                      (ctx->variant == SUSHI_GEMM_AUTO && prefer_tc3x(rows, n, k, 1, d->sm_count)));
+    };
+    int exchange = 0;
+    sushi_cuda_row_sharded_exchange(m, n, k, nranks, ctx->variant, d->sm_count, gather, &exchange);
     if (!do_gather)
     {
-        if (tensor_block && ctx->panel_pipeline)
+        if (tensor_for(count))
         {
             rc = run_gemm_two_panels(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, b, ldb, beta, c_block, ldc,
                                      nullptr, 0);
@@ -1514,35 +1534,36 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     }
 
     // Fused exchange: one launch over the whole block; the epilogue stores C tiles to the peers.
-    const bool tensor_path = ctx->variant == SUSHI_GEMM_TC3X ||
-                             (ctx->variant == SUSHI_GEMM_AUTO && count > 0 && prefer_tc3x(count, n, k, 1, d->sm_count));
-    bool all_tensor = tensor_path;
-    if (gather == 2 && (int)ctx->peer_buffers.size() == nranks && ctx->peer_buffers[rank] == c_full && (n & 3) == 0 &&
-        (reinterpret_cast<uintptr_t>(c_full) & 15) == 0 && all_tensor && count > 0 &&
-        (size_t)m * (size_t)n * sizeof(float) <= ctx->peer_bytes)
+    if (exchange == 2 && !ctx->peer_buffers.empty())
     {
+        // what remains is this rank's own registration: a mismatch is an error, not a silent change of path
+        if ((int)ctx->peer_buffers.size() != nranks || ctx->peer_buffers[rank] != c_full ||
+            (reinterpret_cast<uintptr_t>(c_full) & 15) != 0 || (size_t)m * (size_t)n * sizeof(float) > ctx->peer_bytes)
+            return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG,
+                             "sgemm_row_sharded: gather == 2 needs c_full to be this rank's registered buffer "
+                             "(sushi_cuda_comm_set_peer_buffers), 16-byte aligned and at least m*n*4 bytes");
         SC_CUDA(ctx, cudaSetDevice(d->device));
         // barrier 1: every rank has reached this call, so nobody still reads the previous C
         SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
-        SlabReuse fused;
-        fused.variant = SUSHI_GEMM_TC3X;
-        for (int r = 0; r < nranks; ++r)
-            if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * ldc;
-        rc = 1;
-        if (ctx->panel_pipeline)
+        if (count > 0)
+        {
+            SlabReuse fused;
+            fused.variant = SUSHI_GEMM_TC3X;
+            for (int r = 0; r < nranks; ++r)
+                if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * ldc;
             rc = run_gemm_two_panels(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, b, ldb, beta, c_block, ldc,
                                      fused.peer_c, fused.n_peers);
-        if (rc > 0)
-            rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
-                          &fused);
-        if (rc != SUSHI_CUDA_OK) return rc;
+            if (rc > 0)
+                rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
+                              &fused);
+            if (rc != SUSHI_CUDA_OK) return rc;
+        }
         // barrier 2: every rank's kernel (and with it its stores into this rank's buffer) is complete
         SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
         return SUSHI_CUDA_OK;
     }
 
     // Slab pipeline: multiply slab s on the compute stream, exchange it on the comm stream.
-    const int64_t block = (m + nranks - 1) / nranks;
     int64_t slabs = block / 2048;                 // >= 2048 rows per slab keeps the tile grid full
     if (slabs < 1) slabs = 1;
     if (slabs > 8) slabs = 8;
@@ -1553,8 +1574,7 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     SC_CUDA(ctx, cudaSetDevice(d->device));
     // one kernel family for the whole block, B split into planes once, A planes sized for a slab
     SlabReuse reuse;
-    if (ctx->variant == SUSHI_GEMM_AUTO)
-        reuse.variant = (count > 0 && prefer_tc3x(count, n, k, 1, d->sm_count)) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+    if (ctx->variant == SUSHI_GEMM_AUTO) reuse.variant = tensor_for(count) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
     reuse.max_rows = slab_rows < count ? slab_rows : count;
     for (int64_t s = 0; s < slabs; ++s)
     {
@@ -1675,6 +1695,15 @@ extern "C" int sushi_cuda_sgemm_static_scratch(void* cuda_stream, int trans_a, i
         }
     }
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread)
+    {
+        // a stream of another device would make the kernels address that device's copy of the array
+        int stream_device = -1;
+        if (cudaStreamGetDevice(st, &stream_device) == cudaSuccess && stream_device != device)
+            return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG,
+                             "sgemm_static_scratch: the stream belongs to another device than the current one");
+        cudaGetLastError();
+    }
     int* status = status_dev ? status_dev : sd.status;
     if (m == 0 || n == 0) return SUSHI_CUDA_OK;
     SC_CUDA(nullptr, cudaMemsetAsync(status, 0, sizeof(int), st));       // must start at zero
@@ -1685,6 +1714,16 @@ extern "C" int sushi_cuda_sgemm_static_scratch(void* cuda_stream, int trans_a, i
         if (blocks > (int64_t)sd.sm_count * 16) blocks = (int64_t)sd.sm_count * 16;
         sushi::scale_c_kernel<<<(unsigned)blocks, 256, 0, st>>>(c, m, n, ldc, 0, 1, beta);
         SC_CUDA(nullptr, cudaGetLastError());
+        return SUSHI_CUDA_OK;
+    }
+    if (k < 4)
+    {
+        // a 3xTF32 product can miss the K-scaled tolerance below K = 4: exact-fp32 FFMA kernel (needs no scratch)
+        sushi::SimtGemmArgs g;
+        g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+        g.stride_a = 0; g.stride_b = 0; g.stride_c = 0; g.tiles_m = 0; g.tiles_n = 0;
+        g.alpha = alpha; g.beta = beta; g.act = 0; g.act_param = 0.0f; g.tri = 0;
+        SC_CUDA(nullptr, sushi::launch_sgemm_simt(g, trans_a != 0, trans_b != 0, 1, sd.sm_count, st));
         return SUSHI_CUDA_OK;
     }
     const size_t bytes_a = sushi::split_plane_bytes(m, k, 1);

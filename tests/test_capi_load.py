@@ -106,3 +106,28 @@ def test_header_is_plain_c(tmp_path):
     size, off_alpha, off_epi, off_param = (int(v) for v in out.stdout.split())
     assert size == ctypes.sizeof(GemmDesc)
     assert off_alpha == GemmDesc.alpha.offset and off_epi == GemmDesc.epilogue.offset and off_param == GemmDesc.act_param.offset
+
+
+def test_row_sharded_exchange_is_decided_without_the_rank(lib_path):
+    """The exchange a sharded GEMM runs (and so the collectives each rank issues) is a function of the
+    shared problem only: uneven partitions -- a short last block, empty trailing ranks -- cannot send
+    ranks down different paths."""
+    from sushiblas_b200.capi import row_sharded_exchange, partition, GEMM_AUTO, GEMM_SIMT, GEMM_TC3X
+    # headline shape: fused at every rank count
+    for g in (2, 4, 8):
+        assert row_sharded_exchange(32768, 32768, 32768, g) == 2
+    assert row_sharded_exchange(32768, 32768, 32768, 1) == 0
+    assert row_sharded_exchange(32768, 32768, 32768, 8, gather=0) == 0
+    assert row_sharded_exchange(32768, 32768, 32768, 8, gather=1) == 1
+    # AUTO, m = 1017 on 8 ranks: blocks of 128 and a last block of 121 rows, too small for the tensor
+    # path -- every rank (also those with 128 rows) must take the NCCL exchange
+    assert [partition(1017, 8, r)[1] for r in range(8)] == [128] * 7 + [121]
+    assert row_sharded_exchange(1017, 512, 512, 8, GEMM_AUTO) == 1
+    # forced tensor path, fewer rows than ranks: trailing ranks are empty, the others fused
+    assert [partition(5, 8, r)[1] for r in range(8)] == [1, 1, 1, 1, 1, 0, 0, 0]
+    assert row_sharded_exchange(5, 512, 512, 8, GEMM_TC3X) == 2
+    assert row_sharded_exchange(5, 512, 512, 8, GEMM_SIMT) == 1
+    # K below 4 never runs on the tensor path; n must allow 128-bit peer stores
+    assert row_sharded_exchange(4096, 512, 3, 2, GEMM_TC3X) == 1
+    assert row_sharded_exchange(4096, 510, 512, 2, GEMM_TC3X) == 1
+    assert row_sharded_exchange(0, 512, 512, 2, GEMM_TC3X) == 1

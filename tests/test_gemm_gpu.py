@@ -172,12 +172,31 @@ def test_tc3x_ragged_and_padded(ctx):
     check(ctx, TC3X, 0, 0, 300, 260, 100, 1.0, 0.0)
     check(ctx, TC3X, 1, 0, 257, 255, 77, 2.0, -1.0, pad=(4, 0, 4))
     check(ctx, TC3X, 0, 1, 129, 513, 130, 1.0, 1.0, pad=(1, 3, 5))      # unaligned leading dims: scalar epilogue
-    # k = 1 forced onto the tensor-core path: the 3xTF32 split leaves up to ~12 * 2^-24 |a b| per
-    # product whatever K is, which only fits the K-scaled bound at full budget when K < 4
-    # (the automatic choice never takes this path below K = 128)
-    check(ctx, TC3X, 1, 1, 640, 130, 1, 1.0, 0.5, budget=1.0)
+    # k < 4 asked of the tensor-core path is served by the exact FFMA kernel (see the worst-case test below)
+    check(ctx, TC3X, 1, 1, 640, 130, 1, 1.0, 0.5)
     check(ctx, TC3X, 1, 1, 640, 130, 4, 1.0, 0.5)
     check(ctx, TC3X, 0, 0, 1, 1, 4096, 1.0, 0.0)                         # one element of C
+
+
+@pytest.mark.parametrize("k", [1, 2, 3])
+def test_k_below_4_with_worst_case_split_residues_is_exact_fp32(ctx, k):
+    """Inputs whose low 13 mantissa bits are all set leave the largest possible residue after the hi/lo
+    split: a 3xTF32 product of two such numbers is off by up to ~12 * 2^-24 |a b|, more than the
+    half-budget bound 4*K*2^-24 allows for K < 4.  A forced tensor-path request below K = 4 therefore runs
+    on the FFMA kernel, whose K <= 3 products and sums are within one fp32 rounding each."""
+    m, n = 256, 256
+    rng = np.random.default_rng(5)
+    def worst(shape):
+        x = rng.uniform(1.0, 2.0, size=shape).astype(np.float32)
+        bits = x.view(np.uint32) | np.uint32(0x1FFF)          # maximal lo residue, lo*lo term maximal too
+        return (bits.view(np.float32) * rng.choice([-1.0, 1.0], size=shape)).astype(np.float32)
+    a, b = worst((m, k)), worst((k, n))
+    c0 = np.zeros((m, n), np.float32)
+    out = run_gemm(ctx, TC3X, 0, 0, m, n, k, 1.0, a.ravel(), k, 0, b.ravel(), n, 0, 0.0, c0.ravel(), n, 0, 1)
+    ref, absab = og.gemm_f64_np(0, 0, m, n, k, 1.0, a, k, 0, b, n, 0, 0.0, c0, n, 0, 1)
+    r, q = og.tolerance_ratio(out.reshape(1, m, n), ref, absab, k, budget=BUDGET)
+    assert r <= 1.0, (r, q)
+    assert q <= k + 1.0, q        # fp32 products summed in fp32: about one rounding per term
 
 
 def test_tc3x_beta_zero_ignores_nan_c(ctx):

@@ -59,6 +59,8 @@ def test_static_scratch_matches_regular_entry_point_twice_in_a_row(ctx):
     _case(ctx, stream, 0, 0, 300, 260, 100, 1.0, 0.0, seed=910)
     # and the largest square problem the 32 MiB array admits, after the small one
     _case(ctx, stream, 0, 1, 1024, 1024, 2048, -1.0, 1.0, seed=920)
+    # K below 4: both entry points hand the product to the exact FFMA kernel
+    _case(ctx, stream, 0, 0, 200, 136, 3, 1.0, 0.5, seed=930)
 
 
 def test_static_scratch_rejects_sizes_beyond_its_array(ctx):
