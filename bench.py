@@ -871,8 +871,18 @@ def tf32_ceiling(h: Harness):
         ctx.fill_uniform(a, n * n, SEED); ctx.fill_uniform(b, n * n, SEED + 1)
         out = {}
         for label, products in (("tf32_x1", 1), ("tf32_x3", 3)):
-            med, best = time_calls_flushed(h, lambda: ctx.sgemm_tf32_probe(0, 1, n, n, n, a, n, b, n, c, n, products), steps=10, warmup=3)
-            out[label] = {"ms_median": round(med, 4), "mma_tflops": round(2.0 * n ** 3 * products / (med * 1e-3) / 1e12, 1)}
+            # the library's own CUDA events around the GEMM kernel alone (the operands' pre-pass is not part of the rate)
+            for _ in range(3):
+                ctx.sgemm_tf32_probe(0, 1, n, n, n, a, n, b, n, c, n, products)
+            ctx.sync()
+            ctx.kernel_timing_enable(True)
+            for _ in range(10):
+                ctx.sgemm_tf32_probe(0, 1, n, n, n, a, n, b, n, c, n, products)
+            ctx.sync()
+            gemm_ms, gemm_launches, _, _ = ctx.kernel_timing_read()
+            ctx.kernel_timing_enable(False)
+            ms = gemm_ms / max(1, gemm_launches)
+            out[label] = {"kernel_ms": round(ms, 4), "mma_tflops": round(2.0 * n ** 3 * products / (ms * 1e-3) / 1e12, 1)}
         out["shape"] = f"{n}^3 NT"
         out["ceiling_3xtf32_tflops"] = round(out["tf32_x1"]["mma_tflops"] / 3.0, 1)
         del a, b, c

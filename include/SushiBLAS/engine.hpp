@@ -85,6 +85,29 @@ namespace SushiBLAS
             std::atomic<uint64_t> rng_offset_{0};
     };
 
+    namespace detail
+    {
+        /// Device address of `ptr` (which lies inside `storage`) for an operation that is being enqueued.
+        /// `reads`: the operation reads the range or needs what it does not overwrite; a range that does
+        /// not cover the whole storage always keeps the rest, so the storage's contents are brought up too.
+        template <typename T>
+        inline int stage_in(const SushiRuntime::sushi_ptr<Storage>& storage, T* ptr, int64_t extent, bool reads, T** out)
+        {
+            const bool whole = static_cast<void*>(ptr) == storage->data_ptr &&
+                               static_cast<std::size_t>(extent) * sizeof(T) >= storage->requested_bytes;
+            int rc = SUSHI_CUDA_OK;
+            char* base = static_cast<char*>(storage->allocator->device_for_operation(storage->data_ptr, reads || !whole, &rc));
+            if (!base) return rc != SUSHI_CUDA_OK ? rc : SUSHI_CUDA_ERR_OOM;
+            *out = reinterpret_cast<T*>(base + (reinterpret_cast<char*>(ptr) - static_cast<char*>(storage->data_ptr)));
+            return SUSHI_CUDA_OK;
+        }
+        /// The operation just enqueued writes `storage` on the device.
+        inline void stage_out(const SushiRuntime::sushi_ptr<Storage>& storage)
+        {
+            storage->allocator->mark_device_written(storage->data_ptr);
+        }
+    } // namespace detail
+
     // ---------------------------------------------------------------- Level3::gemm
     inline SushiRuntime::Execution::Event Level3::gemm(const Tensor& A, const Tensor& B, Tensor& C, bool transA,
                                                        bool transB, float alpha, float beta)
@@ -143,17 +166,10 @@ namespace SushiBLAS
         auto prepare = [g, oa, ob, oc, slot](SushiRuntime::Execution::RuntimeContext& rt, sushi_cuda_gemm_desc& q) -> int
         {
             sushi_cuda_ctx* ctx = rt.native_handle();
-            // device address of an operand; host-resident operands are staged through their mirror
-            auto on_device = [ctx](const Operand& o, bool upload, float** out) -> int
-            {
-                char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
-                if (!base) return SUSHI_CUDA_ERR_OOM;
-                *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) -
-                                                        static_cast<char*>(o.storage->data_ptr)));
-                if (o.host && upload && o.extent > 0)
-                    return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
-                return SUSHI_CUDA_OK;
-            };
+            // device address of an operand; host-resident operands live in their mirror (uploaded when stale)
+            (void)ctx;
+            auto on_device = [](const Operand& o, bool reads, float** out) -> int
+            { return detail::stage_in(o.storage, o.ptr, o.extent, reads, out); };
             float *da = nullptr, *db = nullptr, *dc = nullptr;
             int rc = on_device(oa, true, &da);
             if (rc == SUSHI_CUDA_OK) rc = on_device(ob, true, &db);
@@ -169,14 +185,11 @@ namespace SushiBLAS
             q.act_param = slot->param;
             return SUSHI_CUDA_OK;
         };
-        // stage the output back (host-resident C only); `dc` is recomputed, nothing is shared with prepare
-        auto finish = [oc](SushiRuntime::Execution::RuntimeContext& rt) -> int
+        // host-resident C: its host image is stale until the caller waits
+        auto finish = [oc](SushiRuntime::Execution::RuntimeContext&) -> int
         {
-            if (!oc.host || oc.extent <= 0) return SUSHI_CUDA_OK;
-            char* base = static_cast<char*>(oc.storage->allocator->device_view(oc.storage->data_ptr));
-            if (!base) return SUSHI_CUDA_ERR_OOM;
-            float* dc = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(oc.ptr) - static_cast<char*>(oc.storage->data_ptr)));
-            return sushi_cuda_memcpy_d2h(rt.native_handle(), 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
+            detail::stage_out(oc.storage);
+            return SUSHI_CUDA_OK;
         };
         auto work = [g, prepare, finish](SushiRuntime::Execution::RuntimeContext& rt) -> int
         {
@@ -233,15 +246,8 @@ namespace SushiBLAS
             [=](SushiRuntime::Execution::RuntimeContext& rt) -> int
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
-                auto on_device = [ctx](const Operand& o, bool upload, double** out) -> int
-                {
-                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
-                    if (!base) return SUSHI_CUDA_ERR_OOM;
-                    *out = reinterpret_cast<double*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
-                    if (o.host && upload && o.extent > 0)
-                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(double));
-                    return SUSHI_CUDA_OK;
-                };
+                auto on_device = [](const Operand& o, bool reads, double** out) -> int
+                { return detail::stage_in(o.storage, o.ptr, o.extent, reads, out); };
                 double *da = nullptr, *db = nullptr, *dc = nullptr;
                 int rc = on_device(oa, true, &da);
                 if (rc == SUSHI_CUDA_OK) rc = on_device(ob, true, &db);
@@ -252,8 +258,7 @@ namespace SushiBLAS
                 rc = sushi_cuda_dgemm_strided_batched(ctx, 0, g.trans_a, g.trans_b, g.m, g.n, g.k, static_cast<double>(g.alpha),
                                                       da, g.lda, g.stride_a, db, g.ldb, g.stride_b, static_cast<double>(g.beta),
                                                       dc, g.ldc, g.stride_c, g.batch);
-                if (rc == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
-                    rc = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(double));
+                if (rc == SUSHI_CUDA_OK) detail::stage_out(oc.storage);
                 return rc;
             });
         return SushiRuntime::Execution::Event();
@@ -311,15 +316,8 @@ namespace SushiBLAS
             [=](SushiRuntime::Execution::RuntimeContext& rt) -> int
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
-                auto on_device = [ctx](const Operand& o, bool upload, float** out) -> int
-                {
-                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
-                    if (!base) return SUSHI_CUDA_ERR_OOM;
-                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
-                    if (o.host && upload && o.extent > 0)
-                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
-                    return SUSHI_CUDA_OK;
-                };
+                auto on_device = [](const Operand& o, bool reads, float** out) -> int
+                { return detail::stage_in(o.storage, o.ptr, o.extent, reads, out); };
                 float *da = nullptr, *dc = nullptr;
                 int rc2 = on_device(oa, true, &da);
                 // the untouched triangle must survive the copy back: host-resident C always goes up
@@ -327,8 +325,7 @@ namespace SushiBLAS
                 if (rc2 != SUSHI_CUDA_OK) return rc2;
                 rc2 = sushi_cuda_ssyrk_strided_batched(ctx, 0, rm_upper, rm_trans, n, k, alpha, da, lda, stride_a, beta, dc, ldc,
                                                        stride_c, batch);
-                if (rc2 == SUSHI_CUDA_OK && oc.host && oc.extent > 0)
-                    rc2 = sushi_cuda_memcpy_d2h(ctx, 0, oc.ptr, dc, static_cast<std::size_t>(oc.extent) * sizeof(float));
+                if (rc2 == SUSHI_CUDA_OK) detail::stage_out(oc.storage);
                 return rc2;
             });
         return SushiRuntime::Execution::Event();
@@ -391,23 +388,15 @@ namespace SushiBLAS
             [=](SushiRuntime::Execution::RuntimeContext& rt) -> int
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
-                auto on_device = [ctx](const Operand& o, float** out) -> int
-                {
-                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
-                    if (!base) return SUSHI_CUDA_ERR_OOM;
-                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
-                    if (o.host && o.extent > 0)
-                        return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, static_cast<std::size_t>(o.extent) * sizeof(float));
-                    return SUSHI_CUDA_OK;
-                };
+                auto on_device = [](const Operand& o, float** out) -> int
+                { return detail::stage_in(o.storage, o.ptr, o.extent, true, out); };
                 float *da = nullptr, *db = nullptr;
                 int rc2 = on_device(oa, &da);
                 if (rc2 == SUSHI_CUDA_OK) rc2 = on_device(ob, &db);
                 if (rc2 != SUSHI_CUDA_OK) return rc2;
                 rc2 = sushi_cuda_strsm_strided_batched(ctx, 0, rm_left, rm_upper, transA, unit_diag, rm_m, rm_n, alpha, da, lda,
                                                        stride_a, db, ldb, stride_b, batch);
-                if (rc2 == SUSHI_CUDA_OK && ob.host && ob.extent > 0)
-                    rc2 = sushi_cuda_memcpy_d2h(ctx, 0, ob.ptr, db, static_cast<std::size_t>(ob.extent) * sizeof(float));
+                if (rc2 == SUSHI_CUDA_OK) detail::stage_out(ob.storage);
                 return rc2;
             });
         return SushiRuntime::Execution::Event();
@@ -476,14 +465,11 @@ namespace SushiBLAS
             [storage, ptr, count, host, activation, param](SushiRuntime::Execution::RuntimeContext& rt) -> int
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
-                char* base = static_cast<char*>(storage->allocator->device_view(storage->data_ptr));
-                if (!base) return SUSHI_CUDA_ERR_OOM;
-                float* dptr = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(ptr) - static_cast<char*>(storage->data_ptr)));
-                const std::size_t bytes = static_cast<std::size_t>(count) * sizeof(float);
-                int rc = SUSHI_CUDA_OK;
-                if (host) rc = sushi_cuda_memcpy_h2d(ctx, 0, dptr, ptr, bytes);
+                (void)host;
+                float* dptr = nullptr;
+                int rc = detail::stage_in(storage, ptr, count, true, &dptr);
                 if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_activation(ctx, 0, activation, param, dptr, count);
-                if (rc == SUSHI_CUDA_OK && host) rc = sushi_cuda_memcpy_d2h(ctx, 0, ptr, dptr, bytes);
+                if (rc == SUSHI_CUDA_OK) detail::stage_out(storage);
                 return rc;
             });
         return SushiRuntime::Execution::Event();
@@ -512,20 +498,15 @@ namespace SushiBLAS
             {
                 sushi_cuda_ctx* ctx = rt.native_handle();
                 const std::size_t bytes = static_cast<std::size_t>(count) * sizeof(float);
-                auto on_device = [ctx, bytes](const Operand& o, bool upload, float** out) -> int
-                {
-                    char* base = static_cast<char*>(o.storage->allocator->device_view(o.storage->data_ptr));
-                    if (!base) return SUSHI_CUDA_ERR_OOM;
-                    *out = reinterpret_cast<float*>(base + (reinterpret_cast<char*>(o.ptr) - static_cast<char*>(o.storage->data_ptr)));
-                    if (o.host && upload && bytes > 0) return sushi_cuda_memcpy_h2d(ctx, 0, *out, o.ptr, bytes);
-                    return SUSHI_CUDA_OK;
-                };
+                (void)bytes;
+                auto on_device = [count](const Operand& o, bool reads, float** out) -> int
+                { return detail::stage_in(o.storage, o.ptr, count, reads, out); };
                 float *d_dy = nullptr, *d_s = nullptr, *d_dx = nullptr;
                 int rc = on_device(od, true, &d_dy);
                 if (rc == SUSHI_CUDA_OK) rc = on_device(os, true, &d_s);
                 if (rc == SUSHI_CUDA_OK) rc = on_device(ox, false, &d_dx);
                 if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_activation_backward(ctx, 0, activation, param, d_dy, d_s, d_dx, count);
-                if (rc == SUSHI_CUDA_OK && ox.host && bytes > 0) rc = sushi_cuda_memcpy_d2h(ctx, 0, ox.ptr, d_dx, bytes);
+                if (rc == SUSHI_CUDA_OK) detail::stage_out(ox.storage);
                 return rc;
             });
         return SushiRuntime::Execution::Event();

@@ -121,8 +121,13 @@ namespace SushiRuntime
     {
         /// Where a tensor's bytes live.  With cudaMalloc storage and explicit staging:
         ///  DEVICE: device memory only; data() is a device pointer.
-        ///  SHARED: pinned host image the caller reads/writes, mirrored by a device buffer that
-        ///          operations stage through (upload before use, download after a write).
+        ///  SHARED: pinned host image the caller reads/writes, mirrored by a device buffer that operations
+        ///          work on.  Residency is tracked per allocation: within one execute() round an
+        ///          input goes up at most once, what an operation wrote stays on the device for the
+        ///          operations after it (also in later rounds), and the host image is refreshed once,
+        ///          when the caller waits (Event::wait / RuntimeContext::wait_all).  Between a wait
+        ///          and the next execute() the host may rewrite any tensor: a host-valid image is sent
+        ///          up again by the first operation of the next round that reads it.
         ///  HOST:   pinned host image, staged the same way.
         enum class AllocStrategy
         {
@@ -147,6 +152,25 @@ namespace SushiRuntime
                 virtual void* device_view(void* ptr) = 0;
                 /// Native context the allocation belongs to (nullptr for host-only test allocators).
                 virtual sushi_cuda_ctx* native_context() { return nullptr; }
+
+                // -- residency of host-resident allocations (no-ops for allocators without a device)
+                /// Starts an execute() round: host images may have been rewritten since the last one.
+                virtual void begin_round() {}
+                /// Device buffer of allocation `ptr` for an operation that is being enqueued.  With
+                /// `contents` the buffer must hold what the allocation holds (the operation reads it, or
+                /// writes only part of it): a host image newer than the mirror is uploaded first.
+                /// Returns nullptr on failure (*rc receives the status when given).
+                virtual void* device_for_operation(void* ptr, bool contents, int* rc = nullptr)
+                {
+                    (void)contents;
+                    if (rc) *rc = 0;
+                    return device_view(ptr);
+                }
+                /// An enqueued operation writes allocation `ptr` on the device: its host image is stale
+                /// until flush_to_host().
+                virtual void mark_device_written(void* ptr) { (void)ptr; }
+                /// Enqueues the download of every allocation whose host image is stale; returns a status.
+                virtual int flush_to_host() { return 0; }
 
             protected:
                 ~USMAllocator() override = default;
@@ -301,8 +325,78 @@ namespace SushiRuntime
 
                     sushi_cuda_ctx* native_context() override { return ctx_; }
 
+                    void begin_round() override
+                    {
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        ++round_;
+                    }
+
+                    void* device_for_operation(void* ptr, bool contents, int* rc) override
+                    {
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        int status = SUSHI_CUDA_OK;
+                        void* out = nullptr;
+                        auto it = blocks_.find(ptr);
+                        if (it == blocks_.end()) status = SUSHI_CUDA_ERR_INVALID_ARG;
+                        else
+                        {
+                            Block& b = it->second;
+                            if (b.strategy == Memory::AllocStrategy::DEVICE) out = ptr;
+                            else
+                            {
+                                if (!b.mirror) status = sushi_cuda_malloc(ctx_, 0, b.bytes, &b.mirror);
+                                // the mirror is current when the device wrote it last (host image stale) or
+                                // when it was brought up in this round
+                                if (status == SUSHI_CUDA_OK && contents && !b.host_stale && b.valid_round != round_)
+                                    status = sushi_cuda_memcpy_h2d(ctx_, 0, b.mirror, ptr, b.bytes);
+                                if (status == SUSHI_CUDA_OK)
+                                {
+                                    if (contents) b.valid_round = round_;
+                                    out = b.mirror;
+                                }
+                            }
+                        }
+                        if (rc) *rc = status;
+                        return out;
+                    }
+
+                    void mark_device_written(void* ptr) override
+                    {
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        auto it = blocks_.find(ptr);
+                        if (it == blocks_.end() || it->second.strategy == Memory::AllocStrategy::DEVICE) return;
+                        if (!it->second.host_stale) stale_.push_back(ptr);
+                        it->second.host_stale = true;
+                        it->second.valid_round = round_;
+                    }
+
+                    int flush_to_host() override
+                    {
+                        std::lock_guard<std::mutex> lock(mutex_);
+                        int status = SUSHI_CUDA_OK;
+                        for (void* ptr : stale_)
+                        {
+                            auto it = blocks_.find(ptr);
+                            if (it == blocks_.end() || !it->second.host_stale) continue;      // freed meanwhile
+                            Block& b = it->second;
+                            if (status == SUSHI_CUDA_OK) status = sushi_cuda_memcpy_d2h(ctx_, 0, ptr, b.mirror, b.bytes);
+                            b.host_stale = false;
+                        }
+                        stale_.clear();
+                        return status;
+                    }
+
                 private:
-                    struct Block { std::size_t bytes; Memory::AllocStrategy strategy; void* mirror; };
+                    struct Block
+                    {
+                        std::size_t bytes;
+                        Memory::AllocStrategy strategy;
+                        void* mirror;
+                        std::uint64_t valid_round = 0;    ///< execute() round in which the mirror was last made current
+                        bool host_stale = false;          ///< the device wrote the mirror after the host image
+                    };
+                    std::uint64_t round_ = 1;
+                    std::vector<void*> stale_;
                     sushi_cuda_ctx* ctx_;
                     std::mutex mutex_;
                     std::unordered_map<void*, Block> blocks_;
@@ -399,10 +493,13 @@ namespace SushiRuntime
                 sushi_ptr<Memory::USMAllocator> get_allocator() { return allocator_; }
                 sushi_ptr<Memory::USMAllocator> get_allocator(int /*numa_id*/) { return allocator_; }
 
-                /// Global synchronisation; throws std::runtime_error if anything queued has failed.
+                /// Global synchronisation; throws std::runtime_error if anything queued has failed.  Host images
+                /// of the SHARED / HOST allocations that queued operations wrote are refreshed here (one
+                /// download each), behind everything queued, before the call returns.
                 void wait_all()
                 {
-                    const int rc = sushi_cuda_sync(ctx_, 0);
+                    int rc = allocator_ ? allocator_->flush_to_host() : SUSHI_CUDA_OK;
+                    if (rc == SUSHI_CUDA_OK) rc = sushi_cuda_sync(ctx_, 0);
                     if (rc != SUSHI_CUDA_OK)
                         throw std::runtime_error(std::string("wait_all: ") + sushi_cuda_last_error(ctx_));
                 }
@@ -511,6 +608,8 @@ namespace SushiRuntime
                 {
                     std::vector<Task> run;
                     run.swap(tasks_);
+                    // host images may have been rewritten since the last round: inputs go up again, once
+                    ctx_.get_allocator()->begin_round();
                     std::size_t i = 0;
                     while (i < run.size())
                     {

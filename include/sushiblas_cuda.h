@@ -84,9 +84,25 @@ SUSHI_CUDA_API int sushi_cuda_get_stream(sushi_cuda_ctx* ctx, int dev, void** cu
  * faults, traps or hangs.                                                                    */
 SUSHI_CUDA_API int sushi_cuda_selftest_bounded_wait(sushi_cuda_ctx* ctx, int dev, int limit_ms);
 
+/* Host-side fault injection for tests (no counterpart in the reference; nothing on the GPU faults): the
+ * `nth` next call (1 = the very next, 0 = cancel) that reaches `site` returns its error code without making the
+ * CUDA / NCCL call -- SUSHI_CUDA_ERR_OOM for the two allocation sites (device allocation covers sushi_cuda_malloc
+ * and the library's own scratch), SUSHI_CUDA_ERR_COMM for communicator initialisation.  The context stays usable. */
+enum sushi_cuda_fail_site
+{
+    SUSHI_CUDA_FAIL_DEVICE_ALLOC = 1,
+    SUSHI_CUDA_FAIL_COMM_INIT = 2,
+    SUSHI_CUDA_FAIL_HOST_ALLOC = 3
+};
+SUSHI_CUDA_API int sushi_cuda_inject_failure(sushi_cuda_ctx* ctx, int site, int nth);
+
 SUSHI_CUDA_API int sushi_cuda_set_gemm_variant(sushi_cuda_ctx* ctx, int variant);
 /* Number of kernels this context has launched so far (all devices). */
 SUSHI_CUDA_API int sushi_cuda_launch_count(sushi_cuda_ctx* ctx, int64_t* launches);
+/* Bytes this context has moved between host and device through sushi_cuda_memcpy_h2d / _d2h so far
+ * (either pointer may be NULL).  The Engine's residency tests count PCIe crossings with it; the reference
+ * has no counterpart (its shared USM migrates pages without telling anyone).                          */
+SUSHI_CUDA_API int sushi_cuda_copy_bytes(sushi_cuda_ctx* ctx, uint64_t* h2d_bytes, uint64_t* d2h_bytes);
 
 /* Optional per-kernel timing for measurement harnesses: when enabled, every GEMM call brackets
  * its operand pre-pass and its main kernel with CUDA events on the launching stream.
@@ -372,6 +388,14 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, 
  * pins; only the distribution is matched.                                                 */
 SUSHI_CUDA_API int sushi_cuda_fill_uniform(sushi_cuda_ctx* ctx, int dev, float* dst, int64_t count,
                                            uint64_t seed, int64_t first_index);
+
+/* Rate probe of the tensor-core kernel (measurement only; no counterpart in the reference): C <- op(A)*op(B)
+ * through the regular pipeline with both operands pre-split into planes and whole tiles only (no split-K), with
+ * `products` = 3 (the fp32-accurate 3xTF32 product) or 1 (only the hi*hi MMA of every product: a TF32-accurate
+ * result at the kernel's 1xTF32 rate, which bounds what the three-MMA product can reach).                      */
+SUSHI_CUDA_API int sushi_cuda_sgemm_tf32_probe(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b, int64_t m, int64_t n,
+                                               int64_t k, const float* a, int64_t lda, const float* b, int64_t ldb, float* c,
+                                               int64_t ldc, int products);
 
 #ifdef __cplusplus
 }

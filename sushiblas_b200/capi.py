@@ -43,6 +43,8 @@ SIGNATURES = {
     "sushi_cuda_selftest_bounded_wait": (_int, [_vp, _int, _int]),
     "sushi_cuda_set_gemm_variant": (_int, [_vp, _int]),
     "sushi_cuda_launch_count": (_int, [_vp, ctypes.POINTER(_i64)]),
+    "sushi_cuda_inject_failure": (_int, [_vp, _int, _int]),
+    "sushi_cuda_copy_bytes": (_int, [_vp, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "sushi_cuda_kernel_timing_enable": (_int, [_vp, _int]),
     "sushi_cuda_kernel_timing_read": (_int, [_vp, _int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_i64),
                                              ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_i64)]),
@@ -95,6 +97,7 @@ SIGNATURES = {
     "sushi_cuda_sgemm_static_scratch": (_int, [_vp, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
                                                _f32, _vp, _i64, _vp]),
     "sushi_cuda_fill_uniform": (_int, [_vp, _int, _vp, _i64, ctypes.c_uint64, _i64]),
+    "sushi_cuda_sgemm_tf32_probe": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _int]),
 }
 
 _LIB = None
@@ -227,6 +230,16 @@ class SushiCuda:
 
     def set_gemm_variant(self, variant: int):
         self._check(self.lib.sushi_cuda_set_gemm_variant(self._ctx, variant))
+
+    def inject_failure(self, site: int, nth: int = 1):
+        """Host-side fault injection: the nth next call reaching `site` (FAIL_* below) fails without touching the GPU."""
+        self._check(self.lib.sushi_cuda_inject_failure(self._ctx, int(site), int(nth)))
+
+    def copy_bytes(self):
+        """(host->device, device->host) bytes moved through memcpy_h2d / memcpy_d2h so far."""
+        up, down = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        self._check(self.lib.sushi_cuda_copy_bytes(self._ctx, ctypes.byref(up), ctypes.byref(down)))
+        return int(up.value), int(down.value)
 
     def launch_count(self) -> int:
         out = _i64()
@@ -388,6 +401,10 @@ class SushiCuda:
             self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a_local), lda, stride_a,
             _addr(b_local), ldb, stride_b, beta, _addr(c_full), ldc, stride_c, batch, int(gather)))
 
-    # -- harness helper
+    # -- harness helpers
+    def sgemm_tf32_probe(self, trans_a, trans_b, m, n, k, a, lda, b, ldb, c, ldc, products: int, dev: int = 0):
+        self._check(self.lib.sushi_cuda_sgemm_tf32_probe(self._ctx, dev, int(trans_a), int(trans_b), m, n, k, _addr(a), lda,
+                                                         _addr(b), ldb, _addr(c), ldc, int(products)))
+
     def fill_uniform(self, dst, count: int, seed: int, first_index: int = 0, dev: int = 0):
         self._check(self.lib.sushi_cuda_fill_uniform(self._ctx, dev, _addr(dst), count, seed, first_index))

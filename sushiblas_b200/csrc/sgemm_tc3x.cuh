@@ -436,6 +436,9 @@ __device__ __forceinline__ void epilogue_fast(uint32_t taddr0, float4* stg, floa
     }
 }
 
+// PRODUCTS: 3 issues lo*hi + hi*lo + hi*hi per k-step (fp32 accuracy); 1 only hi*hi (rate probe, TF32 accuracy).  A
+// compile-time choice: the MMA-issuing thread is on the critical path and a run-time test in its loop costs 7 %.
+template <int PRODUCTS>
 __global__ void __launch_bounds__(THREADS, 1)
 sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap raw_a, const __grid_constant__ CUtensorMap raw_b,
@@ -595,9 +598,13 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                 const uint64_t koff = (uint64_t)((ks * 8 * 4) >> 4);   // +32 bytes per k-step
                                 const uint32_t acc = (kb > w.kb0 || ks > 0) ? 1u : 0u;   // a run starts from zero
                                 // small terms first, then the leading product
-                                tcgen05_mma_tf32(d, a_lo + koff, b_hi + koff, IDESC_TF32_M128_N256, acc);
-                                tcgen05_mma_tf32(d, a_hi + koff, b_lo + koff, IDESC_TF32_M128_N256, 1u);
-                                tcgen05_mma_tf32(d, a_hi + koff, b_hi + koff, IDESC_TF32_M128_N256, 1u);
+                                if (PRODUCTS == 3)
+                                {
+                                    tcgen05_mma_tf32(d, a_lo + koff, b_hi + koff, IDESC_TF32_M128_N256, acc);
+                                    tcgen05_mma_tf32(d, a_hi + koff, b_lo + koff, IDESC_TF32_M128_N256, 1u);
+                                    tcgen05_mma_tf32(d, a_hi + koff, b_hi + koff, IDESC_TF32_M128_N256, 1u);
+                                }
+                                else tcgen05_mma_tf32(d, a_hi + koff, b_hi + koff, IDESC_TF32_M128_N256, acc);
                             }
                         }
                         tcgen05_commit(empty0 + 8 * s);               // stage reusable once these MMAs retire
@@ -1188,15 +1195,18 @@ struct OperandSource
 // a / b: op(A) (rows = m) and op(B)^T (rows = n).
 // sk_area: zero-initialised exchange area of at least sk_area_bytes(plan) bytes, or nullptr to
 // deal whole tiles only; sk_epoch: a value never used before with this area (and never 0).
+// products: 3 for the fp32-accurate product; 1 issues only the hi*hi MMAs (rate probe, TF32 accuracy).
 inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource& b, float* c,
                                      int64_t m, int64_t n, int64_t k, int64_t ldc, int64_t stride_c, int64_t batch,
                                      float alpha, float beta, int* status, int sm_count, cudaStream_t st,
                                      void* sk_area = nullptr, unsigned int sk_epoch = 0,
                                      float* const* peer_c = nullptr, int n_peers = 0, int act = 0, int tri = 0,
-                                     float act_param = 0.0f)
+                                     float act_param = 0.0f, int products = 3)
 {
     // per-device attribute; cheap enough to set on every launch
-    cudaError_t e = cudaFuncSetAttribute(sgemm_tc3x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = products == 1
+        ? cudaFuncSetAttribute(sgemm_tc3x_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)
+        : cudaFuncSetAttribute(sgemm_tc3x_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const int64_t m_pad = (m + 255) / 256 * 256, n_pad = (n + 255) / 256 * 256;
     const int64_t num_kb = (k + BK - 1) / BK;
@@ -1224,7 +1234,8 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.sk_partials = sk_area ? reinterpret_cast<float*>(static_cast<char*>(sk_area) + SK_FLAG_BYTES) : nullptr;
     p.sk_epoch = sk_epoch;
     if (plan.grid <= 0) return cudaSuccess;
-    sgemm_tc3x_kernel<<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
+    if (products == 1) sgemm_tc3x_kernel<1><<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
+    else sgemm_tc3x_kernel<3><<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
     return cudaGetLastError();
 }
 

@@ -52,41 +52,54 @@ __device__ __forceinline__ int64_t plane_offset(const SplitArgs& p, int64_t bi, 
 }
 
 // k is the contiguous index of the stored operand: element (row, kk) = x[row*ld + kk].
-// One thread per float4 of the padded [rows_pad][num_kb*16] panel, k fastest.
+// One CTA per (64 rows, 4 k-blocks = 64 k): sixteen threads read one row's 256 contiguous bytes (128-bit loads
+// when the operand is 16-byte aligned), four rows per thread in flight, and every (plane, k-block) receives one
+// contiguous 4 KB run.  Neighbouring CTAs take neighbouring k ranges of the same rows.  No index arithmetic
+// beyond the CTA's own decomposition: the pass runs at the speed of the memory system.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 split_tf32_kcontig_kernel(const SplitArgs p)
 {
-    const int64_t k4_per_row = p.num_kb * (SPLIT_KB / 4);
-    const int64_t total = p.batch * p.rows_pad * k4_per_row;
-    const bool vec_ok = ((p.ld & 3) == 0) && ((p.stride_x & 3) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x)
+    const int t = threadIdx.x;
+    const int64_t row_tiles = p.rows_pad / 64;
+    const int64_t k_tiles = (p.num_kb + 3) / 4;
+    int64_t blk = blockIdx.x;
+    const int64_t kt = blk % k_tiles; blk /= k_tiles;
+    const int64_t rt = blk % row_tiles;
+    const int64_t bi = blk / row_tiles;
+    const int k4 = t % 16;
+    const int64_t kk = kt * 64 + k4 * 4;                   // first k of this thread's four
+    const int64_t kb = kt * 4 + k4 / 4;
+    const int within = (k4 % 4) * 4;
+    const int64_t row0 = rt * 64 + t / 16;
+    const float* __restrict__ src = p.x + bi * p.stride_x + kk;
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
     {
-        const int64_t k4 = i % k4_per_row;
-        const int64_t row = (i / k4_per_row) % p.rows_pad;
-        const int64_t bi = i / (k4_per_row * p.rows_pad);
-        const int64_t kk = k4 * 4;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const int64_t row = row0 + 16 * j;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (row < p.rows && kk < p.k)
         {
-            const float* src = p.x + bi * p.stride_x + row * p.ld + kk;
-            if (vec_ok && kk + 3 < p.k)
-            {
-                const float4 q = __ldg(reinterpret_cast<const float4*>(src));
-                v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
-            }
+            const float* q = src + row * p.ld;
+            if (VEC && kk + 3 < p.k) v[j] = __ldg(reinterpret_cast<const float4*>(q));
             else
             {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) if (kk + j < p.k) v[j] = __ldg(src + j);
+                v[j].x = __ldg(q);
+                if (kk + 1 < p.k) v[j].y = __ldg(q + 1);
+                if (kk + 2 < p.k) v[j].z = __ldg(q + 2);
+                if (kk + 3 < p.k) v[j].w = __ldg(q + 3);
             }
         }
+    }
+    if (kb >= p.num_kb) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const int64_t row = row0 + 16 * j;
         float4 hi, lo;
-        split_one(v[0], hi.x, lo.x); split_one(v[1], hi.y, lo.y);
-        split_one(v[2], hi.z, lo.z); split_one(v[3], hi.w, lo.w);
-        const int64_t kb = kk / SPLIT_KB;
-        const int64_t within = kk % SPLIT_KB;
+        split_one(v[j].x, hi.x, lo.x); split_one(v[j].y, hi.y, lo.y);
+        split_one(v[j].z, hi.z, lo.z); split_one(v[j].w, hi.w, lo.w);
         *reinterpret_cast<float4*>(p.planes + plane_offset(p, bi, 0, kb, row) + within) = hi;
         *reinterpret_cast<float4*>(p.planes + plane_offset(p, bi, 1, kb, row) + within) = lo;
     }
@@ -180,19 +193,18 @@ inline cudaError_t launch_split_tf32(const float* x, float* planes, int64_t rows
     p.rows_pad = (rows + SPLIT_ROWPAD - 1) / SPLIT_ROWPAD * SPLIT_ROWPAD;
     p.num_kb = (k + SPLIT_KB - 1) / SPLIT_KB;
     p.batch = batch;
+    (void)sm_count;
+    const int64_t blocks = (p.rows_pad / 64) * ((p.num_kb + 3) / 4) * batch;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    if (blocks == 0) return cudaSuccess;
+    const bool vec = ((ld & 3) == 0) && ((stride_x & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (k_contig)
     {
-        const int64_t total = batch * p.rows_pad * p.num_kb * (SPLIT_KB / 4);
-        int64_t blocks = (total + 255) / 256;
-        const int64_t cap = (int64_t)sm_count * 32;
-        if (blocks > cap) blocks = cap;
-        split_tf32_kcontig_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+        if (vec) split_tf32_kcontig_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(p);
+        else split_tf32_kcontig_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(p);
     }
     else
     {
-        const int64_t blocks = (p.rows_pad / 64) * ((p.num_kb + 3) / 4) * batch;
-        if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-        const bool vec = ((ld & 3) == 0) && ((stride_x & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
         if (vec) split_tf32_rcontig_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(p);
         else split_tf32_rcontig_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(p);
     }

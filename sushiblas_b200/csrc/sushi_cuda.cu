@@ -43,9 +43,6 @@ struct DeviceState
     // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t pipe_events[10] = {};
-    // sharded GEMM: side stream on which most of B is split while the first column panel multiplies
-    cudaStream_t prep_stream = nullptr;
-    cudaEvent_t prep_fork = nullptr, prep_join = nullptr;
     void* trsm_buf = nullptr;             // TRSM: inverted diagonal blocks + one block row/column of temporaries
     size_t trsm_bytes = 0;
     void* group_buf = nullptr;            // device copy of the grouped-launch problem list
@@ -89,6 +86,8 @@ struct sushi_cuda_ctx
     std::string last_error;
     int variant = SUSHI_GEMM_AUTO;
     std::atomic<int64_t> launches{0};
+    std::atomic<uint64_t> h2d_bytes{0}, d2h_bytes{0};   // bytes moved by sushi_cuda_memcpy_h2d / _d2h
+    int fail_countdown[4] = {0, 0, 0, 0};   // host-side fault injection: calls left until the site fails (0: off)
     bool timing = false;
     // multi-GPU (one process per GPU: a single communicator bound to one device index)
     ncclComm_t comm = nullptr;
@@ -108,6 +107,13 @@ int set_error(sushi_cuda_ctx* ctx, int code, const std::string& msg)
 {
     if (ctx) ctx->last_error = msg; else g_tls_error = msg;
     return code;
+}
+
+// Host-side fault injection (sushi_cuda_inject_failure): true when this call of `site` is the one to fail.
+bool injected_failure(sushi_cuda_ctx* ctx, int site)
+{
+    if (!ctx || site < 1 || site > 3 || ctx->fail_countdown[site] == 0) return false;
+    return --ctx->fail_countdown[site] == 0;
 }
 
 int cuda_fail(sushi_cuda_ctx* ctx, cudaError_t e, const char* what)
@@ -137,6 +143,8 @@ int grow(sushi_cuda_ctx* ctx, DeviceState& d, void** buf, size_t* have, size_t n
         SC_CUDA(ctx, cudaFree(*buf));
         *buf = nullptr; *have = 0;
     }
+    if (injected_failure(ctx, SUSHI_CUDA_FAIL_DEVICE_ALLOC))
+        return set_error(ctx, SUSHI_CUDA_ERR_OOM, "injected failure: device allocation (library scratch)");
     SC_CUDA(ctx, cudaMalloc(buf, need));
     *have = need;
     return SUSHI_CUDA_OK;
@@ -242,6 +250,7 @@ struct SlabReuse
     int act = 0;               // epilogue activation (sushi_cuda_activation_kind)
     float act_param = 0.0f;    // its parameter
     int tri = 0;               // triangular output (SYRK): 1 lower, 2 upper
+    int products = 3;          // 1: only the hi*hi MMA of every product (rate probe; forces pre-split planes, no K cut)
 };
 
 int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int64_t n, int64_t k, float alpha,
@@ -279,8 +288,10 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         // costs ~10 % of the kernel's tensor rate (shared-memory bandwidth) for every tile that
         // uses the operand.  Measured break-even on B200: the operand is reused by about eleven
         // 256-wide tiles, so A is split in-kernel when n <= 2048 and B when m <= 2048
-        const bool want_a = n <= 2048;
-        const bool want_b = m <= 2048;
+        const int products = reuse ? reuse->products : 3;
+        const bool probe = reuse && reuse->products != 3;          // rate probe: both operands as planes, whole tiles
+        const bool want_a = n <= 2048 && !probe;
+        const bool want_b = m <= 2048 && !probe;
         // either storage order of an operand can be taken raw: k-contiguous tiles are split in place, row-contiguous
         // ones (A^T, or B not transposed) are transposed by the converters on the way
         const bool fuse_a = want_a && sushi::tc3x::raw_eligible(a, m, k, lda, sa, batch);
@@ -336,8 +347,9 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         else src_b.planes = (same_operand && !fuse_a) ? planes_a : planes_b;
         if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
         SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, m, n, k, ldc, sc, batch, alpha, beta,
-                                                   d.status, d.sm_count, d.stream, sk_area, d.sk_epoch,
-                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, act, tri, act_param));
+                                                   d.status, d.sm_count, d.stream, probe ? nullptr : sk_area, d.sk_epoch,
+                                                   reuse ? reuse->peer_c : nullptr, reuse ? reuse->n_peers : 0, act, tri, act_param,
+                                                   products));
         if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
         ctx->launches += 1 + prepass_launches;
         return SUSHI_CUDA_OK;
@@ -368,80 +380,6 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
     SC_CUDA(ctx, sushi::launch_sgemm_simt(g, ta != 0, tb != 0, batch, d.sm_count, d.stream));
     if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
     ctx->launches++;
-    return SUSHI_CUDA_OK;
-}
-
-// One row block times all of B on the tensor path, as two column panels: panel 0 is sized to whole
-// rounds of the persistent grid (tile columns in multiples of SMs / gcd(SMs, tile rows)) and long
-// enough to cover the split of the rest of B, which runs on a side stream meanwhile.  In the sharded
-// GEMM B is replicated, so its pre-pass is the part of a step that does not shrink with the number
-// of GPUs; this takes most of it off the critical path.  The side stream starts after everything
-// queued on the caller's stream before this call (B may have been produced there) and the second
-// GEMM waits for it.  Returns 1 when the shape does not suit the scheme (the caller then uses
-// run_gemm), 0 on success, a negative error otherwise.
-int run_gemm_two_panels(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t rows, int64_t n, int64_t k, float alpha,
-                        const float* a, int64_t lda, const float* b, int64_t ldb, float beta, float* c, int64_t ldc,
-                        float* const* peer_c, int n_peers)
-{
-    if (rows <= 0 || n <= 0 || k <= 0 || alpha == 0.0f) return 1;
-    const bool want_b = rows <= 2048;
-    if (want_b && tb && sushi::tc3x::raw_eligible(b, n, k, ldb, 0, 1)) return 1;       // B needs no pre-pass
-    const int64_t tiles_m = (rows + 255) / 256, tiles_n = (n + 255) / 256;
-    const int64_t unit = d.sm_count / std::gcd((int64_t)d.sm_count, tiles_m);           // tile columns per whole round
-    int64_t cols0 = 0;
-    for (int64_t tc = unit; tc * 2 <= tiles_n; tc += unit)
-    {
-        // GEMM of panel 0 (~235 TFLOP/s) against the split of the rest (12 B per element at ~4.5 TB/s)
-        const int64_t n0 = tc * 256;
-        if (rows * n0 >= 400 * (n - n0)) { cols0 = n0; break; }
-    }
-    if (cols0 == 0 || (n - cols0 + 255) / 256 * tiles_m < d.sm_count) return 1;
-    SC_CUDA(ctx, cudaSetDevice(d.device));
-    if (!d.prep_stream)
-    {
-        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d.prep_stream, cudaStreamNonBlocking));
-        SC_CUDA(ctx, cudaEventCreateWithFlags(&d.prep_fork, cudaEventDisableTiming));
-        SC_CUDA(ctx, cudaEventCreateWithFlags(&d.prep_join, cudaEventDisableTiming));
-    }
-    const bool want_a = n <= 2048;
-    const bool fuse_a = want_a && !ta && sushi::tc3x::raw_eligible(a, rows, k, lda, 0, 1);
-    const size_t bytes_b0 = sushi::split_plane_bytes(cols0, k, 1), bytes_b1 = sushi::split_plane_bytes(n - cols0, k, 1);
-    const size_t bytes_a = fuse_a ? 0 : sushi::split_plane_bytes(rows, k, 1);
-    int rc = grow(ctx, d, &d.workspace, &d.workspace_bytes, bytes_b0 + bytes_b1 + bytes_a);
-    if (rc != SUSHI_CUDA_OK) return rc;
-    float* planes_b0 = static_cast<float*>(d.workspace);
-    float* planes_b1 = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b0);
-    float* planes_a = reinterpret_cast<float*>(static_cast<char*>(d.workspace) + bytes_b0 + bytes_b1);
-    // column `col` of op(B): op(B)^T row `col`
-    const float* b1 = tb ? b + cols0 * ldb : b + cols0;
-
-    SC_CUDA(ctx, cudaEventRecord(d.prep_fork, d.stream));
-    SC_CUDA(ctx, cudaStreamWaitEvent(d.prep_stream, d.prep_fork, 0));
-    SC_CUDA(ctx, sushi::launch_split_tf32(b1, planes_b1, n - cols0, k, ldb, 0, 1, /*k_contig=*/tb != 0, d.sm_count, d.prep_stream));
-    SC_CUDA(ctx, cudaEventRecord(d.prep_join, d.prep_stream));
-
-    if ((rc = timing_mark(ctx, d, 0, fuse_a ? 1 : 2)) != SUSHI_CUDA_OK) return rc;
-    if (!fuse_a) SC_CUDA(ctx, sushi::launch_split_tf32(a, planes_a, rows, k, lda, 0, 1, /*k_contig=*/!ta, d.sm_count, d.stream));
-    SC_CUDA(ctx, sushi::launch_split_tf32(b, planes_b0, cols0, k, ldb, 0, 1, /*k_contig=*/tb != 0, d.sm_count, d.stream));
-    sushi::tc3x::OperandSource src_a, src_b;
-    if (fuse_a) { src_a.raw = a; src_a.ld = lda; src_a.stride = 0; } else src_a.planes = planes_a;
-    float* peers[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-    for (int i = 0; i < n_peers && i < 7; ++i) peers[i] = peer_c[i];
-    src_b.planes = planes_b0;
-    if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
-    SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c, rows, cols0, k, ldc, 0, 1, alpha, beta, d.status, d.sm_count,
-                                               d.stream, nullptr, 0, n_peers ? peers : nullptr, n_peers));
-    if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
-
-    SC_CUDA(ctx, cudaStreamWaitEvent(d.stream, d.prep_join, 0));
-    for (int i = 0; i < n_peers && i < 7; ++i) peers[i] = peer_c[i] + cols0;
-    src_b.planes = planes_b1;
-    if ((rc = timing_mark(ctx, d, 0, 1)) != SUSHI_CUDA_OK) return rc;
-    if ((rc = timing_mark(ctx, d, 1, 0)) != SUSHI_CUDA_OK) return rc;
-    SC_CUDA(ctx, sushi::tc3x::launch_sgemm_tc3x(src_a, src_b, c + cols0, rows, n - cols0, k, ldc, 0, 1, alpha, beta, d.status,
-                                               d.sm_count, d.stream, nullptr, 0, n_peers ? peers : nullptr, n_peers));
-    if ((rc = timing_mark(ctx, d, 2, 0)) != SUSHI_CUDA_OK) return rc;
-    ctx->launches += (fuse_a ? 0 : 1) + 4;
     return SUSHI_CUDA_OK;
 }
 
@@ -593,9 +531,6 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         if (d.status_host) cudaFreeHost(d.status_host);
         for (cudaEvent_t e : d.timing_events) cudaEventDestroy(e);
         if (d.copy_in) { cudaStreamSynchronize(d.copy_in); cudaStreamDestroy(d.copy_in); }
-        if (d.prep_stream) { cudaStreamSynchronize(d.prep_stream); cudaStreamDestroy(d.prep_stream); }
-        if (d.prep_fork) cudaEventDestroy(d.prep_fork);
-        if (d.prep_join) cudaEventDestroy(d.prep_join);
         if (d.copy_out) { cudaStreamSynchronize(d.copy_out); cudaStreamDestroy(d.copy_out); }
         for (cudaEvent_t e : d.pipe_events) if (e) cudaEventDestroy(e);
         if (d.own_stream) cudaStreamDestroy(d.own_stream);
@@ -710,8 +645,18 @@ extern "C" int sushi_cuda_malloc(sushi_cuda_ctx* ctx, int dev, size_t bytes, voi
     DeviceState* d = get_dev(ctx, dev);
     if (!d || !ptr || bytes == 0) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "malloc: bad argument");
     *ptr = nullptr;
+    if (injected_failure(ctx, SUSHI_CUDA_FAIL_DEVICE_ALLOC))
+        return set_error(ctx, SUSHI_CUDA_ERR_OOM, "injected failure: device allocation");
     SC_CUDA(ctx, cudaSetDevice(d->device));
     SC_CUDA(ctx, cudaMalloc(ptr, bytes));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_inject_failure(sushi_cuda_ctx* ctx, int site, int nth)
+{
+    if (!ctx || site < 1 || site > 3 || nth < 0)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "inject_failure: bad argument");
+    ctx->fail_countdown[site] = nth;
     return SUSHI_CUDA_OK;
 }
 
@@ -729,6 +674,8 @@ extern "C" int sushi_cuda_host_alloc(sushi_cuda_ctx* ctx, size_t bytes, void** p
 {
     if (!ctx || !ptr || bytes == 0) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "host_alloc: bad argument");
     *ptr = nullptr;
+    if (injected_failure(ctx, SUSHI_CUDA_FAIL_HOST_ALLOC))
+        return set_error(ctx, SUSHI_CUDA_ERR_OOM, "injected failure: pinned host allocation");
     SC_CUDA(ctx, cudaSetDevice(ctx->devs[0].device));
     SC_CUDA(ctx, cudaHostAlloc(ptr, bytes, cudaHostAllocPortable));
     return SUSHI_CUDA_OK;
@@ -751,6 +698,16 @@ static int copy_async(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, 
     if (!dst || !src) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, std::string(what) + ": null pointer");
     SC_CUDA(ctx, cudaSetDevice(d->device));
     SC_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, kind, d->stream));
+    if (kind == cudaMemcpyHostToDevice) ctx->h2d_bytes += bytes;
+    if (kind == cudaMemcpyDeviceToHost) ctx->d2h_bytes += bytes;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_copy_bytes(sushi_cuda_ctx* ctx, uint64_t* h2d_bytes, uint64_t* d2h_bytes)
+{
+    if (!ctx) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "copy_bytes: bad context");
+    if (h2d_bytes) *h2d_bytes = ctx->h2d_bytes;
+    if (d2h_bytes) *d2h_bytes = ctx->d2h_bytes;
     return SUSHI_CUDA_OK;
 }
 
@@ -1346,6 +1303,8 @@ extern "C" int sushi_cuda_comm_init_rank(sushi_cuda_ctx* ctx, int dev, const voi
         return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "comm_init_rank: bad argument");
     if (ctx->comm) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "comm_init_rank: communicator already exists");
     std::string err;
+    if (injected_failure(ctx, SUSHI_CUDA_FAIL_COMM_INIT))
+        return set_error(ctx, SUSHI_CUDA_ERR_COMM, "injected failure: communicator initialisation");
     if (!load_nccl(&err)) return set_error(ctx, SUSHI_CUDA_ERR_COMM, err);
     SC_CUDA(ctx, cudaSetDevice(d->device));
     Id128 id;
@@ -1523,15 +1482,7 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     int exchange = 0;
     sushi_cuda_row_sharded_exchange(m, n, k, nranks, ctx->variant, d->sm_count, gather, &exchange);
     if (!do_gather)
-    {
-        if (tensor_for(count))
-        {
-            rc = run_gemm_two_panels(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, b, ldb, beta, c_block, ldc,
-                                     nullptr, 0);
-            if (rc <= 0) return rc;
-        }
         return run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1);
-    }
 
     // Fused exchange: one launch over the whole block; the epilogue stores C tiles to the peers.
     if (exchange == 2 && !ctx->peer_buffers.empty())
@@ -1551,11 +1502,8 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
             fused.variant = SUSHI_GEMM_TC3X;
             for (int r = 0; r < nranks; ++r)
                 if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * ldc;
-            rc = run_gemm_two_panels(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, b, ldb, beta, c_block, ldc,
-                                     fused.peer_c, fused.n_peers);
-            if (rc > 0)
-                rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
-                              &fused);
+            rc = run_gemm(ctx, *d, trans_a, trans_b, count, n, k, alpha, a_local, lda, 0, b, ldb, 0, beta, c_block, ldc, 0, 1,
+                          &fused);
             if (rc != SUSHI_CUDA_OK) return rc;
         }
         // barrier 2: every rank's kernel (and with it its stores into this rank's buffer) is complete
@@ -1646,6 +1594,22 @@ extern "C" int sushi_cuda_fill_uniform(sushi_cuda_ctx* ctx, int dev, float* dst,
     ctx->launches++;
     SC_CUDA(ctx, cudaGetLastError());
     return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_sgemm_tf32_probe(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b, int64_t m, int64_t n,
+                                           int64_t k, const float* a, int64_t lda, const float* b, int64_t ldb, float* c,
+                                           int64_t ldc, int products)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || (products != 1 && products != 3))
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_tf32_probe: bad argument (products is 1 or 3)");
+    int rc = validate_gemm(ctx, m, n, k, a, lda, b, ldb, c, ldc, trans_a, trans_b, 0, 0, 0, 1);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    if (m == 0 || n == 0 || k == 0) return SUSHI_CUDA_OK;
+    SlabReuse probe;
+    probe.variant = SUSHI_GEMM_TC3X;
+    probe.products = products == 1 ? 1 : 2;       // 2: the regular three products, but on the probe's path (planes, whole tiles)
+    return run_gemm(ctx, *d, trans_a, trans_b, m, n, k, 1.0f, a, lda, 0, b, ldb, 0, 0.0f, c, ldc, 0, 1, &probe);
 }
 
 // ======================================================================== allocation-free variant

@@ -467,6 +467,91 @@ TEST_CASE(FrameworkSimShapesAndStress)
     }
 }
 
+TEST_CASE(DeepForwardPassOnDefaultTensorsCrossesPcieOncePerTensor)
+{
+    // tests/runtime/test_framework_sim.cpp:18-72 exactly as the reference writes it: default (SHARED) tensors
+    // filled through data_as<T>() (tests/test_common.hpp:36-46), ten GEMM + ReLU layers, one execute().wait().
+    // Residency: X and every weight go up once, no activation crosses PCIe between layers, every written
+    // activation comes down once, at the wait.
+    sb::Engine engine(runtime());
+    sushi_cuda_ctx* native = runtime().native_handle();
+    const int batch = 512, features = 1024, layers = 10;
+    auto X = engine.create_tensor({batch, features});
+    fill_tensor(X, std::vector<float>(size_t(batch) * features, 1.0f));
+    std::vector<sb::Tensor> weights, activations;
+    activations.push_back(X);
+    for (int i = 0; i < layers; ++i)
+    {
+        auto W = engine.create_tensor({features, features});
+        fill_tensor(W, std::vector<float>(size_t(features) * features, 0.01f));
+        weights.push_back(W);
+        activations.push_back(engine.create_tensor({batch, features}));
+    }
+    const uint64_t act_bytes = uint64_t(batch) * features * 4, w_bytes = uint64_t(features) * features * 4;
+    double ms = 0.0;
+    for (int pass = 0; pass < 2; ++pass)          // the first pass also allocates mirrors and the library's scratch
+    {
+        uint64_t up0 = 0, down0 = 0, up1 = 0, down1 = 0;
+        EXPECT_EQ(sushi_cuda_copy_bytes(native, &up0, &down0), SUSHI_CUDA_OK);
+        auto t0 = std::chrono::steady_clock::now();
+        for (int i = 0; i < layers; ++i)
+        {
+            engine.blas().gemm(activations[i], weights[i], activations[i + 1]);
+            if (i < layers - 1) engine.nonlinear().relu(activations[i + 1]);
+        }
+        engine.execute().wait();
+        ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        EXPECT_EQ(sushi_cuda_copy_bytes(native, &up1, &down1), SUSHI_CUDA_OK);
+        std::printf("       DeepForwardPass 10 x (512x1024x1024) on SHARED tensors, pass %d: %.3f ms, %.1f MB up, %.1f MB down\n",
+                    pass, ms, double(up1 - up0) / 1e6, double(down1 - down0) / 1e6);
+        EXPECT_EQ(up1 - up0, act_bytes + layers * w_bytes);          // X and the ten weights, once each
+        EXPECT_EQ(down1 - down0, layers * act_bytes);                // H1 .. H10, once each, at the wait
+    }
+    // all ones times 0.01: H_l = 1024 * 0.01 * H_{l-1} = 10.24^l (ReLU changes nothing)
+    double want = 1.0;
+    for (int l = 1; l <= layers; ++l)
+    {
+        want *= 10.24;
+        EXPECT_NEAR(activations[l].data_as<float>()[12345] / want, 1.0, 1e-4);
+    }
+    EXPECT_TRUE(ms > 0);
+
+    // a second round reads what the first left on the device: H11 = H10 * W0 sends W0 up again (the host may
+    // have rewritten it since the wait) but not H10, unless the host touches it -- a host write is picked up
+    auto H11 = engine.create_tensor({batch, features});
+    uint64_t up0 = 0, up1 = 0;
+    sushi_cuda_copy_bytes(native, &up0, nullptr);
+    engine.blas().gemm(activations[layers], weights[0], H11);
+    engine.execute().wait();
+    sushi_cuda_copy_bytes(native, &up1, nullptr);
+    EXPECT_EQ(up1 - up0, act_bytes + w_bytes);                       // host-valid images are re-sent once per round
+    EXPECT_NEAR(H11.data_as<float>()[777] / (want * 10.24), 1.0, 1e-4);
+    std::fill_n(activations[layers].data_as<float>(), size_t(batch) * features, 2.0f);
+    engine.blas().gemm(activations[layers], weights[0], H11);
+    engine.execute().wait();
+    EXPECT_NEAR(H11.data_as<float>()[777], 2.0f * 10.24f, 1e-3);
+
+    // two rounds without a wait in between: the second reads the first's output from the device
+    auto P = engine.create_tensor({64, 64}), Q = engine.create_tensor({64, 64}), R = engine.create_tensor({64, 64});
+    auto S = engine.create_tensor({64, 64});
+    std::fill_n(P.data_as<float>(), 4096, 1.0f); std::fill_n(Q.data_as<float>(), 4096, 0.5f);
+    engine.blas().gemm(P, Q, R);
+    engine.execute();
+    engine.blas().gemm(R, Q, S);
+    engine.execute().wait();
+    EXPECT_NEAR(R.data_as<float>()[100], 32.0f, 1e-4);
+    EXPECT_NEAR(S.data_as<float>()[100], 32.0f * 32.0f, 1e-3);
+
+    // an operation that writes a slice keeps the rest of the storage: the whole image goes up first
+    auto C = engine.create_tensor({8, 8}), A = engine.create_tensor({4, 8}), B = engine.create_tensor({8, 8});
+    std::fill_n(C.data_as<float>(), 64, 7.0f); std::fill_n(A.data_as<float>(), 32, 1.0f); std::fill_n(B.data_as<float>(), 64, 1.0f);
+    auto top = C.slice(0, 0, 4);
+    engine.blas().gemm(A, B, top);
+    engine.execute().wait();
+    EXPECT_EQ(C.data_as<float>()[0], 8.0f);
+    EXPECT_EQ(C.data_as<float>()[63], 7.0f);
+}
+
 TEST_CASE(ExampleFlowWithWaitAll)
 {
     // examples/example.cpp:34-56: column-major engine, 1024^2 tensors, execute() then ctx.wait_all()

@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 
 from oracle import ref_gemm as og
+from sushiblas_b200 import SushiCuda, SushiCudaError
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -597,6 +598,61 @@ def test_storage_calls_round_trip(ctx):
     ctx.free(d); ctx.free(d2); ctx.host_free(h)
 
 
+def test_injected_host_side_failures_are_reported_and_survivable(ctx):
+    own = SushiCuda([0])                         # a context of its own: its scratch starts empty
+    own.set_stream(torch.cuda.current_stream().cuda_stream)
+    try:
+        _injected_failures(own)
+    finally:
+        torch.cuda.synchronize()
+        own.close()
+
+
+def _injected_failures(ctx):
+    """Failure paths that cannot be provoked on a healthy machine are reached through the host-side hook
+    (nothing on the GPU faults): a device allocation, the library's own scratch allocation inside a GEMM, a
+    pinned-host allocation and the communicator initialisation each return their error code once, name the
+    injection in the message, and leave the context usable."""
+    FAIL_DEVICE_ALLOC, FAIL_COMM_INIT, FAIL_HOST_ALLOC = 1, 2, 3
+    copies_before = ctx.copy_bytes()
+    ctx.inject_failure(FAIL_DEVICE_ALLOC, 1)
+    with pytest.raises(SushiCudaError) as e:
+        ctx.malloc(1 << 20)
+    assert e.value.code == -4 and "injected" in str(e.value)
+    p = ctx.malloc(1 << 20)                      # the next call is served again
+    ctx.free(p)
+    ctx.inject_failure(FAIL_HOST_ALLOC, 2)       # the second next one
+    h = ctx.host_alloc(4096)
+    with pytest.raises(SushiCudaError) as e:
+        ctx.host_alloc(4096)
+    assert e.value.code == -4
+    ctx.host_free(h)
+    # scratch of the tensor path: an unaligned leading dimension forces the pre-pass, whose planes are larger than
+    # anything this context has needed so far
+    m, n, k = 1536, 1280, 6148
+    cs = make_case(91, 0, 0, m, n, k, 1, pad=(1, 0, 0))
+    da, db, dc = dev(cs["a"]), dev(cs["b"]), dev(cs["c"])
+    ctx.set_gemm_variant(TC3X)
+    ctx.inject_failure(FAIL_DEVICE_ALLOC, 1)
+    with pytest.raises(SushiCudaError) as e:
+        ctx.sgemm(0, 0, m, n, k, 1.0, da, cs["lda"], db, cs["ldb"], 0.0, dc, cs["ldc"])
+    assert e.value.code == -4 and "scratch" in str(e.value)
+    ctx.sgemm(0, 0, m, n, k, 1.0, da, cs["lda"], db, cs["ldb"], 0.0, dc, cs["ldc"])
+    ctx.sync()
+    ctx.set_gemm_variant(AUTO)
+    ref, absab = og.gemm_f64_np(0, 0, m, n, k, 1.0, cs["a"], cs["lda"], 0, cs["b"], cs["ldb"], 0, 0.0, cs["c"], cs["ldc"], 0, 1)
+    r, _ = og.tolerance_ratio(dc.cpu().numpy().reshape(1, m, n), ref, absab, k, budget=BUDGET)
+    assert r <= 1.0
+    ctx.inject_failure(FAIL_COMM_INIT, 1)
+    with pytest.raises(SushiCudaError) as e:
+        ctx.comm_init_rank(bytes(128), 1, 0)
+    assert e.value.code == -6 and "injected" in str(e.value)
+    ctx.inject_failure(FAIL_COMM_INIT, 0)        # cancelling is allowed
+    with pytest.raises(SushiCudaError):
+        ctx.inject_failure(7, 1)
+    assert ctx.copy_bytes() == copies_before     # none of this moved a byte over PCIe through the library
+
+
 def test_bounded_wait_expiry_reaches_the_host_and_context_survives(ctx):
     """Failure detection without a fault: a kernel-side wait on a barrier nothing arrives on gives
     up after its limit and records a code; sync reports KERNEL_TIMEOUT once, clears it, and the
@@ -631,36 +687,38 @@ def test_tall_and_skinny_products(ctx, tb):
     check(ctx, AUTO, 0, tb, 2100, 16, 64, 1.0, 0.5, pad=(1, 0, 0), seed=852)
 
 
-def test_row_block_in_two_column_panels_matches_single_call(ctx):
-    """The sharded entry point multiplies a row block in two column panels (the split of most of B
-    runs on a side stream under the first panel's GEMM).  Same kernels, same per-tile arithmetic:
-    the result must equal the plain call bit for bit, in every transpose, with alpha / beta."""
-    m, n, k = 1024, 18944 + 256, 272          # 4 tile rows -> panels of 37 tile columns; ragged k
+def test_split_inside_the_kernel_equals_pre_split_planes(ctx):
+    """Operands of a problem this small are split into hi / lo inside the GEMM kernel (either storage order); the
+    rate probe forces the pre-pass and whole tiles.  Same rounding, same per-tile arithmetic: bit-equal results
+    in every transpose, and the one-product probe (hi * hi only) stays within TF32 accuracy of the oracle."""
+    m, n, k = 1024, 1536, 232                 # 15 k-blocks: too few for the few-tiles K cut, so both paths deal whole tiles
+    a = og.uniform_pm1(700, m * k)
+    b = og.uniform_pm1(710, k * n)
+    da, db = dev(a), dev(b)
     for ta, tb in [(0, 0), (0, 1), (1, 0), (1, 1)]:
-        a = og.uniform_pm1(700 + ta, m * k)
-        b = og.uniform_pm1(710 + tb, k * n)
-        c0 = og.uniform_pm1(720, m * n)
-        da, db = dev(a), dev(b)
         lda, ldb = (m if ta else k), (k if tb else n)
-        c1, c2 = dev(c0), dev(c0)
+        c1, c2, c3 = (torch.empty(m * n, device="cuda") for _ in range(3))
         ctx.set_gemm_variant(TC3X)
         before = ctx.launch_count()
-        ctx.sgemm_row_sharded(ta, tb, m, n, k, 1.5, da, lda, db, ldb, 0.5, c1, n, gather=0)
-        sharded_launches = ctx.launch_count() - before
-        ctx.sgemm(ta, tb, m, n, k, 1.5, da, lda, db, ldb, 0.5, c2, n)
+        ctx.sgemm(ta, tb, m, n, k, 1.0, da, lda, db, ldb, 0.0, c1, n)
+        assert ctx.launch_count() - before == 1, (ta, tb)                 # no pre-pass
+        before = ctx.launch_count()
+        ctx.sgemm_tf32_probe(ta, tb, m, n, k, da, lda, db, ldb, c2, n, 3)
+        assert ctx.launch_count() - before == 3, (ta, tb)                 # two pre-pass launches and the GEMM
+        ctx.sgemm_tf32_probe(ta, tb, m, n, k, da, lda, db, ldb, c3, n, 1)
         ctx.sync()
         ctx.set_gemm_variant(AUTO)
-        if not (tb and m <= 2048):             # B split inside the kernel: nothing to pipeline
-            assert sharded_launches >= 4, (ta, tb, sharded_launches)      # two B splits and two GEMMs at least
         assert torch.equal(c1, c2), (ta, tb)
-        rows = np.array([0, 255, 256, 1023])
-        got = c1.cpu().numpy().reshape(m, n)[rows]
         av = a.reshape(k, m).T if ta else a.reshape(m, k)
         bv = b.reshape(n, k).T if tb else b.reshape(k, n)
-        ref = 1.5 * (av[rows].astype(np.float64) @ bv.astype(np.float64)) + 0.5 * c0.reshape(m, n)[rows]
-        absab = np.abs(av[rows]).astype(np.float64) @ np.abs(bv).astype(np.float64)
-        r, _ = og.tolerance_ratio(got[None], ref[None], absab[None], k, beta=0.5, c_in=c0.reshape(m, n)[rows][None], budget=BUDGET)
+        ref = av.astype(np.float64) @ bv.astype(np.float64)
+        absab = np.abs(av).astype(np.float64) @ np.abs(bv).astype(np.float64)
+        r, _ = og.tolerance_ratio(c1.cpu().numpy().reshape(1, m, n), ref[None], absab[None], k, budget=BUDGET)
         assert r <= 1.0, (ta, tb, r)
+        # hi * hi alone: each factor carries a relative error of at most 2^-11
+        err1 = np.abs(c3.cpu().numpy().reshape(m, n).astype(np.float64) - ref)
+        assert np.all(err1 <= 2.0 ** -9.9 * absab + 1e-30), (ta, tb, float((err1 / absab).max()))
+        assert float((err1 / absab).max()) > 2.0 ** -16, "the one-product probe should not be fp32-accurate"
 
 
 def test_launch_counter_counts_kernels(ctx):
