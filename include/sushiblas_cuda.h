@@ -371,6 +371,24 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, in
                                                 const float* b, int64_t ldb,
                                                 float beta, float* c_full, int64_t ldc, int gather);
 
+/* Host-buffer form of the row-block sharded GEMM (host staging of device tensors: reference src/io.cpp:73-78,
+ * 103-108; host-resident inputs and outputs are what the reference's callers hold, include/SushiBLAS/engine.hpp:
+ * 156-168).  `a_local_host` holds this rank's rows of op(A) and `c_block_host` receives this rank's rows of C,
+ * both laid out as for sushi_cuda_sgemm_row_sharded's local block; `b_host` is the whole B, of which every rank
+ * needs only its share of the k rows to be valid when B is stored k x n with ldb == n: the rank uploads that
+ * share and the others arrive device to device through the communicator, under the upload of A.  (A transposed
+ * or padded B goes up whole on every rank.)  The block is multiplied in row chunks as they arrive and each
+ * chunk of C streams back while the next multiplies; C goes up first only when beta != 0 or ldc != n.
+ * `a_local_dev`, `b_dev` (whole B) and `c_block_dev` are caller-owned device buffers of the same layouts; the
+ * call allocates nothing of that size.  It is collective over the communicator and completes in stream order
+ * on the context's stream; the host buffers should be pinned (sushi_cuda_host_alloc) for the copies to overlap. */
+SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded_host(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                     int64_t m, int64_t n, int64_t k, float alpha,
+                                                     const float* a_local_host, int64_t lda,
+                                                     const float* b_host, int64_t ldb,
+                                                     float beta, float* c_block_host, int64_t ldc,
+                                                     float* a_local_dev, float* b_dev, float* c_block_dev);
+
 /* Batch-index sharded strided-batched GEMM: the rank owns batches [first, first+count) of
  * the global `batch`; a_local / b_local point at its first owned batch; c_full is the whole
  * batch x m x n result (contiguous: ldc == n, stride_c == m*n is required when gather != 0). */

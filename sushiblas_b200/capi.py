@@ -92,6 +92,8 @@ SIGNATURES = {
     "sushi_cuda_row_sharded_exchange": (_int, [_i64, _i64, _i64, _int, _int, _int, _int, ctypes.POINTER(_int)]),
     "sushi_cuda_sgemm_row_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
                                             _f32, _vp, _i64, _int]),
+    "sushi_cuda_sgemm_row_sharded_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
+                                                 _f32, _vp, _i64, _vp, _vp, _vp]),
     "sushi_cuda_sgemm_batch_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
                                               _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _i64, _i64, _int]),
     "sushi_cuda_sgemm_static_scratch": (_int, [_vp, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
@@ -394,6 +396,13 @@ class SushiCuda:
         self._check(self.lib.sushi_cuda_sgemm_row_sharded(
             self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a_local), lda, _addr(b), ldb,
             beta, _addr(c_full), ldc, int(gather)))
+
+    def sgemm_row_sharded_host(self, trans_a, trans_b, m, n, k, alpha, a_local_host, lda, b_host, ldb, beta, c_block_host, ldc,
+                               a_local_dev, b_dev, c_block_dev, dev: int = 0):
+        """Host buffers in and out (pinned for overlap); the three device buffers are caller-owned scratch."""
+        self._check(self.lib.sushi_cuda_sgemm_row_sharded_host(
+            self._ctx, dev, int(trans_a), int(trans_b), m, n, k, alpha, _addr(a_local_host), lda, _addr(b_host), ldb,
+            beta, _addr(c_block_host), ldc, _addr(a_local_dev), _addr(b_dev), _addr(c_block_dev)))
 
     def sgemm_batch_sharded(self, trans_a, trans_b, m, n, k, alpha, a_local, lda, stride_a, b_local, ldb, stride_b,
                             beta, c_full, ldc, stride_c, batch, gather: bool = True, dev: int = 0):

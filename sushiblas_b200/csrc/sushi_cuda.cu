@@ -1545,6 +1545,116 @@ extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int tr
     return SUSHI_CUDA_OK;
 }
 
+// Host-buffer form of the row-sharded GEMM.  Every rank uploads its rows of A and only ITS share of B's k rows;
+// the shares are exchanged device to device (NVLink) while A is still going up, the block is multiplied in row
+// chunks as they arrive and each chunk of C streams back while the next one multiplies.  One cudaMemcpyAsync per
+// piece; the copies run on the device's copy streams, the exchange on the communicator's stream.
+extern "C" int sushi_cuda_sgemm_row_sharded_host(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
+                                                 int64_t m, int64_t n, int64_t k, float alpha,
+                                                 const float* a_local_host, int64_t lda,
+                                                 const float* b_host, int64_t ldb,
+                                                 float beta, float* c_block_host, int64_t ldc,
+                                                 float* a_local_dev, float* b_dev, float* c_block_dev)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_row_sharded_host: bad context or device index");
+    const int nranks = ctx->comm ? ctx->nranks : 1, rank = ctx->comm ? ctx->rank : 0;
+    if (ctx->comm && ctx->comm_dev != dev)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_row_sharded_host: communicator is bound to another device");
+    int64_t first, count;
+    sushi_cuda_partition(m, nranks, rank, &first, &count);
+    int rc = validate_gemm(ctx, count, n, k, a_local_host, lda, b_host, ldb, c_block_host, ldc, trans_a, trans_b, 0, 0, 0, 1);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    if (!a_local_dev || !b_dev || !c_block_dev)
+        return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "sgemm_row_sharded_host: null device buffer");
+    if (m == 0 || n == 0) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    if (!d->copy_in)
+    {
+        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->copy_in, cudaStreamNonBlocking));
+        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->copy_out, cudaStreamNonBlocking));
+        for (cudaEvent_t& e : d->pipe_events) SC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    cudaEvent_t* ev = d->pipe_events;          // [0] start, [1..4] chunk uploaded, [5..8] chunk multiplied, [9] all downloaded
+    if ((rc = ensure_events(ctx, 2)) != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaEventRecord(ev[0], d->stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_in, ev[0], 0));      // after everything queued before this call
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[0], 0));
+
+    // ---- B: this rank's k rows go up, the others' arrive over the interconnect.  That needs B stored k x n with
+    // dense rows (a share is then one contiguous run); otherwise every rank uploads all of B.
+    const int64_t b_rows = trans_b ? n : k, b_cols = trans_b ? k : n;
+    const bool exchange_b = nranks > 1 && !trans_b && ldb == n && k > 0;
+    if (k > 0)
+    {
+        if (exchange_b)
+        {
+            int64_t k0, kc;
+            sushi_cuda_partition(k, nranks, rank, &k0, &kc);
+            if (kc > 0)
+                SC_CUDA(ctx, cudaMemcpyAsync(b_dev + k0 * ldb, b_host + k0 * ldb, (size_t)kc * (size_t)n * sizeof(float),
+                                             cudaMemcpyHostToDevice, d->copy_in));
+            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[0], d->copy_in));
+            SC_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->slab_events[0], 0));
+            const int64_t block = (k + nranks - 1) / nranks;
+            if ((rc = gather_slab(ctx, b_dev, k, n, 0, block)) != SUSHI_CUDA_OK) return rc;
+            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[1], ctx->comm_stream));
+            SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[1], 0));
+        }
+        else
+        {
+            SC_CUDA(ctx, cudaMemcpyAsync(b_dev, b_host, (size_t)extent(b_rows, b_cols, ldb, 0, 1) * sizeof(float),
+                                         cudaMemcpyHostToDevice, d->copy_in));
+            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[0], d->copy_in));
+            SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[0], 0));
+        }
+    }
+
+    // ---- A and C in row chunks of whole tiles
+    const bool upload_c = beta != 0.0f || ldc != n;
+    int chunks = count >= 2048 ? 4 : 1;
+    int64_t per = (count + chunks - 1) / chunks;
+    per = (per + 255) / 256 * 256;
+    SlabReuse reuse;
+    // one kernel family for the whole block, chosen from what all ranks share (the largest block)
+    {
+        const int64_t block = (m + nranks - 1) / nranks;
+        if (ctx->variant == SUSHI_GEMM_AUTO)
+            reuse.variant = (k >= 4 && prefer_tc3x(block, n, k, 1, d->sm_count)) ? SUSHI_GEMM_TC3X : SUSHI_GEMM_SIMT;
+    }
+    reuse.max_rows = per < count ? per : count;
+    for (int i = 0; i < chunks; ++i)
+    {
+        const int64_t r0 = i * per, r1 = (r0 + per < count) ? r0 + per : count;
+        if (r1 <= r0) continue;
+        const int64_t rows = r1 - r0;
+        const size_t cc = (size_t)extent(rows, n, ldc, 0, 1) * sizeof(float);
+        if (k > 0)
+        {
+            if (trans_a)
+                SC_CUDA(ctx, cudaMemcpy2DAsync(a_local_dev + r0, (size_t)lda * sizeof(float), a_local_host + r0, (size_t)lda * sizeof(float),
+                                               (size_t)rows * sizeof(float), (size_t)k, cudaMemcpyHostToDevice, d->copy_in));
+            else
+                SC_CUDA(ctx, cudaMemcpyAsync(a_local_dev + r0 * lda, a_local_host + r0 * lda, (size_t)extent(rows, k, lda, 0, 1) * sizeof(float),
+                                             cudaMemcpyHostToDevice, d->copy_in));
+        }
+        if (upload_c)
+            SC_CUDA(ctx, cudaMemcpyAsync(c_block_dev + r0 * ldc, c_block_host + r0 * ldc, cc, cudaMemcpyHostToDevice, d->copy_in));
+        SC_CUDA(ctx, cudaEventRecord(ev[1 + i], d->copy_in));
+        SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[1 + i], 0));
+        rc = run_gemm(ctx, *d, trans_a, trans_b, rows, n, k, alpha, trans_a ? a_local_dev + r0 : a_local_dev + r0 * lda, lda, 0,
+                      b_dev, ldb, 0, beta, c_block_dev + r0 * ldc, ldc, 0, 1, &reuse);
+        if (rc != SUSHI_CUDA_OK) return rc;
+        SC_CUDA(ctx, cudaEventRecord(ev[5 + i], d->stream));
+        SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[5 + i], 0));
+        SC_CUDA(ctx, cudaMemcpyAsync(c_block_host + r0 * ldc, c_block_dev + r0 * ldc, cc, cudaMemcpyDeviceToHost, d->copy_out));
+    }
+    // the call completes on the caller's stream once the last download has
+    SC_CUDA(ctx, cudaEventRecord(ev[9], d->copy_out));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[9], 0));
+    return SUSHI_CUDA_OK;
+}
+
 extern "C" int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                               int64_t m, int64_t n, int64_t k, float alpha,
                                               const float* a_local, int64_t lda, int64_t stride_a,

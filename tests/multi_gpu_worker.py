@@ -4,7 +4,7 @@
         --master-port 29511 tests/multi_gpu_worker.py
 
 Each rank multiplies its row block (or batch block) through the sharded C-ABI entry points --
-NCCL slab exchange and the exchange fused into the GEMM epilogue (peer stores over NVLink) --
+NCCL slab exchange, the exchange fused into the GEMM epilogue (peer stores over NVLink) and the host-buffer form --
 then compares the gathered result with the same problem computed by this rank alone through
 sushi_cuda_sgemm.  Where both sides run the same tiles in the same order the results must be
 bit-identical; the fused case checks that all ranks hold identical bits and that they agree
@@ -121,6 +121,49 @@ def main():
                 ctx.ipc_close(opened[r])
         dist.barrier()
         ctx.free(c_mine)
+
+    # ---- host-buffer form: every rank uploads its rows of A and its share of B's k rows, the shares are exchanged
+    # device to device, C's rows come back to the rank's host.  Even and uneven partitions of m and of k, beta != 0,
+    # transposed A, and a transposed B (no exchange: every rank uploads all of it).
+    for (m, n, k, ta, tb, alpha, beta) in [(8192, 512, 1024, 0, 0, 1.0, 0.0), (4100, 256, 301, 0, 0, 1.5, 0.5),
+                                           (2048 * world, 384, 512, 1, 0, 1.0, 1.0), (3000, 320, 256, 0, 1, 1.0, 0.0)]:
+        a = full(41, k, m) if ta else full(41, m, k)
+        b = full(42, n, k) if tb else full(42, k, n)
+        c_in = full(43, m, n)
+        first, count = partition(m, world, rank)
+        rows = max(count, 1)
+        a_local = (a[:, first:first + rows] if ta else a[first:first + rows]).contiguous()
+        ha = a_local.cpu().pin_memory()
+        hb = torch.empty_like(b, device="cpu").pin_memory()
+        k0, kc = partition(k, world, rank)
+        if tb:
+            hb.copy_(b)                                      # stored n x k: goes up whole
+        else:
+            hb.fill_(float("nan"))                           # only this rank's share of the k rows is valid on its host
+            hb[k0:k0 + kc].copy_(b[k0:k0 + kc])
+        hc = c_in[first:first + rows].cpu().pin_memory()
+        da = torch.empty_like(a_local); db = torch.full_like(b, float("nan")); dc = torch.empty(rows, n, device=dev)
+        ctx.set_gemm_variant(2 if m >= 1024 else 1)
+        torch.cuda.synchronize(); dist.barrier()
+        ctx.sgemm_row_sharded_host(ta, tb, m, n, k, alpha, ha, rows if ta else k, hb, k if tb else n, beta, hc, n, da, db, dc)
+        c_one = c_in.clone()
+        ctx.sgemm(ta, tb, m, n, k, alpha, a, m if ta else k, b, k if tb else n, beta, c_one, n)
+        ctx.sync()
+        torch.cuda.synchronize()
+        if count:
+            want = c_one[first:first + count].cpu().numpy()
+            got = hc[:count].numpy()
+            diff = np.abs(got.astype(np.float64) - want)
+            opa = (a.t() if ta else a)[first:first + count]
+            opb = b.t() if tb else b
+            absab = (opa.abs().double() @ opb.abs().double()).cpu().numpy()
+            bound = 8.0 * k * 2.0 ** -24 * absab + 2.0 ** -23 * np.abs(beta * c_in[first:first + count].cpu().numpy().astype(np.float64))
+            if not np.all(diff <= bound):
+                failures.append(f"row_sharded_host m={m} n={n} k={k} ta={ta} tb={tb}: worst ratio to the bound "
+                                f"{float((diff / np.maximum(bound, 1e-300)).max())} on rank {rank}")
+        if not tb and not torch.equal(db, b):
+            failures.append(f"row_sharded_host m={m} k={k}: the exchanged B differs from the original on rank {rank}")
+        dist.barrier()
 
     # ---- batch-sharded strided-batched GEMM
     for (batch, m, n, k) in [(16, 256, 256, 192), (5, 64, 48, 32)]:

@@ -577,6 +577,40 @@ def test_host_entry_point_chunked_pipeline(ctx, ta, tb):
     assert r <= 1.0, (ta, tb, r)
 
 
+def test_row_sharded_host_entry_on_one_rank(ctx):
+    """The host-buffer form of the row-sharded GEMM without a communicator (one rank owns everything): B goes up
+    whole, A and C move in row chunks that overlap the multiplication.  Chunked and unchunked sizes, transposes,
+    beta != 0 (C goes up first) and a padded C."""
+    import ctypes
+
+    def pinned(arr):
+        ptr = ctx.host_alloc(arr.nbytes)
+        view = np.frombuffer((ctypes.c_float * arr.size).from_address(ptr), dtype=np.float32)
+        view[:] = arr.reshape(-1)
+        return ptr, view
+
+    for (m, n, k, ta, tb, alpha, beta, padc) in [(4608, 640, 520, 0, 0, 1.0, 0.0, 0), (4100, 384, 300, 1, 1, 1.5, 0.5, 0),
+                                                 (700, 200, 96, 0, 1, 1.0, 1.0, 3), (2304, 512, 256, 1, 0, 2.0, 0.0, 0)]:
+        cs = make_case(300 + m % 97, ta, tb, m, n, k, 1, pad=(0, 0, padc))
+        pa, ha = pinned(cs["a"]); pb, hb = pinned(cs["b"]); pc, hc = pinned(cs["c"])
+        da = torch.empty(cs["a"].size, device="cuda"); db = torch.empty(cs["b"].size, device="cuda")
+        dc = torch.full((cs["c"].size,), float("nan"), device="cuda")
+        ctx.set_gemm_variant(TC3X if m >= 1024 else AUTO)
+        ctx.sgemm_row_sharded_host(ta, tb, m, n, k, alpha, ha, cs["lda"], hb, cs["ldb"], beta, hc, cs["ldc"], da, db, dc)
+        ctx.sync()
+        ctx.set_gemm_variant(AUTO)
+        ref, absab = og.gemm_f64_np(ta, tb, m, n, k, alpha, cs["a"], cs["lda"], 0, cs["b"], cs["ldb"], 0, beta, cs["c"], cs["ldc"], 0, 1)
+        got = og._view(hc.copy(), m, n, cs["ldc"], 0, 1)
+        cin = og._view(cs["c"], m, n, cs["ldc"], 0, 1)
+        r, _ = og.tolerance_ratio(got, ref, absab, k, beta=beta, c_in=cin, budget=BUDGET)
+        assert r <= 1.0, (m, n, k, ta, tb, r)
+        if padc:                                             # the padding columns of the host C keep their contents
+            full = hc.reshape(m, cs["ldc"]); orig = cs["c"].reshape(m, cs["ldc"])
+            assert np.array_equal(full[:, n:], orig[:, n:])
+        for ptr in (pa, pb, pc):
+            ctx.host_free(ptr)
+
+
 def test_storage_calls_round_trip(ctx):
     nbytes = 1 << 20
     d = ctx.malloc(nbytes)
