@@ -454,26 +454,33 @@ class GemmProblem:
             self.first, self.count = partition(batch, h.world, h.rank)
             self.a = torch.empty(max(self.count, 1), m, k, device=dev)
             self.b = torch.empty(max(self.count, 1), k, n, device=dev)
-            self.c = torch.empty(batch, m, n, device=dev)
+            if h.world > 1 and gather == "fused":
+                self._register_peer_c(batch * m * n * 4)
+            else:
+                self.c = torch.empty(batch, m, n, device=dev)
         else:
             self.first, self.count = partition(m, h.world, h.rank) if self.shard == "rows" else (0, m)
             self.a = torch.empty(self.count, k, device=dev)          # square when transposed cases exist
             self.b = torch.empty(k, n, device=dev)
             if h.world > 1 and gather == "fused":
-                # C lives in a plain cudaMalloc block so that it can be mapped into the peers (CUDA IPC):
-                # the GEMM epilogue then stores finished tiles straight into every rank's C over NVLink
-                self.c_raw = ctx.malloc(m * n * 4)
-                handles = [None] * h.world
-                h.dist.all_gather_object(handles, ctx.ipc_export(self.c_raw))
-                self.opened = [ctx.ipc_open(handles[r]) if r != h.rank else None for r in range(h.world)]
-                ctx.comm_set_peer_buffers([self.c_raw if r == h.rank else self.opened[r] for r in range(h.world)], m * n * 4)
-                self.c = self.c_raw
-                self.gather_mode = 2
+                self._register_peer_c(m * n * 4)
             else:
                 self.c = torch.empty(m, n, device=dev)
         self.fill_inputs()
         self.fill_c()
         ctx.sync()
+
+    def _register_peer_c(self, nbytes):
+        """C lives in a plain cudaMalloc block so that it can be mapped into the peers (CUDA IPC): the GEMM
+        epilogue then stores finished tiles straight into every rank's C over NVLink."""
+        h, ctx = self.h, self.h.ctx
+        self.c_raw = ctx.malloc(nbytes)
+        handles = [None] * h.world
+        h.dist.all_gather_object(handles, ctx.ipc_export(self.c_raw))
+        self.opened = [ctx.ipc_open(handles[r]) if r != h.rank else None for r in range(h.world)]
+        ctx.comm_set_peer_buffers([self.c_raw if r == h.rank else self.opened[r] for r in range(h.world)], nbytes)
+        self.c = self.c_raw
+        self.gather_mode = 2
 
     # ---- inputs
     def _fill(self, t, dist_spec, seed, first_index):
@@ -507,7 +514,7 @@ class GemmProblem:
         m, n, k = w["m"], w["n"], w["k"]
         if self.shard == "batch":
             ctx.sgemm_batch_sharded(ta, tb, m, n, k, w["alpha"], self.a, k, m * k, self.b, n, k * n, w["beta"], self.c, n,
-                                    m * n, w["batch"], gather=self.h.world > 1)
+                                    m * n, w["batch"], gather=self.gather_mode if self.h.world > 1 else 0)
         elif self.shard == "rows":
             ctx.sgemm_row_sharded(ta, tb, m, n, k, w["alpha"], self.a, k, self.b, n, w["beta"], self.c, n,
                                   gather=self.gather_mode)

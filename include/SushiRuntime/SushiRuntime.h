@@ -405,7 +405,11 @@ namespace SushiRuntime
 
         /// One process per GPU: which rank this process is, how many there are, which CUDA device it
         /// drives, and a file through which rank 0 hands the 128-byte NCCL id to the others (any
-        /// path all ranks can read; it is created by rank 0 and may be deleted afterwards).
+        /// path all ranks can read).  Rank 0 writes the id followed by `job_token` (at most 63 characters)
+        /// and removes the file once every rank has joined; the other ranks accept a file only when its
+        /// token equals theirs, so a file left behind by an earlier job -- a crashed one, since a finished
+        /// one removes it -- is ignored as long as the jobs use different tokens (a launcher's job id, a
+        /// timestamp), and otherwise the wait for a matching file ends after `timeout_s`.
         struct DistributedConfig
         {
             int rank = 0;
@@ -413,6 +417,7 @@ namespace SushiRuntime
             int device = 0;
             std::string id_file;
             int timeout_s = 60;
+            std::string job_token;
         };
 
         /// Owns the device context.  Construction needs a CUDA device (sm_100a): there is no CPU
@@ -444,15 +449,21 @@ namespace SushiRuntime
                                                  sushi_cuda_last_error(nullptr));
                     allocator_ = make_sushi<detail::CudaAllocator>(ctx_);
                     if (cfg.nranks == 1) return;
-                    unsigned char id[128];
+                    // file image: 128 bytes of NCCL id, then the job token in 64 zero-padded bytes
+                    unsigned char image[192] = {0}, want_token[64] = {0};
+                    if (cfg.job_token.size() > 63) fail_plain("job_token is longer than 63 characters");
+                    std::memcpy(want_token, cfg.job_token.data(), cfg.job_token.size());
                     if (cfg.rank == 0)
                     {
-                        rc = sushi_cuda_comm_unique_id(id);
+                        rc = sushi_cuda_comm_unique_id(image);
                         if (rc != SUSHI_CUDA_OK) fail("cannot create the NCCL id");
+                        std::memcpy(image + 128, want_token, sizeof want_token);
+                        std::remove(cfg.id_file.c_str());          // whatever an earlier job left there
                         const std::string tmp = cfg.id_file + ".tmp";
                         std::FILE* f = std::fopen(tmp.c_str(), "wb");
-                        if (!f || std::fwrite(id, 1, sizeof id, f) != sizeof id) fail("cannot write the NCCL id file");
-                        std::fclose(f);
+                        const bool written = f && std::fwrite(image, 1, sizeof image, f) == sizeof image;
+                        if (f) std::fclose(f);
+                        if (!written) fail("cannot write the NCCL id file");
                         if (std::rename(tmp.c_str(), cfg.id_file.c_str()) != 0) fail("cannot publish the NCCL id file");
                     }
                     else
@@ -464,15 +475,32 @@ namespace SushiRuntime
                         {
                             if (std::FILE* f = std::fopen(cfg.id_file.c_str(), "rb"))
                             {
-                                got = std::fread(id, 1, sizeof id, f) == sizeof id;
+                                got = std::fread(image, 1, sizeof image, f) == sizeof image &&
+                                      std::memcmp(image + 128, want_token, sizeof want_token) == 0;
                                 std::fclose(f);
                             }
                             if (!got) std::this_thread::sleep_for(std::chrono::milliseconds(20));
                         }
-                        if (!got) fail("timed out waiting for the NCCL id file of rank 0");
+                        if (!got) fail_plain("timed out waiting for the NCCL id file of rank 0 (none, or none with this job's token)");
                     }
-                    rc = sushi_cuda_comm_init_rank(ctx_, 0, id, cfg.nranks, cfg.rank);
+                    rc = sushi_cuda_comm_init_rank(ctx_, 0, image, cfg.nranks, cfg.rank);
                     if (rc != SUSHI_CUDA_OK) fail("cannot join the NCCL communicator");
+                    // the communicator exists on every rank, so every rank has read the file
+                    if (cfg.rank == 0) std::remove(cfg.id_file.c_str());
+                }
+
+                /// Host half of the rendezvous alone (no device): true when `path` holds an id image whose
+                /// token equals `job_token`.  What the waiting ranks test; exposed for host-only tests.
+                static bool id_file_matches(const std::string& path, const std::string& job_token)
+                {
+                    unsigned char image[192] = {0}, want[64] = {0};
+                    if (job_token.size() > 63) return false;
+                    std::memcpy(want, job_token.data(), job_token.size());
+                    std::FILE* f = std::fopen(path.c_str(), "rb");
+                    if (!f) return false;
+                    const bool ok = std::fread(image, 1, sizeof image, f) == sizeof image && std::memcmp(image + 128, want, sizeof want) == 0;
+                    std::fclose(f);
+                    return ok;
                 }
 
                 int rank() const { return rank_; }
@@ -515,6 +543,14 @@ namespace SushiRuntime
                     if (ctx_) sushi_cuda_destroy(ctx_);
                     ctx_ = nullptr;
                     throw std::runtime_error(msg);
+                }
+                /// Same for failures of the host-side protocol (no library error text to append).
+                [[noreturn]] void fail_plain(const char* what)
+                {
+                    allocator_.reset();
+                    if (ctx_) sushi_cuda_destroy(ctx_);
+                    ctx_ = nullptr;
+                    throw std::runtime_error(std::string("RuntimeContext: ") + what);
                 }
                 sushi_cuda_ctx* ctx_ = nullptr;
                 sushi_ptr<Memory::USMAllocator> allocator_;

@@ -391,7 +391,11 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded_host(sushi_cuda_ctx* ctx, int de
 
 /* Batch-index sharded strided-batched GEMM: the rank owns batches [first, first+count) of
  * the global `batch`; a_local / b_local point at its first owned batch; c_full is the whole
- * batch x m x n result (contiguous: ldc == n, stride_c == m*n is required when gather != 0). */
+ * batch x m x n result (contiguous: ldc == n, stride_c == m*n is required when gather != 0).
+ * gather == 1: one in-place NCCL all-gather of the batch blocks after the GEMM.  gather == 2: the exchange is
+ * fused into the GEMM epilogue (peer stores over NVLink between two 4-byte all-reduce barriers), under the
+ * conditions of the row-sharded form: registered peer buffers with c_full this rank's own, n % 4 == 0 and the
+ * tensor path suiting the largest and the last batch block; otherwise the call runs gather == 1.            */
 SUSHI_CUDA_API int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                                   int64_t m, int64_t n, int64_t k, float alpha,
                                                   const float* a_local, int64_t lda, int64_t stride_a,

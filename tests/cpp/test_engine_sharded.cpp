@@ -13,7 +13,7 @@ static std::string g_id_file;
 
 static sr::Execution::RuntimeContext& runtime()
 {
-    static sr::Execution::DistributedConfig cfg{g_rank, g_nranks, g_rank, g_id_file, 60};
+    static sr::Execution::DistributedConfig cfg{g_rank, g_nranks, g_rank, g_id_file, 60, "test_engine_sharded"};
     static sr::Execution::RuntimeContext ctx(cfg);
     return ctx;
 }

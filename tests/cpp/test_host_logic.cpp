@@ -8,6 +8,7 @@
 #include <fstream>
 #include <iterator>
 #include <vector>
+#include <unistd.h>
 #include <SushiBLAS/SushiBLAS.h>
 #include "check.hpp"
 
@@ -264,6 +265,35 @@ TEST_CASE(runtime_context_fails_loudly_without_a_device)
     int count = 0;
     if (sushi_cuda_device_count(&count) == SUSHI_CUDA_OK && count > 0) return;     // a GPU is present
     EXPECT_THROWS(sr::Execution::RuntimeContext ctx, "cannot create the CUDA context");
+}
+
+TEST_CASE(nccl_id_file_of_another_job_is_not_accepted)
+{
+    // host half of the multi-GPU rendezvous: a waiting rank takes the id file only when it carries its job's token,
+    // so what an earlier (crashed) job left at the same path is ignored
+    const std::string path = "/tmp/sushiblas_host_logic_id_" + std::to_string(::getpid()) + ".bin";
+    std::remove(path.c_str());
+    EXPECT_TRUE(!sr::Execution::RuntimeContext::id_file_matches(path, "job-2"));          // no file
+    {
+        unsigned char image[192] = {0};
+        std::memcpy(image + 128, "job-1", 5);
+        std::FILE* f = std::fopen(path.c_str(), "wb");
+        EXPECT_TRUE(f != nullptr);
+        std::fwrite(image, 1, sizeof image, f);
+        std::fclose(f);
+    }
+    EXPECT_TRUE(sr::Execution::RuntimeContext::id_file_matches(path, "job-1"));
+    EXPECT_TRUE(!sr::Execution::RuntimeContext::id_file_matches(path, "job-2"));          // stale: another job's token
+    EXPECT_TRUE(!sr::Execution::RuntimeContext::id_file_matches(path, ""));
+    {
+        std::FILE* f = std::fopen(path.c_str(), "wb");                                    // a bare 128-byte id: too short
+        unsigned char id[128] = {0};
+        std::fwrite(id, 1, sizeof id, f);
+        std::fclose(f);
+    }
+    EXPECT_TRUE(!sr::Execution::RuntimeContext::id_file_matches(path, ""));
+    EXPECT_TRUE(!sr::Execution::RuntimeContext::id_file_matches(path, std::string(64, 'x')));   // token too long
+    std::remove(path.c_str());
 }
 
 int main() { return check::run_all(); }

@@ -181,6 +181,42 @@ def main():
         torch.cuda.synchronize()
         compare(c_shard.cpu().numpy(), c_one.cpu().numpy(), k, 1.0, 0.0, f"batch_sharded batch={batch} m={m}")
 
+    # ---- batch-sharded GEMM with the exchange fused into the epilogue (peer stores): even and uneven batch counts,
+    # fewer batches than ranks, beta != 0
+    for (batch, m, n, k, alpha, beta) in [(4 * world, 512, 512, 256, 1.0, 0.0), (4 * world + 1, 256, 512, 384, 1.5, 0.5),
+                                          (world - 1, 512, 256, 128, 1.0, 0.0)]:
+        nbytes = batch * m * n * 4
+        c_mine = ctx.malloc(nbytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, ctx.ipc_export(c_mine))
+        opened = [ctx.ipc_open(handles[r]) if r != rank else None for r in range(world)]
+        ctx.comm_set_peer_buffers([c_mine if r == rank else opened[r] for r in range(world)], nbytes)
+        a = full(51, batch * m, k).view(batch, m, k); b = full(52, batch * k, n).view(batch, k, n); c_in = full(53, batch * m, n)
+        first, count = partition(batch, world, rank)
+        ctx.set_gemm_variant(2)
+        a_local = a[first:first + count].contiguous() if count else a[:1].contiguous()
+        b_local = b[first:first + count].contiguous() if count else b[:1].contiguous()
+        for _ in range(2):
+            ctx.memcpy_d2d(c_mine, c_in, nbytes)
+            ctx.sync(); dist.barrier()
+            ctx.sgemm_batch_sharded(0, 0, m, n, k, alpha, a_local, k, m * k, b_local, n, k * n, beta, c_mine, n, m * n, batch, gather=2)
+        c_one = c_in.clone()
+        ctx.sgemm_strided_batched(0, 0, m, n, k, alpha, a, k, m * k, b, n, k * n, beta, c_one, n, m * n, batch)
+        got = np.empty((batch * m, n), dtype=np.float32)
+        ctx.memcpy_d2h(got, c_mine, nbytes)
+        ctx.sync()
+        torch.cuda.synchronize()
+        absab = torch.bmm(a.abs().double(), b.abs().double()).reshape(batch * m, n).cpu().numpy()
+        compare(got, c_one.cpu().numpy(), k, alpha, beta, f"fused batch gather batch={batch} m={m} n={n} k={k}", absab=absab,
+                c_in=c_in.cpu().numpy())
+        dist.barrier()
+        ctx.comm_set_peer_buffers([], 0)
+        for r in range(world):
+            if r != rank:
+                ctx.ipc_close(opened[r])
+        dist.barrier()
+        ctx.free(c_mine)
+
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     for f in failures:
