@@ -70,7 +70,15 @@ constexpr int PLANE_BYTES = 256 * BK * 4;             // one 256-row plane of on
 constexpr int OPERAND_BYTES = 2 * PLANE_BYTES;        // hi + lo: 32 KB
 constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;        // A + B: 64 KB
 constexpr int EPI_WARPS = 8;
-constexpr int THREADS = 64 + EPI_WARPS * 32;          // 320
+constexpr int THREADS = 64 + EPI_WARPS * 32;          // 320: launches whose operands are all pre-split planes
+// Launches with a raw operand add eight converter warps and lay the roles out by warpgroup (four warps) so that
+// setmaxnreg can move registers between them: warps 0..3 producer, MMA issuer and two idle, 4..11 epilogue, 12..19
+// converters.  The pool that setmaxnreg trades within is what the CTA was launched with (640 x 96), not the
+// register file: an increase that the decreases do not cover would wait for ever.
+constexpr int THREADS_RAW = 640;
+constexpr int CONV_WARP0 = 12;
+constexpr int REGS_COMPILED_RAW = 96, REGS_CTRL = 32, REGS_EPI = 152, REGS_CONV = 72;
+static_assert(128 * REGS_CTRL + 256 * REGS_EPI + 256 * REGS_CONV <= THREADS_RAW * REGS_COMPILED_RAW, "setmaxnreg pool");
 constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;          // per epilogue warp: 32 rows x 32 cols
 constexpr int SMEM_CTRL_BYTES = 256;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + SMEM_CTRL_BYTES + 1024;
@@ -438,11 +446,15 @@ __device__ __forceinline__ void epilogue_fast(uint32_t taddr0, float4* stg, floa
 
 // PRODUCTS: 3 issues lo*hi + hi*lo + hi*hi per k-step (fp32 accuracy); 1 only hi*hi (rate probe, TF32 accuracy).  A
 // compile-time choice: the MMA-issuing thread is on the critical path and a run-time test in its loop costs 7 %.
-template <int PRODUCTS>
-__global__ void __launch_bounds__(THREADS, 1)
+// RAW: the launch has at least one raw operand (640 threads, dedicated converter warps); otherwise 320 threads.
+template <int REGS> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
+template <int REGS> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
+
+template <int PRODUCTS, bool RAW>
+__global__ void __launch_bounds__(RAW ? THREADS_RAW : THREADS, 1)
 sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap raw_a, const __grid_constant__ CUtensorMap raw_b,
-                  const Params p)
+                  const __grid_constant__ Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment keeps every plane base on a swizzle-pattern boundary
@@ -491,9 +503,16 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     const int32_t cta = (int32_t)blockIdx.x, grid = (int32_t)gridDim.x;
+    constexpr int EPI_WARP0 = RAW ? 4 : 2;       // first epilogue warp (warp & 3 is the TMEM lane quarter either way)
 
-    if (warp == 0)
+    // With a raw operand every branch below starts with its warpgroup's setmaxnreg (all four warps of a group run it).
+    if (RAW && warp >= 2 && warp < 4)
     {
+        reg_dec<REGS_CTRL>();                    // the two idle warps of the control group
+    }
+    else if (warp == 0)
+    {
+        if (RAW) reg_dec<REGS_CTRL>();
         // ------------------------------------------------------------ TMA producer
         uint32_t it = 0;
         bool ok = true;
@@ -553,6 +572,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     else if (warp == 1)
     {
+        if (RAW) reg_dec<REGS_CTRL>();
         // ------------------------------------------------------------ MMA issuer
         uint32_t it = 0, tl = 0;
         bool ok = true;
@@ -623,16 +643,90 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         __syncwarp();
     }
-    else
+    else if (RAW && warp >= CONV_WARP0)
     {
+        reg_dec<REGS_CONV>();
+        // ------------------------------------------------------------ converter warps (launches with a raw operand)
+        // Split the raw operand tiles of every stage in place: hi = rna_tf32(x) over the raw values, lo beside it.
+        const int ew = warp - CONV_WARP0;        // 0..7: the 32 rows of a tile this warp converts
+        const int te = ew * 32 + lane;           // 0..255
+        uint32_t it = 0;
+        bool ok = true;
+        WorkItem w;
+        for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
+        {
+            {
+                const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+                if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
+            }
+            for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
+            {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                const int okc = mbar_wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_CONVERT, WAIT_LIMIT_NS);
+                ok = __all_sync(0xffffffffu, okc) != 0;
+                if (!ok) break;
+                uint8_t* stage = stage_base + s * STAGE_BYTES;
+#pragma unroll
+                for (int op = 0; op < 2; ++op)
+                {
+                    if (!((p.raw_mask >> op) & 1)) continue;
+                    float4* hi = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES);
+                    float4* lo = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES + PLANE_BYTES);
+                    if ((p.raw_mask >> (op + 2)) & 1)
+                    {
+                        // Row-contiguous operand: this warp's 32 rows arrived as [16 k][32 rows] in the 2 KB of
+                        // the lo slot that hold these rows' lo values afterwards, so reading before writing is
+                        // a matter of this warp alone.  A lane takes one row: 16 conflict-free loads, then the
+                        // row's 64 bytes of hi and of lo in the MMA's K-major layout (16-byte chunk c of row r
+                        // at position c ^ ((r >> 1) & 3): SWIZZLE_64B).
+                        const float* raw = reinterpret_cast<const float*>(lo) + ew * (32 * BK);
+                        float x[BK];
+#pragma unroll
+                        for (int kk = 0; kk < BK; ++kk) x[kk] = raw[kk * 32 + lane];
+                        __syncwarp();
+                        const int r = ew * 32 + lane;
+#pragma unroll
+                        for (int c = 0; c < BK / 4; ++c)
+                        {
+                            float4 h4, l4;
+                            split_tf32_1(x[4 * c + 0], h4.x, l4.x); split_tf32_1(x[4 * c + 1], h4.y, l4.y);
+                            split_tf32_1(x[4 * c + 2], h4.z, l4.z); split_tf32_1(x[4 * c + 3], h4.w, l4.w);
+                            const int pos = r * (BK / 4) + (c ^ ((r >> 1) & 3));
+                            hi[pos] = h4;
+                            lo[pos] = l4;
+                        }
+                        continue;
+                    }
+#pragma unroll
+                    for (int j = 0; j < PLANE_BYTES / 16 / (EPI_WARPS * 32); ++j)
+                    {
+                        const int e = te + j * (EPI_WARPS * 32);
+                        const float4 x = hi[e];
+                        float4 h4, l4;
+                        split_tf32_1(x.x, h4.x, l4.x); split_tf32_1(x.y, h4.y, l4.y);
+                        split_tf32_1(x.z, h4.z, l4.z); split_tf32_1(x.w, h4.w, l4.w);
+                        hi[e] = h4;
+                        lo[e] = l4;
+                    }
+                }
+                // generic-proxy writes must be visible to the tensor core's async-proxy reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(conv0 + 8 * s);
+            }
+        }
+    }
+    else if (warp >= EPI_WARP0 && warp < EPI_WARP0 + EPI_WARPS)
+    {
+        if (RAW) reg_inc<REGS_EPI>();
         // ------------------------------------------------------------ epilogue warps
-        const int ew = warp - 2;                 // 0..7
+        const int ew = warp - EPI_WARP0;         // 0..7
         const int h = ew >> 2;                   // accumulator half (rows h*128 ..)
         const int q = warp & 3;                  // TMEM lane quarter this warp may access
         float4* stg = reinterpret_cast<float4*>(epi_base + ew * EPI_STAGE_BYTES);   // [32 rows][8 float4]
         const bool has_beta = (p.beta != 0.0f);
         const int rsub = lane >> 3, c4 = lane & 7;
-        uint32_t tl = 0, published = 0, it = 0;
+        uint32_t tl = 0, published = 0;
         bool ok = true;
         WorkItem w;
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
@@ -640,67 +734,6 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
             if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
             const uint32_t tl_now = tl++;
-            if (p.raw_mask)
-            {
-                // converter duty: split the raw operand tiles of every stage of this run in place
-                const int te = ew * 32 + lane;                       // 0..255
-                for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
-                {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    const int okc = mbar_wait_bounded(full0 + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_CONVERT, WAIT_LIMIT_NS);
-                    ok = __all_sync(0xffffffffu, okc) != 0;
-                    if (!ok) break;
-                    uint8_t* stage = stage_base + s * STAGE_BYTES;
-#pragma unroll
-                    for (int op = 0; op < 2; ++op)
-                    {
-                        if (!((p.raw_mask >> op) & 1)) continue;
-                        float4* hi = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES);
-                        float4* lo = reinterpret_cast<float4*>(stage + op * OPERAND_BYTES + PLANE_BYTES);
-                        if ((p.raw_mask >> (op + 2)) & 1)
-                        {
-                            // Row-contiguous operand: this warp's 32 rows arrived as [16 k][32 rows] in the 2 KB of
-                            // the lo slot that hold these rows' lo values afterwards, so reading before writing is
-                            // a matter of this warp alone.  A lane takes one row: 16 conflict-free loads, then the
-                            // row's 64 bytes of hi and of lo in the MMA's K-major layout (16-byte chunk c of row r
-                            // at position c ^ ((r >> 1) & 3): SWIZZLE_64B).
-                            const float* raw = reinterpret_cast<const float*>(lo) + ew * (32 * BK);
-                            float x[BK];
-#pragma unroll
-                            for (int kk = 0; kk < BK; ++kk) x[kk] = raw[kk * 32 + lane];
-                            __syncwarp();
-                            const int r = ew * 32 + lane;
-#pragma unroll
-                            for (int c = 0; c < BK / 4; ++c)
-                            {
-                                float4 h4, l4;
-                                split_tf32_1(x[4 * c + 0], h4.x, l4.x); split_tf32_1(x[4 * c + 1], h4.y, l4.y);
-                                split_tf32_1(x[4 * c + 2], h4.z, l4.z); split_tf32_1(x[4 * c + 3], h4.w, l4.w);
-                                const int pos = r * (BK / 4) + (c ^ ((r >> 1) & 3));
-                                hi[pos] = h4;
-                                lo[pos] = l4;
-                            }
-                            continue;
-                        }
-#pragma unroll
-                        for (int j = 0; j < PLANE_BYTES / 16 / (EPI_WARPS * 32); ++j)
-                        {
-                            const int e = te + j * (EPI_WARPS * 32);
-                            const float4 x = hi[e];
-                            float4 h4, l4;
-                            split_tf32_1(x.x, h4.x, l4.x); split_tf32_1(x.y, h4.y, l4.y);
-                            split_tf32_1(x.z, h4.z, l4.z); split_tf32_1(x.w, h4.w, l4.w);
-                            hi[e] = h4;
-                            lo[e] = l4;
-                        }
-                    }
-                    // generic-proxy writes must be visible to the tensor core's async-proxy reads
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(conv0 + 8 * s);
-                }
-                if (!ok) break;
-            }
             int okl = mbar_wait_bounded(acc_full, tl_now & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
             if (okl && w.kind == 2)
             {
@@ -1204,10 +1237,13 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
                                      float act_param = 0.0f, int products = 3)
 {
     // per-device attribute; cheap enough to set on every launch
+    const bool any_raw = a.raw != nullptr || b.raw != nullptr;
     cudaError_t e = products == 1
-        ? cudaFuncSetAttribute(sgemm_tc3x_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)
-        : cudaFuncSetAttribute(sgemm_tc3x_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        ? cudaFuncSetAttribute(sgemm_tc3x_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)
+        : any_raw ? cudaFuncSetAttribute(sgemm_tc3x_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)
+                  : cudaFuncSetAttribute(sgemm_tc3x_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    if (products == 1 && any_raw) return cudaErrorInvalidValue;       // the rate probe runs over planes only
     const int64_t m_pad = (m + 255) / 256 * 256, n_pad = (n + 255) / 256 * 256;
     const int64_t num_kb = (k + BK - 1) / BK;
     CUtensorMap map_a, map_b, raw_a, raw_b;
@@ -1234,8 +1270,9 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.sk_partials = sk_area ? reinterpret_cast<float*>(static_cast<char*>(sk_area) + SK_FLAG_BYTES) : nullptr;
     p.sk_epoch = sk_epoch;
     if (plan.grid <= 0) return cudaSuccess;
-    if (products == 1) sgemm_tc3x_kernel<1><<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
-    else sgemm_tc3x_kernel<3><<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
+    if (products == 1) sgemm_tc3x_kernel<1, false><<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
+    else if (any_raw) sgemm_tc3x_kernel<3, true><<<(unsigned)plan.grid, THREADS_RAW, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
+    else sgemm_tc3x_kernel<3, false><<<(unsigned)plan.grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, raw_a, raw_b, p);
     return cudaGetLastError();
 }
 
