@@ -396,6 +396,11 @@ SUSHI_CUDA_API int sushi_cuda_sgemm_row_sharded_host(sushi_cuda_ctx* ctx, int de
  * fused into the GEMM epilogue (peer stores over NVLink between two 4-byte all-reduce barriers), under the
  * conditions of the row-sharded form: registered peer buffers with c_full this rank's own, n % 4 == 0 and the
  * tensor path suiting the largest and the last batch block; otherwise the call runs gather == 1.            */
+/* Which exchange sushi_cuda_sgemm_batch_sharded runs: 0 none, 1 NCCL all-gather, 2 peer stores fused into the GEMM
+ * epilogue -- like sushi_cuda_row_sharded_exchange, pure host arithmetic over what every rank knows.            */
+SUSHI_CUDA_API int sushi_cuda_batch_sharded_exchange(int64_t m, int64_t n, int64_t k, int64_t batch, int nranks, int variant,
+                                                     int sm_count, int gather, int* exchange);
+
 SUSHI_CUDA_API int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                                   int64_t m, int64_t n, int64_t k, float alpha,
                                                   const float* a_local, int64_t lda, int64_t stride_a,

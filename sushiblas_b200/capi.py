@@ -90,6 +90,7 @@ SIGNATURES = {
     "sushi_cuda_ipc_close": (_int, [_vp, _int, _vp]),
     "sushi_cuda_comm_set_peer_buffers": (_int, [_vp, _int, ctypes.POINTER(_vp), _int, _sz]),
     "sushi_cuda_row_sharded_exchange": (_int, [_i64, _i64, _i64, _int, _int, _int, _int, ctypes.POINTER(_int)]),
+    "sushi_cuda_batch_sharded_exchange": (_int, [_i64, _i64, _i64, _i64, _int, _int, _int, _int, ctypes.POINTER(_int)]),
     "sushi_cuda_sgemm_row_sharded": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
                                             _f32, _vp, _i64, _int]),
     "sushi_cuda_sgemm_row_sharded_host": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
@@ -138,6 +139,17 @@ def partition(total: int, nranks: int, rank: int):
     if rc != 0:
         raise SushiCudaError(rc, lib.sushi_cuda_last_error(None).decode())
     return first.value, count.value
+
+
+def batch_sharded_exchange(m: int, n: int, k: int, batch: int, nranks: int, variant: int = GEMM_AUTO, sm_count: int = 148,
+                           gather: int = 2) -> int:
+    """0 none, 1 NCCL all-gather, 2 fused peer stores (pure host arithmetic over rank-independent quantities)."""
+    lib = load_library()
+    out = _int()
+    rc = lib.sushi_cuda_batch_sharded_exchange(m, n, k, batch, nranks, variant, sm_count, gather, ctypes.byref(out))
+    if rc != 0:
+        raise SushiCudaError(rc, lib.sushi_cuda_last_error(None).decode())
+    return out.value
 
 
 def row_sharded_exchange(m: int, n: int, k: int, nranks: int, variant: int = GEMM_AUTO, sm_count: int = 148,

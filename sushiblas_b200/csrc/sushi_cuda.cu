@@ -1452,6 +1452,26 @@ extern "C" int sushi_cuda_row_sharded_exchange(int64_t m, int64_t n, int64_t k, 
     return SUSHI_CUDA_OK;
 }
 
+extern "C" int sushi_cuda_batch_sharded_exchange(int64_t m, int64_t n, int64_t k, int64_t batch, int nranks, int variant,
+                                                 int sm_count, int gather, int* exchange)
+{
+    if (!exchange || m < 0 || n < 0 || k < 0 || batch < 0 || nranks < 1 || sm_count < 1)
+        return set_error(nullptr, SUSHI_CUDA_ERR_INVALID_ARG, "batch_sharded_exchange: bad argument");
+    *exchange = 0;
+    if (gather == 0 || nranks == 1) return SUSHI_CUDA_OK;
+    *exchange = 1;
+    if (gather != 2 || (n & 3) != 0 || m == 0 || batch == 0) return SUSHI_CUDA_OK;
+    // the two block sizes that occur: ceil(batch / nranks) and the shorter block of the last rank that owns entries
+    const int64_t block = (batch + nranks - 1) / nranks;
+    const int64_t nonempty = (batch + block - 1) / block;
+    const int64_t last = batch - (nonempty - 1) * block;
+    auto tensor_for = [&](int64_t cnt) {
+        return cnt > 0 && k >= 4 && (variant == SUSHI_GEMM_TC3X || (variant == SUSHI_GEMM_AUTO && prefer_tc3x(m, n, k, cnt, sm_count)));
+    };
+    if (tensor_for(block) && tensor_for(last)) *exchange = 2;
+    return SUSHI_CUDA_OK;
+}
+
 extern "C" int sushi_cuda_sgemm_row_sharded(sushi_cuda_ctx* ctx, int dev, int trans_a, int trans_b,
                                             int64_t m, int64_t n, int64_t k, float alpha,
                                             const float* a_local, int64_t lda,
@@ -1679,38 +1699,32 @@ extern "C" int sushi_cuda_sgemm_batch_sharded(sushi_cuda_ctx* ctx, int dev, int 
     // Fused exchange (gather == 2): the epilogue of this rank's GEMM stores its finished tiles into every peer's
     // buffer, as in the row-sharded form (a batch entry is addressed like a row block: bi * stride_c).  Whether it runs
     // is decided from quantities all ranks share -- the largest and the last batch block -- never from this rank's own.
-    if (do_gather && gather == 2 && !ctx->peer_buffers.empty())
+    int exchange = 0;
+    sushi_cuda_batch_sharded_exchange(m, n, k, batch, nranks, ctx->variant, d->sm_count, gather, &exchange);
+    if (do_gather && exchange == 2 && !ctx->peer_buffers.empty())
     {
-        const int64_t block = (batch + nranks - 1) / nranks, last = batch - (int64_t)(nranks - 1) * block;
-        auto tensor_for = [&](int64_t cnt) {
-            return cnt > 0 && k >= 4 && (ctx->variant == SUSHI_GEMM_TC3X ||
-                                         (ctx->variant == SUSHI_GEMM_AUTO && prefer_tc3x(m, n, k, cnt, d->sm_count)));
-        };
-        if ((n % 4) == 0 && tensor_for(block) && (last <= 0 || tensor_for(last)))
+        if ((int)ctx->peer_buffers.size() != nranks || ctx->peer_buffers[rank] != c_full ||
+            (reinterpret_cast<uintptr_t>(c_full) & 15) != 0 ||
+            (size_t)batch * (size_t)m * (size_t)n * sizeof(float) > ctx->peer_bytes)
+            return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG,
+                             "sgemm_batch_sharded: gather == 2 needs c_full to be this rank's registered buffer "
+                             "(sushi_cuda_comm_set_peer_buffers), 16-byte aligned and at least batch*m*n*4 bytes");
+        SC_CUDA(ctx, cudaSetDevice(d->device));
+        // barrier 1: every rank has reached this call, so nobody still reads the previous C
+        SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
+        if (count > 0)
         {
-            if ((int)ctx->peer_buffers.size() != nranks || ctx->peer_buffers[rank] != c_full ||
-                (reinterpret_cast<uintptr_t>(c_full) & 15) != 0 ||
-                (size_t)batch * (size_t)m * (size_t)n * sizeof(float) > ctx->peer_bytes)
-                return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG,
-                                 "sgemm_batch_sharded: gather == 2 needs c_full to be this rank's registered buffer "
-                                 "(sushi_cuda_comm_set_peer_buffers), 16-byte aligned and at least batch*m*n*4 bytes");
-            SC_CUDA(ctx, cudaSetDevice(d->device));
-            // barrier 1: every rank has reached this call, so nobody still reads the previous C
-            SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
-            if (count > 0)
-            {
-                SlabReuse fused;
-                fused.variant = SUSHI_GEMM_TC3X;
-                for (int r = 0; r < nranks; ++r)
-                    if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * stride_c;
-                rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a_local, lda, stride_a, b_local, ldb, stride_b, beta,
-                              c_full + first * stride_c, ldc, stride_c, count, &fused);
-                if (rc != SUSHI_CUDA_OK) return rc;
-            }
-            // barrier 2: every rank's kernel (and with it its stores into this rank's buffer) is complete
-            SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
-            return SUSHI_CUDA_OK;
+            SlabReuse fused;
+            fused.variant = SUSHI_GEMM_TC3X;
+            for (int r = 0; r < nranks; ++r)
+                if (r != rank) fused.peer_c[fused.n_peers++] = static_cast<float*>(ctx->peer_buffers[r]) + first * stride_c;
+            rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a_local, lda, stride_a, b_local, ldb, stride_b, beta,
+                          c_full + first * stride_c, ldc, stride_c, count, &fused);
+            if (rc != SUSHI_CUDA_OK) return rc;
         }
+        // barrier 2: every rank's kernel (and with it its stores into this rank's buffer) is complete
+        SC_NCCL(ctx, g_nccl.AllReduce(ctx->barrier_word, ctx->barrier_word, 1, NCCL_FLOAT32, 0, ctx->comm, d->stream));
+        return SUSHI_CUDA_OK;
     }
     rc = run_gemm(ctx, *d, trans_a, trans_b, m, n, k, alpha, a_local, lda, stride_a, b_local, ldb, stride_b, beta,
                   c_full + first * stride_c, ldc, stride_c, count);

@@ -131,3 +131,22 @@ def test_row_sharded_exchange_is_decided_without_the_rank(lib_path):
     assert row_sharded_exchange(4096, 512, 3, 2, GEMM_TC3X) == 1
     assert row_sharded_exchange(4096, 510, 512, 2, GEMM_TC3X) == 1
     assert row_sharded_exchange(0, 512, 512, 2, GEMM_TC3X) == 1
+
+
+def test_batch_sharded_exchange_is_decided_without_the_rank(lib_path):
+    """Same rule for the batch-sharded form: the fused exchange is chosen from the largest and the last batch
+    block, so ranks with fewer (or no) entries issue the same collectives as the others."""
+    from sushiblas_b200.capi import batch_sharded_exchange, partition, GEMM_AUTO, GEMM_SIMT, GEMM_TC3X
+    for g in (2, 4, 8):
+        assert batch_sharded_exchange(512, 512, 512, 256, g) == 2           # the batched configuration
+    assert batch_sharded_exchange(512, 512, 512, 256, 1) == 0
+    assert batch_sharded_exchange(512, 512, 512, 256, 8, gather=0) == 0
+    assert batch_sharded_exchange(512, 512, 512, 256, 8, gather=1) == 1
+    # fewer entries than ranks under the forced tensor path: trailing ranks own nothing, everybody fused
+    assert [partition(3, 4, r)[1] for r in range(4)] == [1, 1, 1, 0]
+    assert batch_sharded_exchange(512, 256, 128, 3, 4, GEMM_TC3X) == 2
+    assert batch_sharded_exchange(512, 256, 128, 3, 4, GEMM_SIMT) == 1
+    # tiny entries under AUTO go to the FFMA kernel on every rank: no peer stores anywhere
+    assert batch_sharded_exchange(32, 32, 32, 5, 2, GEMM_AUTO) == 1
+    assert batch_sharded_exchange(512, 510, 512, 8, 2, GEMM_TC3X) == 1      # n must allow 128-bit peer stores
+    assert batch_sharded_exchange(512, 512, 3, 8, 2, GEMM_TC3X) == 1        # K < 4 never runs on the tensor path
