@@ -346,7 +346,7 @@ namespace SushiRuntime
                             {
                                 if (!b.mirror) status = sushi_cuda_malloc(ctx_, 0, b.bytes, &b.mirror);
                                 // the mirror is current when the device wrote it last (host image stale) or
-                                // when it was brought up in this round
+                                // when it was brought up in the current execute() round
                                 if (status == SUSHI_CUDA_OK && contents && !b.host_stale && b.valid_round != round_)
                                     status = sushi_cuda_memcpy_h2d(ctx_, 0, b.mirror, ptr, b.bytes);
                                 if (status == SUSHI_CUDA_OK)
