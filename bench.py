@@ -777,15 +777,19 @@ def measure_e2e(h: Harness, prob: GemmProblem, np):
         steps, warm = 5, 2
     elif prob.shard == "rows":
         rows = prob.count
-        pa, ha = pinned(max(rows, 1) * k); pb, hb = pinned(k * n); pc, hc = pinned(max(rows, 1) * n)
-        ctx.memcpy_d2h(ha, prob.a, ha.nbytes); ctx.memcpy_d2h(hb, prob.b, hb.nbytes)
+        # every rank uploads its rows of A and its share of B's k rows (the rest of B arrives over NVLink) and
+        # reads its rows of C back; the device buffers of the device-timed run serve as the call's scratch.  Only
+        # the rank's share of B exists on its host: the call is given the address the whole B would start at.
+        b_first, b_rows = partition(k, h.world, h.rank)
+        pa, ha = pinned(max(rows, 1) * k); pb, hb = pinned(max(b_rows, 1) * n); pc, hc = pinned(max(rows, 1) * n)
+        ctx.memcpy_d2h(ha, prob.a, ha.nbytes)
+        ctx.memcpy_d2h(hb, _addr(prob.b) + b_first * n * 4, b_rows * n * 4)
         ctx.sync()
         c_block = _addr(prob.c) + prob.first * n * 4
-        # every rank uploads its rows of A and its share of B's k rows (the rest of B arrives over NVLink) and
-        # reads its rows of C back; the device buffers of the device-timed run serve as the call's scratch
+        b_host = pb - b_first * n * 4
+
         def step():
-            ctx.sgemm_row_sharded_host(0, 0, m, n, k, alpha, ha, k, hb, n, beta, hc, n, prob.a, prob.b, c_block)
-        _, b_rows = partition(k, h.world, h.rank)
+            ctx.sgemm_row_sharded_host(0, 0, m, n, k, alpha, ha, k, b_host, n, beta, hc, n, prob.a, prob.b, c_block)
         h2d, d2h = ha.nbytes + b_rows * n * 4 + (hc.nbytes if beta != 0 else 0), hc.nbytes
         api = "sushi_cuda_sgemm_row_sharded_host (each rank's host receives its rows of C)"
         steps, warm = (3, 1) if m * n * k > 1e12 else (5, 2)
