@@ -42,7 +42,7 @@ struct DeviceState
     int* status_host = nullptr;           // pinned mirror
     // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
-    cudaEvent_t pipe_events[10] = {};
+    cudaEvent_t pipe_events[18] = {};
     void* trsm_buf = nullptr;             // TRSM: inverted diagonal blocks + one block row/column of temporaries
     size_t trsm_bytes = 0;
     void* group_buf = nullptr;            // device copy of the grouped-launch problem list
@@ -1595,48 +1595,85 @@ extern "C" int sushi_cuda_sgemm_row_sharded_host(sushi_cuda_ctx* ctx, int dev, i
         SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->copy_out, cudaStreamNonBlocking));
         for (cudaEvent_t& e : d->pipe_events) SC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
-    cudaEvent_t* ev = d->pipe_events;          // [0] start, [1..4] chunk uploaded, [5..8] chunk multiplied, [9] all downloaded
-    if ((rc = ensure_events(ctx, 2)) != SUSHI_CUDA_OK) return rc;
+    cudaEvent_t* ev = d->pipe_events;          // [0] start, [1..8] chunk uploaded, [9..16] chunk multiplied, [17] all downloaded
     SC_CUDA(ctx, cudaEventRecord(ev[0], d->stream));
     SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_in, ev[0], 0));      // after everything queued before this call
     SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[0], 0));
 
-    // ---- B: this rank's k rows go up, the others' arrive over the interconnect.  That needs B stored k x n with
-    // dense rows (a share is then one contiguous run); otherwise every rank uploads all of B.
+    // ---- plan (everything that decides which collectives run is a function of what all ranks share)
+    // B: this rank's k rows go up, the others' arrive over the interconnect.  That needs B stored k x n with dense
+    // rows (a share is then one contiguous run); otherwise every rank uploads all of B.  Each share travels in
+    // `pieces` sub-shares so that the first row chunk can start multiplying against the first sub-shares while the
+    // later ones are still on their way up.
     const int64_t b_rows = trans_b ? n : k, b_cols = trans_b ? k : n;
     const bool exchange_b = nranks > 1 && !trans_b && ldb == n && k > 0;
+    const int64_t k_block = (k + nranks - 1) / nranks;
+    // pieces of about 2048 k rows: long enough for the panel GEMMs of the first chunk to run at speed
+    const int pieces = exchange_b ? (int)std::min<int64_t>(8, std::max<int64_t>(1, k_block / 2048)) : 1;
+    const int64_t piece_rows = ((k_block + pieces - 1) / pieces + 15) / 16 * 16;
+    if ((rc = ensure_events(ctx, (size_t)(2 * pieces + 1))) != SUSHI_CUDA_OK) return rc;
+    // A and C in row chunks of whole tiles
+    const bool upload_c = beta != 0.0f || ldc != n;
+    const int chunks = count >= 2048 ? 4 : 1;      // eight chunks measured slower (182 against 176 ms at 32768^3 on two GPUs)
+    int64_t per = (count + chunks - 1) / chunks;
+    per = (per + 255) / 256 * 256;
+    auto upload_chunk = [&](int i) -> int
+    {
+        const int64_t r0 = i * per, r1 = (r0 + per < count) ? r0 + per : count;
+        if (r1 > r0)
+        {
+            const int64_t rows = r1 - r0;
+            if (k > 0)
+            {
+                if (trans_a)
+                    SC_CUDA(ctx, cudaMemcpy2DAsync(a_local_dev + r0, (size_t)lda * sizeof(float), a_local_host + r0, (size_t)lda * sizeof(float),
+                                                   (size_t)rows * sizeof(float), (size_t)k, cudaMemcpyHostToDevice, d->copy_in));
+                else
+                    SC_CUDA(ctx, cudaMemcpyAsync(a_local_dev + r0 * lda, a_local_host + r0 * lda, (size_t)extent(rows, k, lda, 0, 1) * sizeof(float),
+                                                 cudaMemcpyHostToDevice, d->copy_in));
+            }
+            if (upload_c)
+                SC_CUDA(ctx, cudaMemcpyAsync(c_block_dev + r0 * ldc, c_block_host + r0 * ldc, (size_t)extent(rows, n, ldc, 0, 1) * sizeof(float),
+                                             cudaMemcpyHostToDevice, d->copy_in));
+        }
+        SC_CUDA(ctx, cudaEventRecord(ev[1 + i], d->copy_in));
+        return SUSHI_CUDA_OK;
+    };
+
+    // ---- copies and exchange: chunk 0 of A first, then B (piece by piece, each exchanged as soon as it is up), then the rest of A
+    if ((rc = upload_chunk(0)) != SUSHI_CUDA_OK) return rc;
     if (k > 0)
     {
         if (exchange_b)
         {
             int64_t k0, kc;
             sushi_cuda_partition(k, nranks, rank, &k0, &kc);
-            if (kc > 0)
-                SC_CUDA(ctx, cudaMemcpyAsync(b_dev + k0 * ldb, b_host + k0 * ldb, (size_t)kc * (size_t)n * sizeof(float),
-                                             cudaMemcpyHostToDevice, d->copy_in));
-            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[0], d->copy_in));
-            SC_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->slab_events[0], 0));
-            const int64_t block = (k + nranks - 1) / nranks;
-            if ((rc = gather_slab(ctx, b_dev, k, n, 0, block)) != SUSHI_CUDA_OK) return rc;
-            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[1], ctx->comm_stream));
-            SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[1], 0));
+            for (int s_i = 0; s_i < pieces; ++s_i)
+            {
+                const int64_t u0 = s_i * piece_rows, u1 = (s_i == pieces - 1) ? k_block : u0 + piece_rows;
+                const int64_t lo = u0 < kc ? u0 : kc, hi = u1 < kc ? u1 : kc;      // this rank's part of the piece
+                if (hi > lo)
+                    SC_CUDA(ctx, cudaMemcpyAsync(b_dev + (k0 + lo) * ldb, b_host + (k0 + lo) * ldb, (size_t)(hi - lo) * (size_t)n * sizeof(float),
+                                                 cudaMemcpyHostToDevice, d->copy_in));
+                SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[s_i], d->copy_in));
+                SC_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->slab_events[s_i], 0));
+                if ((rc = gather_slab(ctx, b_dev, k, n, u0, u1)) != SUSHI_CUDA_OK) return rc;
+                SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[pieces + s_i], ctx->comm_stream));
+            }
         }
         else
         {
             SC_CUDA(ctx, cudaMemcpyAsync(b_dev, b_host, (size_t)extent(b_rows, b_cols, ldb, 0, 1) * sizeof(float),
                                          cudaMemcpyHostToDevice, d->copy_in));
-            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[0], d->copy_in));
-            SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[0], 0));
+            SC_CUDA(ctx, cudaEventRecord(ctx->slab_events[pieces], d->copy_in));
         }
     }
+    for (int i = 1; i < chunks; ++i)
+        if ((rc = upload_chunk(i)) != SUSHI_CUDA_OK) return rc;
 
-    // ---- A and C in row chunks of whole tiles
-    const bool upload_c = beta != 0.0f || ldc != n;
-    int chunks = count >= 2048 ? 4 : 1;
-    int64_t per = (count + chunks - 1) / chunks;
-    per = (per + 255) / 256 * 256;
+    // ---- multiplication
     SlabReuse reuse;
-    // one kernel family for the whole block, chosen from what all ranks share (the largest block)
+    // one kernel family for the full-K chunks, chosen from what all ranks share (the largest block)
     {
         const int64_t block = (m + nranks - 1) / nranks;
         if (ctx->variant == SUSHI_GEMM_AUTO)
@@ -1649,29 +1686,49 @@ extern "C" int sushi_cuda_sgemm_row_sharded_host(sushi_cuda_ctx* ctx, int dev, i
         if (r1 <= r0) continue;
         const int64_t rows = r1 - r0;
         const size_t cc = (size_t)extent(rows, n, ldc, 0, 1) * sizeof(float);
-        if (k > 0)
-        {
-            if (trans_a)
-                SC_CUDA(ctx, cudaMemcpy2DAsync(a_local_dev + r0, (size_t)lda * sizeof(float), a_local_host + r0, (size_t)lda * sizeof(float),
-                                               (size_t)rows * sizeof(float), (size_t)k, cudaMemcpyHostToDevice, d->copy_in));
-            else
-                SC_CUDA(ctx, cudaMemcpyAsync(a_local_dev + r0 * lda, a_local_host + r0 * lda, (size_t)extent(rows, k, lda, 0, 1) * sizeof(float),
-                                             cudaMemcpyHostToDevice, d->copy_in));
-        }
-        if (upload_c)
-            SC_CUDA(ctx, cudaMemcpyAsync(c_block_dev + r0 * ldc, c_block_host + r0 * ldc, cc, cudaMemcpyHostToDevice, d->copy_in));
-        SC_CUDA(ctx, cudaEventRecord(ev[1 + i], d->copy_in));
         SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[1 + i], 0));
-        rc = run_gemm(ctx, *d, trans_a, trans_b, rows, n, k, alpha, trans_a ? a_local_dev + r0 : a_local_dev + r0 * lda, lda, 0,
-                      b_dev, ldb, 0, beta, c_block_dev + r0 * ldc, ldc, 0, 1, &reuse);
-        if (rc != SUSHI_CUDA_OK) return rc;
-        SC_CUDA(ctx, cudaEventRecord(ev[5 + i], d->stream));
-        SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[5 + i], 0));
+        if (i == 0 && exchange_b && pieces > 1)
+        {
+            // the first chunk is accumulated over the k ranges of the pieces in the order they arrive: piece s_i of
+            // every rank's share, i.e. nranks disjoint k ranges per piece
+            bool first_panel = true;
+            for (int s_i = 0; s_i < pieces; ++s_i)
+            {
+                SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[pieces + s_i], 0));
+                const int64_t u0 = s_i * piece_rows, u1 = (s_i == pieces - 1) ? k_block : u0 + piece_rows;
+                for (int o = 0; o < nranks; ++o)
+                {
+                    int64_t o0, oc;
+                    sushi_cuda_partition(k, nranks, o, &o0, &oc);
+                    const int64_t lo = u0 < oc ? u0 : oc, hi = u1 < oc ? u1 : oc;
+                    if (hi <= lo) continue;
+                    const int64_t ka = o0 + lo, kw = hi - lo;
+                    const float* a_panel = trans_a ? a_local_dev + ka * lda + r0 : a_local_dev + r0 * lda + ka;
+                    rc = run_gemm(ctx, *d, trans_a, trans_b, rows, n, kw, alpha, a_panel, lda, 0, b_dev + ka * ldb, ldb, 0,
+                                  first_panel ? beta : 1.0f, c_block_dev + r0 * ldc, ldc, 0, 1);
+                    if (rc != SUSHI_CUDA_OK) return rc;
+                    first_panel = false;
+                }
+            }
+        }
+        else
+        {
+            if (i == 0 && k > 0)
+                for (int s_i = 0; s_i < pieces; ++s_i) SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[pieces + s_i], 0));
+            rc = run_gemm(ctx, *d, trans_a, trans_b, rows, n, k, alpha, trans_a ? a_local_dev + r0 : a_local_dev + r0 * lda, lda, 0,
+                          b_dev, ldb, 0, beta, c_block_dev + r0 * ldc, ldc, 0, 1, &reuse);
+            if (rc != SUSHI_CUDA_OK) return rc;
+        }
+        SC_CUDA(ctx, cudaEventRecord(ev[9 + i], d->stream));
+        SC_CUDA(ctx, cudaStreamWaitEvent(d->copy_out, ev[9 + i], 0));
         SC_CUDA(ctx, cudaMemcpyAsync(c_block_host + r0 * ldc, c_block_dev + r0 * ldc, cc, cudaMemcpyDeviceToHost, d->copy_out));
     }
+    // a rank without rows still owes the main stream the arrival of B (the buffer is the caller's)
+    if (count == 0 && k > 0)
+        for (int s_i = 0; s_i < pieces; ++s_i) SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ctx->slab_events[pieces + s_i], 0));
     // the call completes on the caller's stream once the last download has
-    SC_CUDA(ctx, cudaEventRecord(ev[9], d->copy_out));
-    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[9], 0));
+    SC_CUDA(ctx, cudaEventRecord(ev[17], d->copy_out));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, ev[17], 0));
     return SUSHI_CUDA_OK;
 }
 

@@ -125,8 +125,11 @@ def main():
     # ---- host-buffer form: every rank uploads its rows of A and its share of B's k rows, the shares are exchanged
     # device to device, C's rows come back to the rank's host.  Even and uneven partitions of m and of k, beta != 0,
     # transposed A, and a transposed B (no exchange: every rank uploads all of it).
+    # Shares of 4096 k rows or more travel in pieces of ~2048 rows and the first row chunk is accumulated piece by piece.
     for (m, n, k, ta, tb, alpha, beta) in [(8192, 512, 1024, 0, 0, 1.0, 0.0), (4100, 256, 301, 0, 0, 1.5, 0.5),
-                                           (2048 * world, 384, 512, 1, 0, 1.0, 1.0), (3000, 320, 256, 0, 1, 1.0, 0.0)]:
+                                           (2048 * world, 384, 512, 1, 0, 1.0, 1.0), (3000, 320, 256, 0, 1, 1.0, 0.0),
+                                           (2304 * world, 256, 4200 * world, 0, 0, 1.5, 0.5),
+                                           (2050 * world, 256, 6144 * world + 5, 1, 0, 1.0, 0.0)]:
         a = full(41, k, m) if ta else full(41, m, k)
         b = full(42, n, k) if tb else full(42, k, n)
         c_in = full(43, m, n)
