@@ -129,13 +129,15 @@ def main():
     for (m, n, k, ta, tb, alpha, beta) in [(8192, 512, 1024, 0, 0, 1.0, 0.0), (4100, 256, 301, 0, 0, 1.5, 0.5),
                                            (2048 * world, 384, 512, 1, 0, 1.0, 1.0), (3000, 320, 256, 0, 1, 1.0, 0.0),
                                            (2304 * world, 256, 4200 * world, 0, 0, 1.5, 0.5),
-                                           (2050 * world, 256, 6144 * world + 5, 1, 0, 1.0, 0.0)]:
+                                           (2050 * world, 256, 6144 * world + 5, 1, 0, 1.0, 0.0),
+                                           (world - 1, 64, 48, 0, 0, 2.0, 0.0)]:      # fewer rows than ranks: the last rank owns none
         a = full(41, k, m) if ta else full(41, m, k)
         b = full(42, n, k) if tb else full(42, k, n)
         c_in = full(43, m, n)
         first, count = partition(m, world, rank)
         rows = max(count, 1)
-        a_local = (a[:, first:first + rows] if ta else a[first:first + rows]).contiguous()
+        lo = first if count else 0                          # a rank without rows still passes valid (unused) buffers
+        a_local = (a[:, lo:lo + rows] if ta else a[lo:lo + rows]).contiguous()
         ha = a_local.cpu().pin_memory()
         hb = torch.empty_like(b, device="cpu").pin_memory()
         k0, kc = partition(k, world, rank)
@@ -144,7 +146,7 @@ def main():
         else:
             hb.fill_(float("nan"))                           # only this rank's share of the k rows is valid on its host
             hb[k0:k0 + kc].copy_(b[k0:k0 + kc])
-        hc = c_in[first:first + rows].cpu().pin_memory()
+        hc = c_in[lo:lo + rows].cpu().pin_memory()
         da = torch.empty_like(a_local); db = torch.full_like(b, float("nan")); dc = torch.empty(rows, n, device=dev)
         ctx.set_gemm_variant(2 if m >= 1024 else 1)
         torch.cuda.synchronize(); dist.barrier()
