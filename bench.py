@@ -46,7 +46,10 @@ U24 = 2.0 ** -24
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture of that kernel on that workload).  A constant: the bench cannot read DRAM counters itself.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # tensor kernel, one launch of 4096^3 with beta != 0: 552.6 MB read + 51.9 MB written (ncu --set full, 2 launches)
+    "sgemm_4096_nn_nt_tn_tt": 604.5e6,
+}
 
 
 def log(*a):
@@ -666,7 +669,7 @@ def roofline_of(name, w, count_rows, t, peaks, steps):
     return {
         "bound": "tensor", "kernel": "sgemm_tc3x_kernel", "achieved": round(achieved, 2), "peak": round(peak_3x, 2),
         "unit": UNIT, "frac": round(achieved / peak_3x, 4), "traffic": traffic,
-        "traffic_source": "constant in bench.py from one ncu capture of this kernel on this workload" if traffic else None,
+        "traffic_source": "constant typed into bench.py from an ncu capture of this kernel on this workload (dram__bytes_read.sum + dram__bytes_write.sum per launch); not measured by this run" if traffic else None,
         "peak_source": f"{peaks['source']} bf16 {'sustained' if long_region else 'burst'} {bf16_peak} TFLOP/s / 2 (TF32 rate) / 3 (3xTF32)",
         "frac_of_nominal": round(achieved / (2250.0 / 6.0), 4),
         "avg_launch_ms": round(avg_gemm_ms, 4), "launches": t["gemm_launches"],
