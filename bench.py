@@ -863,9 +863,9 @@ def other_configs(h: Harness, peaks):
 
 
 def tf32_ceiling(h: Harness):
-    """Rate of the same tensor-core kernel when it issues ONE TF32 MMA per product instead of three (the
-    hi*hi term alone; the result is a TF32-accurate product, used for nothing else): the measured 1xTF32 ceiling of
-    this kernel on this GPU, whose third is the 3xTF32 ceiling the roofline fraction can be read against."""
+    """MMA rate of the same tensor-core kernel when it issues ONE TF32 MMA per product (the hi*hi term alone; a
+    TF32-accurate result, used for nothing else) and when it issues the regular three: what the tensor pipe is seen to
+    sustain on this GPU, to set beside the "bf16 peak / 2" assumed for the TF32 rate in the roofline denominator."""
     torch, ctx = h.torch, h.ctx
     if not hasattr(ctx, "sgemm_tf32_probe"):
         return None
@@ -888,7 +888,10 @@ def tf32_ceiling(h: Harness):
             ms = gemm_ms / max(1, gemm_launches)
             out[label] = {"kernel_ms": round(ms, 4), "mma_tflops": round(2.0 * n ** 3 * products / (ms * 1e-3) / 1e12, 1)}
         out["shape"] = f"{n}^3 NT"
-        out["ceiling_3xtf32_tflops"] = round(out["tf32_x1"]["mma_tflops"] / 3.0, 1)
+        out["tf32_mma_tflops_sustained"] = out["tf32_x3"]["mma_tflops"]
+        out["note"] = ("MMA work per second of the same kernel with one and with three MMAs per product; with one the kernel is "
+                       "bound by feeding its stages (same bytes per stage), so the three-product run is the measured lower bound of the "
+                       "TF32 tensor rate: compare it with the bf16 / 2 assumed by roofline.peak_source")
         del a, b, c
         torch.cuda.empty_cache()
         return out
