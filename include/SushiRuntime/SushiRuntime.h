@@ -301,6 +301,7 @@ namespace SushiRuntime
                         else
                         {
                             if (b.mirror) sushi_cuda_free(ctx_, 0, b.mirror);
+                            if (b.written) sushi_cuda_marker_destroy(ctx_, b.written);
                             sushi_cuda_host_free(ctx_, ptr);
                         }
                     }
@@ -329,16 +330,19 @@ namespace SushiRuntime
                     {
                         std::lock_guard<std::mutex> lock(mutex_);
                         ++round_;
+                        // uploads of this round may overtake its own operations, never those of earlier rounds
+                        // (which may still read the mirrors about to be refreshed)
+                        fence_status_ = sushi_cuda_upload_fence(ctx_, 0);
                     }
 
                     void* device_for_operation(void* ptr, bool contents, int* rc) override
                     {
                         std::lock_guard<std::mutex> lock(mutex_);
-                        int status = SUSHI_CUDA_OK;
+                        int status = fence_status_;
                         void* out = nullptr;
                         auto it = blocks_.find(ptr);
-                        if (it == blocks_.end()) status = SUSHI_CUDA_ERR_INVALID_ARG;
-                        else
+                        if (status == SUSHI_CUDA_OK && it == blocks_.end()) status = SUSHI_CUDA_ERR_INVALID_ARG;
+                        if (status == SUSHI_CUDA_OK)
                         {
                             Block& b = it->second;
                             if (b.strategy == Memory::AllocStrategy::DEVICE) out = ptr;
@@ -348,7 +352,7 @@ namespace SushiRuntime
                                 // the mirror is current when the device wrote it last (host image stale) or
                                 // when it was brought up in the current execute() round
                                 if (status == SUSHI_CUDA_OK && contents && !b.host_stale && b.valid_round != round_)
-                                    status = sushi_cuda_memcpy_h2d(ctx_, 0, b.mirror, ptr, b.bytes);
+                                    status = sushi_cuda_upload_ahead(ctx_, 0, b.mirror, ptr, b.bytes);
                                 if (status == SUSHI_CUDA_OK)
                                 {
                                     if (contents) b.valid_round = round_;
@@ -365,9 +369,18 @@ namespace SushiRuntime
                         std::lock_guard<std::mutex> lock(mutex_);
                         auto it = blocks_.find(ptr);
                         if (it == blocks_.end() || it->second.strategy == Memory::AllocStrategy::DEVICE) return;
-                        if (!it->second.host_stale) stale_.push_back(ptr);
-                        it->second.host_stale = true;
-                        it->second.valid_round = round_;
+                        Block& b = it->second;
+                        if (!b.host_stale) stale_.push_back(ptr);
+                        b.host_stale = true;
+                        b.valid_round = round_;
+                        // the point in the stream after which the mirror holds what this operation wrote; without
+                        // a marker the download is ordered behind everything queued (flush_to_host)
+                        if (!b.written && sushi_cuda_marker_create(ctx_, 0, &b.written) != SUSHI_CUDA_OK) b.written = nullptr;
+                        if (b.written && sushi_cuda_marker_record(ctx_, 0, b.written) != SUSHI_CUDA_OK)
+                        {
+                            sushi_cuda_marker_destroy(ctx_, b.written);
+                            b.written = nullptr;
+                        }
                     }
 
                     int flush_to_host() override
@@ -379,7 +392,11 @@ namespace SushiRuntime
                             auto it = blocks_.find(ptr);
                             if (it == blocks_.end() || !it->second.host_stale) continue;      // freed meanwhile
                             Block& b = it->second;
-                            if (status == SUSHI_CUDA_OK) status = sushi_cuda_memcpy_d2h(ctx_, 0, ptr, b.mirror, b.bytes);
+                            // each image comes down as soon as its last writer has finished, beside whatever
+                            // the device still has queued
+                            if (status == SUSHI_CUDA_OK)
+                                status = b.written ? sushi_cuda_download_behind(ctx_, 0, ptr, b.mirror, b.bytes, b.written)
+                                                   : sushi_cuda_memcpy_d2h(ctx_, 0, ptr, b.mirror, b.bytes);
                             b.host_stale = false;
                         }
                         stale_.clear();
@@ -394,8 +411,10 @@ namespace SushiRuntime
                         void* mirror;
                         std::uint64_t valid_round = 0;    ///< execute() round in which the mirror was last made current
                         bool host_stale = false;          ///< the device wrote the mirror after the host image
+                        sushi_cuda_marker* written = nullptr;   ///< stream position of the last device write
                     };
                     std::uint64_t round_ = 1;
+                    int fence_status_ = SUSHI_CUDA_OK;
                     std::vector<void*> stale_;
                     sushi_cuda_ctx* ctx_;
                     std::mutex mutex_;

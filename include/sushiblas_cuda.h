@@ -99,8 +99,8 @@ SUSHI_CUDA_API int sushi_cuda_inject_failure(sushi_cuda_ctx* ctx, int site, int 
 SUSHI_CUDA_API int sushi_cuda_set_gemm_variant(sushi_cuda_ctx* ctx, int variant);
 /* Number of kernels this context has launched so far (all devices). */
 SUSHI_CUDA_API int sushi_cuda_launch_count(sushi_cuda_ctx* ctx, int64_t* launches);
-/* Bytes this context has moved between host and device through sushi_cuda_memcpy_h2d / _d2h so far
- * (either pointer may be NULL).  The Engine's residency tests count PCIe crossings with it; the reference
+/* Bytes this context has moved between host and device through sushi_cuda_memcpy_h2d / _d2h and
+ * sushi_cuda_upload_ahead so far (either pointer may be NULL).  The Engine's residency tests count PCIe crossings with it; the reference
  * has no counterpart (its shared USM migrates pages without telling anyone).                          */
 SUSHI_CUDA_API int sushi_cuda_copy_bytes(sushi_cuda_ctx* ctx, uint64_t* h2d_bytes, uint64_t* d2h_bytes);
 
@@ -127,6 +127,26 @@ SUSHI_CUDA_API int sushi_cuda_memcpy_h2d(sushi_cuda_ctx* ctx, int dev, void* dst
 SUSHI_CUDA_API int sushi_cuda_memcpy_d2h(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes);
 SUSHI_CUDA_API int sushi_cuda_memcpy_d2d(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes);
 SUSHI_CUDA_API int sushi_cuda_memset(sushi_cuda_ctx* ctx, int dev, void* dst, int byte, size_t bytes);
+/* Uploads that overlap queued work (what the reference gets from shared-USM page migration running beside
+ * its kernels).  _ahead() copies pinned host memory on the context's upload stream and makes the device's
+ * stream wait for it, so everything enqueued afterwards sees the data while work enqueued earlier keeps
+ * running.  The upload stream itself only waits for the work that was queued at the last _fence(): call
+ * _fence() once nothing enqueued before it may still touch the destinations of the uploads that follow
+ * (the Engine does so at the start of every execute() round).                                        */
+SUSHI_CUDA_API int sushi_cuda_upload_fence(sushi_cuda_ctx* ctx, int dev);
+SUSHI_CUDA_API int sushi_cuda_upload_ahead(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes);
+/* Downloads that do not wait for unrelated work.  A marker names a point in the device's stream
+ * (_record(): everything enqueued so far).  _download_behind() copies to pinned host memory on the
+ * context's download stream as soon as the work before `after` has finished, whatever else is still
+ * queued behind it; the device's stream then waits for the copy, so sushi_cuda_sync() covers it and
+ * later work cannot overwrite the source under it.  The Engine records a marker after every operation
+ * that writes a SHARED/HOST tensor and downloads each written tensor behind its last marker.        */
+typedef struct sushi_cuda_marker sushi_cuda_marker;
+SUSHI_CUDA_API int sushi_cuda_marker_create(sushi_cuda_ctx* ctx, int dev, sushi_cuda_marker** marker);
+SUSHI_CUDA_API int sushi_cuda_marker_record(sushi_cuda_ctx* ctx, int dev, sushi_cuda_marker* marker);
+SUSHI_CUDA_API int sushi_cuda_marker_destroy(sushi_cuda_ctx* ctx, sushi_cuda_marker* marker);
+SUSHI_CUDA_API int sushi_cuda_download_behind(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes,
+                                              sushi_cuda_marker* after);
 
 /* ---- GEMM ---------------------------------------------------------------------------
  * C <- alpha * op(A) * op(B) + beta * C, row-major, op(X) = X or X^T.

@@ -56,6 +56,12 @@ SIGNATURES = {
     "sushi_cuda_memcpy_d2h": (_int, [_vp, _int, _vp, _vp, _sz]),
     "sushi_cuda_memcpy_d2d": (_int, [_vp, _int, _vp, _vp, _sz]),
     "sushi_cuda_memset": (_int, [_vp, _int, _vp, _int, _sz]),
+    "sushi_cuda_upload_fence": (_int, [_vp, _int]),
+    "sushi_cuda_upload_ahead": (_int, [_vp, _int, _vp, _vp, _sz]),
+    "sushi_cuda_marker_create": (_int, [_vp, _int, ctypes.POINTER(_vp)]),
+    "sushi_cuda_marker_record": (_int, [_vp, _int, _vp]),
+    "sushi_cuda_marker_destroy": (_int, [_vp, _vp]),
+    "sushi_cuda_download_behind": (_int, [_vp, _int, _vp, _vp, _sz, _vp]),
     "sushi_cuda_sgemm": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64,
                                 _f32, _vp, _i64]),
     "sushi_cuda_sgemm_strided_batched": (_int, [_vp, _int, _int, _int, _i64, _i64, _i64, _f32,
@@ -296,6 +302,30 @@ class SushiCuda:
 
     def memcpy_d2d(self, dst, src, nbytes: int, dev: int = 0):
         self._check(self.lib.sushi_cuda_memcpy_d2d(self._ctx, dev, _addr(dst), _addr(src), nbytes))
+
+    def upload_fence(self, dev: int = 0):
+        """Uploads issued with upload_ahead() from now on start after everything enqueued so far."""
+        self._check(self.lib.sushi_cuda_upload_fence(self._ctx, dev))
+
+    def upload_ahead(self, dst, src, nbytes: int, dev: int = 0):
+        """Host-to-device copy on the upload stream; work enqueued afterwards waits for it, earlier work does not."""
+        self._check(self.lib.sushi_cuda_upload_ahead(self._ctx, dev, _addr(dst), _addr(src), nbytes))
+
+    def marker_create(self, dev: int = 0) -> int:
+        m = _vp(None)
+        self._check(self.lib.sushi_cuda_marker_create(self._ctx, dev, ctypes.byref(m)))
+        return m.value
+
+    def marker_record(self, marker: int, dev: int = 0):
+        """The marker names the work enqueued on the device's stream so far."""
+        self._check(self.lib.sushi_cuda_marker_record(self._ctx, dev, marker))
+
+    def marker_destroy(self, marker: int):
+        self._check(self.lib.sushi_cuda_marker_destroy(self._ctx, marker))
+
+    def download_behind(self, dst, src, nbytes: int, marker: int, dev: int = 0):
+        """Device-to-host copy that starts once the work before `marker` is done; sync() covers it."""
+        self._check(self.lib.sushi_cuda_download_behind(self._ctx, dev, _addr(dst), _addr(src), nbytes, marker))
 
     def memset(self, dst, byte: int, nbytes: int, dev: int = 0):
         self._check(self.lib.sushi_cuda_memset(self._ctx, dev, _addr(dst), byte, nbytes))

@@ -43,6 +43,13 @@ struct DeviceState
     // host-buffer entry point: copy streams and events of the chunked upload / multiply / download pipeline
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t pipe_events[18] = {};
+    // uploads that run ahead of queued work: own stream, fence (work queued so far) and completion events
+    cudaStream_t ahead_stream = nullptr;
+    cudaEvent_t ahead_fence = nullptr, ahead_done = nullptr;
+    bool ahead_fenced = false;
+    // downloads that start as soon as their source is final: own stream and completion event
+    cudaStream_t behind_stream = nullptr;
+    cudaEvent_t behind_done = nullptr;
     void* trsm_buf = nullptr;             // TRSM: inverted diagonal blocks + one block row/column of temporaries
     size_t trsm_bytes = 0;
     void* group_buf = nullptr;            // device copy of the grouped-launch problem list
@@ -533,6 +540,11 @@ extern "C" int sushi_cuda_destroy(sushi_cuda_ctx* ctx)
         if (d.copy_in) { cudaStreamSynchronize(d.copy_in); cudaStreamDestroy(d.copy_in); }
         if (d.copy_out) { cudaStreamSynchronize(d.copy_out); cudaStreamDestroy(d.copy_out); }
         for (cudaEvent_t e : d.pipe_events) if (e) cudaEventDestroy(e);
+        if (d.ahead_stream) { cudaStreamSynchronize(d.ahead_stream); cudaStreamDestroy(d.ahead_stream); }
+        if (d.ahead_fence) cudaEventDestroy(d.ahead_fence);
+        if (d.ahead_done) cudaEventDestroy(d.ahead_done);
+        if (d.behind_stream) { cudaStreamSynchronize(d.behind_stream); cudaStreamDestroy(d.behind_stream); }
+        if (d.behind_done) cudaEventDestroy(d.behind_done);
         if (d.own_stream) cudaStreamDestroy(d.own_stream);
     }
     delete ctx;
@@ -717,6 +729,97 @@ extern "C" int sushi_cuda_memcpy_d2h(sushi_cuda_ctx* ctx, int dev, void* dst, co
 { return copy_async(ctx, dev, dst, src, bytes, cudaMemcpyDeviceToHost, "memcpy_d2h"); }
 extern "C" int sushi_cuda_memcpy_d2d(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes)
 { return copy_async(ctx, dev, dst, src, bytes, cudaMemcpyDeviceToDevice, "memcpy_d2d"); }
+
+static int ensure_ahead_stream(sushi_cuda_ctx* ctx, DeviceState* d)
+{
+    if (d->ahead_stream) return SUSHI_CUDA_OK;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaEventCreateWithFlags(&d->ahead_fence, cudaEventDisableTiming));
+    SC_CUDA(ctx, cudaEventCreateWithFlags(&d->ahead_done, cudaEventDisableTiming));
+    SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->ahead_stream, cudaStreamNonBlocking));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_upload_fence(sushi_cuda_ctx* ctx, int dev)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "upload_fence: bad context or device index");
+    int rc = ensure_ahead_stream(ctx, d);
+    if (rc != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaEventRecord(d->ahead_fence, d->stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->ahead_stream, d->ahead_fence, 0));
+    d->ahead_fenced = true;
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_upload_ahead(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "upload_ahead: bad context or device index");
+    if (bytes == 0) return SUSHI_CUDA_OK;
+    if (!dst || !src) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "upload_ahead: null pointer");
+    int rc = d->ahead_fenced ? SUSHI_CUDA_OK : sushi_cuda_upload_fence(ctx, dev);   // never ahead of everything
+    if (rc != SUSHI_CUDA_OK) return rc;
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d->ahead_stream));
+    // a wait takes the event's state at this call, so one event serves every upload
+    SC_CUDA(ctx, cudaEventRecord(d->ahead_done, d->ahead_stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, d->ahead_done, 0));
+    ctx->h2d_bytes += bytes;
+    return SUSHI_CUDA_OK;
+}
+
+// A marker is a CUDA event behind an opaque pointer.
+extern "C" int sushi_cuda_marker_create(sushi_cuda_ctx* ctx, int dev, sushi_cuda_marker** marker)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !marker) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "marker_create: bad context, device index or pointer");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    cudaEvent_t e = nullptr;
+    SC_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    *marker = reinterpret_cast<sushi_cuda_marker*>(e);
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_marker_record(sushi_cuda_ctx* ctx, int dev, sushi_cuda_marker* marker)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !marker) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "marker_record: bad context, device index or marker");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    SC_CUDA(ctx, cudaEventRecord(reinterpret_cast<cudaEvent_t>(marker), d->stream));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_marker_destroy(sushi_cuda_ctx* ctx, sushi_cuda_marker* marker)
+{
+    if (!ctx) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "marker_destroy: bad context");
+    if (marker) SC_CUDA(ctx, cudaEventDestroy(reinterpret_cast<cudaEvent_t>(marker)));
+    return SUSHI_CUDA_OK;
+}
+
+extern "C" int sushi_cuda_download_behind(sushi_cuda_ctx* ctx, int dev, void* dst, const void* src, size_t bytes,
+                                          sushi_cuda_marker* after)
+{
+    DeviceState* d = get_dev(ctx, dev);
+    if (!d || !after) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "download_behind: bad context, device index or marker");
+    if (bytes == 0) return SUSHI_CUDA_OK;
+    if (!dst || !src) return set_error(ctx, SUSHI_CUDA_ERR_INVALID_ARG, "download_behind: null pointer");
+    SC_CUDA(ctx, cudaSetDevice(d->device));
+    if (!d->behind_stream)
+    {
+        SC_CUDA(ctx, cudaEventCreateWithFlags(&d->behind_done, cudaEventDisableTiming));
+        SC_CUDA(ctx, cudaStreamCreateWithFlags(&d->behind_stream, cudaStreamNonBlocking));
+    }
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->behind_stream, reinterpret_cast<cudaEvent_t>(after), 0));
+    SC_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d->behind_stream));
+    // the device's stream joins the download: a sync of it covers the copy, and nothing enqueued later
+    // overwrites the source under it
+    SC_CUDA(ctx, cudaEventRecord(d->behind_done, d->behind_stream));
+    SC_CUDA(ctx, cudaStreamWaitEvent(d->stream, d->behind_done, 0));
+    ctx->d2h_bytes += bytes;
+    return SUSHI_CUDA_OK;
+}
 
 extern "C" int sushi_cuda_memset(sushi_cuda_ctx* ctx, int dev, void* dst, int byte, size_t bytes)
 {

@@ -632,6 +632,52 @@ def test_storage_calls_round_trip(ctx):
     ctx.free(d); ctx.free(d2); ctx.host_free(h)
 
 
+def test_uploads_ahead_of_and_downloads_behind_queued_work(ctx):
+    """upload_ahead / download_behind move data on streams of their own and are ordered against the device's
+    stream only where they must be.  Operands uploaded ahead are seen by the GEMM enqueued after them although a
+    long GEMM was queued before; a result downloaded behind its marker is complete at sync() although another
+    long GEMM was queued after the marker; work enqueued after the download does not overwrite its source under
+    it; the bytes are counted like those of the plain copies."""
+    import ctypes
+    m, n, k, big = 1024, 768, 512, 4096
+    cs = make_case(77, 0, 0, m, n, k, 1)
+
+    def pinned(arr):
+        ptr = ctx.host_alloc(arr.nbytes)
+        view = np.frombuffer((ctypes.c_float * arr.size).from_address(ptr), dtype=np.float32)
+        view[:] = arr.reshape(-1)
+        return ptr, view
+
+    pa, _ = pinned(cs["a"]); pb, _ = pinned(cs["b"])
+    pc, hc = pinned(np.full(m * n, np.nan, dtype=np.float32))
+    da = torch.empty(m * k, device="cuda"); db = torch.empty(k * n, device="cuda")
+    dc = torch.full((m * n,), float("nan"), device="cuda")
+    x = torch.randn(big * big, device="cuda"); z = torch.empty(big * big, device="cuda")
+    torch.cuda.synchronize()
+    up0, down0 = ctx.copy_bytes()
+    ctx.upload_fence()
+    ctx.sgemm(0, 0, big, big, big, 1.0, x, big, x, big, 0.0, z, big)       # the uploads run beside this one
+    ctx.upload_ahead(da, pa, cs["a"].nbytes)
+    ctx.upload_ahead(db, pb, cs["b"].nbytes)
+    ctx.sgemm(0, 0, m, n, k, 1.0, da, cs["lda"], db, cs["ldb"], 0.0, dc, n)
+    marker = ctx.marker_create()
+    ctx.marker_record(marker)
+    ctx.sgemm(0, 0, big, big, big, 1.0, x, big, x, big, 0.0, z, big)       # the download does not wait for this one
+    ctx.download_behind(pc, dc, m * n * 4, marker)
+    ctx.memset(dc, 0, m * n * 4)                                           # enqueued after the download
+    ctx.sync()
+    up1, down1 = ctx.copy_bytes()
+    assert (up1 - up0, down1 - down0) == (cs["a"].nbytes + cs["b"].nbytes, m * n * 4)
+    ref, absab = og.gemm_f64_np(0, 0, m, n, k, 1.0, cs["a"], cs["lda"], 0, cs["b"], cs["ldb"], 0, 0.0,
+                                np.zeros(m * n, dtype=np.float32), n, 0, 1)
+    r, _ = og.tolerance_ratio(og._view(hc.copy(), m, n, n, 0, 1), ref, absab, k, budget=BUDGET)
+    assert r <= 1.0, r
+    assert not dc.any().item()
+    ctx.marker_destroy(marker)
+    for ptr in (pa, pb, pc):
+        ctx.host_free(ptr)
+
+
 def test_injected_host_side_failures_are_reported_and_survivable(ctx):
     own = SushiCuda([0])                         # a context of its own: its scratch starts empty
     own.set_stream(torch.cuda.current_stream().cuda_stream)
