@@ -10,7 +10,7 @@
 //
 // A streams through the SM exactly once.  A warp owns 16 rows; lane (g = lane / 4, t = lane % 4)
 // fetches the float4 at k = 4 t (and 16 + 4 t) of rows g and g + 8 -- 64 contiguous bytes per row
-// and instruction -- four steps ahead with cp.async into a private ring in shared memory (its own
+// and instruction -- DEPTH steps ahead with cp.async into a private ring in shared memory (its own
 // copies only, so cp.async.wait_group is all the synchronisation the stream needs; the lookahead
 // runs on across row blocks, so the pipe never drains), and splits the values into hi / lo in
 // registers.  The MMA's k index is free to be permuted as long as both operands agree: step s of a
@@ -37,11 +37,14 @@ struct SkinnyArgs
     float act_param;
 };
 
-constexpr int SKINNY_THREADS = 256;
-constexpr int SKINNY_ROWS = (SKINNY_THREADS / 32) * 16;   // rows per CTA and row block
 constexpr int SKINNY_KC = 256;                            // k per shared-memory chunk of op(B)
 constexpr int SKINNY_KPP = SKINNY_KC / 2 + 1;             // float4 per column of the chunk (odd: conflict-free)
-constexpr int SKINNY_DEPTH = 4;                           // steps (32 k) of A in flight per lane
+// Two shapes of CTA (THREADS, CTAs per SM, DEPTH = steps of 32 k of A in flight per lane; a CTA's row block is
+// 16 rows per warp).  The kernel is bound by instruction issue and latency, not by HBM, so what counts is how many
+// warps an SM holds and that the row blocks fill the machine in a whole number of rounds:
+//   narrow: 256 threads, two CTAs per SM (16 warps per SM, up to 96 registers), DEPTH 4
+//   wide:   896 threads, one CTA per SM (28 warps per SM, 72 registers), DEPTH 3 (2 when op(B) has more than 16 columns)
+constexpr int SKINNY_THREADS_NARROW = 256, SKINNY_THREADS_WIDE = 896;
 
 __device__ __forceinline__ void skinny_cp_async16(uint32_t dst, const float* src, uint32_t src_bytes)
 {
@@ -51,12 +54,19 @@ __device__ __forceinline__ void skinny_cp_async_commit() { asm volatile("cp.asyn
 template <int N>
 __device__ __forceinline__ void skinny_cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
+// x = hi + lo with hi = rna_tf32(x), lo = rna_tf32(x - hi).  Round-to-nearest-away on the 13 dropped mantissa bits
+// is "add half an ulp to the magnitude bits, clear them" -- two integer instructions, the same bits as
+// cvt.rna.tf32.f32 for every finite x (a carry into the exponent is the correct rounding, up to infinity) and
+// measurably cheaper in this instruction-bound loop.  Where hi is not finite (x is, or rounds to, infinity; NaN)
+// lo is 0; a NaN keeps its bits (the carry could otherwise run into the sign of an all-ones payload).
 __device__ __forceinline__ void skinny_split(float x, uint32_t& hi, uint32_t& lo)
 {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const uint32_t xb = __float_as_uint(x);
+    hi = (xb + 0x1000u) & 0xffffe000u;
     const float r = x - __uint_as_float(hi);          // exact in fp32
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
-    if (!(fabsf(__uint_as_float(hi)) <= 3.402823466e+38f)) lo = 0u;   // inf / nan stay in the hi part only
+    lo = (__float_as_uint(r) + 0x1000u) & 0xffffe000u;
+    if (!(fabsf(x) < 0x1.ffep127f)) lo = 0u;          // 0x7f7ff000: the smallest magnitude that rounds to infinity
+    if (x != x) hi = xb;
 }
 
 __device__ __forceinline__ void skinny_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
@@ -65,23 +75,11 @@ __device__ __forceinline__ void skinny_mma(float (&d)[4], uint32_t a0, uint32_t 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Position of a lane in the CTA's flattened work: row block, k-chunk, 32-wide step inside the chunk.
-struct SkinnyCursor
-{
-    int64_t rb, k0;
-    int ko;
-    __device__ __forceinline__ void advance(int64_t k, int64_t rb_step)
-    {
-        ko += 32;
-        const int64_t kc = (k - k0) < SKINNY_KC ? (k - k0) : SKINNY_KC;
-        if (ko >= kc) { ko = 0; k0 += SKINNY_KC; if (k0 >= k) { k0 = 0; rb += rb_step; } }
-    }
-};
-
-template <int NB>                                    // blocks of 8 columns
-__global__ void __launch_bounds__(SKINNY_THREADS, 2)
+template <int NB, int SKINNY_THREADS, int SKINNY_DEPTH>       // NB: blocks of 8 columns
+__global__ void __launch_bounds__(SKINNY_THREADS, SKINNY_THREADS <= 256 ? 2 : 1)
 sgemm_skinny_kernel(const SkinnyArgs p)
 {
+    constexpr int SKINNY_ROWS = (SKINNY_THREADS / 32) * 16;   // rows per CTA and row block
     // dynamic shared memory: op(B) chunk [8 NB][KPP] float4, then the lanes' private ring [DEPTH][4][THREADS] float4
     extern __shared__ __align__(16) float4 skinny_smem[];
     float4* Bq = skinny_smem;
@@ -116,32 +114,53 @@ sgemm_skinny_kernel(const SkinnyArgs p)
             Bq[c * SKINNY_KPP + kp] = make_float4(__uint_as_float(h0), __uint_as_float(h1), __uint_as_float(l0), __uint_as_float(l1));
         }
     };
-    // this lane's four float4 of one step (rows g, g + 8; k halves 0, 16) into ring slot `slot`;
-    // rows or k beyond the matrix arrive as zeros
-    auto issue = [&](const SkinnyCursor& cur, int slot)
+    // The lane walks its CTA's work -- row blocks blockIdx.x, + gridDim.x, ..., each `steps` steps of 32 k -- twice:
+    // once DEPTH steps ahead, issuing copies, once consuming.  Both walks keep running pointers (source, ring slot)
+    // so that a step costs a handful of instructions besides the arithmetic: the kernel is bound by instruction
+    // throughput, not by HBM.
+    const int steps = (int)((p.k + 31) / 32);
+    const int k_lane = (int)p.k - 4 * tig;               // a float4 at k offset x of this lane is inside iff x < k_lane
+    const int64_t lda8 = 8 * p.lda;
+    constexpr uint32_t SLOT_BYTES = 4u * SKINNY_THREADS * 16u;
+    const uint32_t ring_end = ring_addr + SKINNY_DEPTH * SLOT_BYTES;
+
+    int64_t a_rb = blockIdx.x;                           // walk ahead: row block, step, source of (row g, this step)
+    int a_s = 0;
+    uint32_t a_dst = ring_addr;
+    const float* a_src = A;
+    bool a_ok0 = false, a_ok1 = false;
+    auto ahead_enter_block = [&]()
     {
-        if (cur.rb < p.row_blocks)
+        const int64_t row0 = a_rb * SKINNY_ROWS + lane_row;
+        const bool live = a_rb < p.row_blocks;
+        a_ok0 = live && row0 < p.m;
+        a_ok1 = live && row0 + 8 < p.m;
+        a_src = A + (a_ok0 ? row0 : 0) * p.lda + 4 * tig;
+    };
+    // this lane's four float4 of one step (rows g, g + 8; k halves 0, 16) into the ring slot at a_dst; rows or k
+    // beyond the matrix arrive as zeros; one group per step, empty past the end
+    auto issue = [&]()
+    {
+        const int kk = 32 * a_s;
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
         {
-            const int64_t row0 = cur.rb * SKINNY_ROWS + lane_row;
-            const int64_t kk = cur.k0 + cur.ko + 4 * tig;
-            const float* src = A + row0 * p.lda + kk;
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int q = 0; q < 2; ++q)
-                {
-                    const bool ok = (row0 + 8 * h < p.m) && (kk + 16 * q < p.k);
-                    skinny_cp_async16(ring_addr + (uint32_t)((slot * 4 + h * 2 + q) * SKINNY_THREADS) * 16u,
-                                      ok ? src + 8 * h * p.lda + 16 * q : A, ok ? 16u : 0u);
-                }
+            const bool kin = kk + 16 * q < k_lane;
+            const bool ok0 = a_ok0 && kin, ok1 = a_ok1 && kin;
+            skinny_cp_async16(a_dst + (uint32_t)(q * SKINNY_THREADS) * 16u, ok0 ? a_src + 16 * q : A, ok0 ? 16u : 0u);
+            skinny_cp_async16(a_dst + (uint32_t)((2 + q) * SKINNY_THREADS) * 16u, ok1 ? a_src + lda8 + 16 * q : A, ok1 ? 16u : 0u);
         }
-        skinny_cp_async_commit();                     // one group per step, empty past the end
+        skinny_cp_async_commit();
+        a_dst += SLOT_BYTES;
+        if (a_dst == ring_end) a_dst = ring_addr;
+        a_src += 32;
+        if (++a_s == steps) { a_s = 0; a_rb += gridDim.x; ahead_enter_block(); }
     };
 
     const bool single_chunk = p.k <= SKINNY_KC;          // then op(B) is prepared once per CTA
-    SkinnyCursor ahead{(int64_t)blockIdx.x, 0, 0};
+    ahead_enter_block();
 #pragma unroll
-    for (int d = 0; d < SKINNY_DEPTH; ++d) { issue(ahead, d); ahead.advance(p.k, gridDim.x); }
+    for (int d = 0; d < SKINNY_DEPTH; ++d) issue();
     if (single_chunk) { load_b_chunk(0); __syncthreads(); }
 
     float acc[NB][4];
@@ -149,13 +168,15 @@ sgemm_skinny_kernel(const SkinnyArgs p)
     for (int j = 0; j < NB; ++j) { acc[j][0] = 0.f; acc[j][1] = 0.f; acc[j][2] = 0.f; acc[j][3] = 0.f; }
     const bool vec_c = ((p.ldc & 1) == 0) && ((p.stride_c & 1) == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 7) == 0);
 
-    int slot = 0;
-    for (SkinnyCursor cur{(int64_t)blockIdx.x, 0, 0}; cur.rb < p.row_blocks;)
+    const float4* c_ring = ring + t;                     // consuming walk: ring slot, row block, step
+    const float4* const c_ring_end = c_ring + SKINNY_DEPTH * 4 * SKINNY_THREADS;
+    int c_s = 0;
+    for (int64_t c_rb = blockIdx.x; c_rb < p.row_blocks;)
     {
-        if (!single_chunk && cur.ko == 0)
+        if (!single_chunk && (c_s & 7) == 0)
         {
             __syncthreads();                          // the previous chunk has been read by everyone
-            load_b_chunk(cur.k0);
+            load_b_chunk((int64_t)(c_s >> 3) * SKINNY_KC);
             __syncthreads();
         }
         skinny_cp_async_wait<SKINNY_DEPTH - 1>();     // the oldest step of this lane has landed
@@ -163,12 +184,12 @@ sgemm_skinny_kernel(const SkinnyArgs p)
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int q = 0; q < 2; ++q) av[h][q] = ring[(slot * 4 + h * 2 + q) * SKINNY_THREADS + t];
-        issue(ahead, slot);                           // refill the slot just read
-        ahead.advance(p.k, gridDim.x);
-        slot = (slot + 1) % SKINNY_DEPTH;
+            for (int q = 0; q < 2; ++q) av[h][q] = c_ring[(h * 2 + q) * SKINNY_THREADS];
+        c_ring += 4 * SKINNY_THREADS;
+        if (c_ring == c_ring_end) c_ring = ring + t;
+        issue();                                      // refill the slot just read
 
-        const float4* bq_lane = Bq + gid * SKINNY_KPP + (cur.ko >> 1) + 2 * tig;
+        const float4* bq_lane = Bq + gid * SKINNY_KPP + 16 * (c_s & 7) + 2 * tig;
 #pragma unroll
         for (int q = 0; q < 2; ++q)
         {
@@ -195,9 +216,10 @@ sgemm_skinny_kernel(const SkinnyArgs p)
                 }
             }
         }
-        const int64_t rb_done = cur.rb;
-        cur.advance(p.k, gridDim.x);
-        if (cur.rb == rb_done) continue;              // more k of the same rows to come
+        if (++c_s < steps) continue;                  // more k of the same rows to come
+        const int64_t rb_done = c_rb;
+        c_s = 0;
+        c_rb += gridDim.x;
 
         // the row block is complete: a lane holds columns 2t, 2t+1 of rows g and g + 8 in every block
         const int64_t row0 = rb_done * SKINNY_ROWS + lane_row;
@@ -244,33 +266,55 @@ sgemm_skinny_kernel(const SkinnyArgs p)
 // Shapes this kernel serves: op(A) = A (k contiguous) readable with aligned 128-bit loads, few columns, many rows.
 inline bool skinny_eligible(int ta, int64_t m, int64_t n, int64_t k, const float* a, int64_t lda, int64_t stride_a)
 {
-    return !ta && n >= 1 && n <= 32 && m >= 2048 && k >= 32 && (k % 4) == 0 && (lda % 4) == 0 && (stride_a % 4) == 0 &&
+    return !ta && n >= 1 && n <= 32 && m >= 2048 && k >= 32 && k <= (int64_t(1) << 30) && (k % 4) == 0 && (lda % 4) == 0 && (stride_a % 4) == 0 &&
            (reinterpret_cast<uintptr_t>(a) & 15) == 0;
 }
 
-template <int NB>
+template <int NB, int THREADS, int DEPTH>
 inline cudaError_t launch_sgemm_skinny_inst(const SkinnyArgs& p, dim3 grid, cudaStream_t st)
 {
-    const size_t smem = sizeof(float4) * (8 * NB * SKINNY_KPP + SKINNY_DEPTH * 4 * SKINNY_THREADS);
-    cudaError_t e = cudaFuncSetAttribute(sgemm_skinny_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = sizeof(float4) * (8 * NB * SKINNY_KPP + DEPTH * 4 * THREADS);
+    cudaError_t e = cudaFuncSetAttribute(sgemm_skinny_kernel<NB, THREADS, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    sgemm_skinny_kernel<NB><<<grid, SKINNY_THREADS, smem, st>>>(p);
+    sgemm_skinny_kernel<NB, THREADS, DEPTH><<<grid, THREADS, smem, st>>>(p);
     return cudaGetLastError();
 }
 
-inline cudaError_t launch_sgemm_skinny(SkinnyArgs p, int64_t batch, int sm_count, cudaStream_t st)
+// Rounds the SMs need for `rows * batch` rows when an SM holds `rows_per_sm` of them at a time.
+inline int64_t skinny_rounds(int64_t m, int64_t batch, int rows_per_cta, int ctas_per_sm, int sm_count)
+{
+    const int64_t blocks = ((m + rows_per_cta - 1) / rows_per_cta) * batch;
+    const int64_t slots = (int64_t)sm_count * ctas_per_sm;
+    return (blocks + slots - 1) / slots;
+}
+
+inline cudaError_t launch_sgemm_skinny(SkinnyArgs p, int64_t batch, int sm_count, cudaStream_t st, int shape = 0)
 {
     if (batch <= 0 || batch > 65535) return cudaErrorInvalidValue;
-    p.row_blocks = (p.m + SKINNY_ROWS - 1) / SKINNY_ROWS;
+    constexpr int ROWS_N = SKINNY_THREADS_NARROW / 32 * 16, ROWS_W = SKINNY_THREADS_WIDE / 32 * 16;
+    // a round of the wide shape holds 28 warps per SM against 16: it wins when it does not need more rounds per
+    // row than the narrow one, i.e. when the rows keep its larger blocks busy (shape: 1 narrow, 2 wide, 0 by this rule)
+    const int64_t work_n = skinny_rounds(p.m, batch, ROWS_N, 2, sm_count) * 2 * ROWS_N;
+    const int64_t work_w = skinny_rounds(p.m, batch, ROWS_W, 1, sm_count) * ROWS_W;
+    const bool wide = shape ? shape == 2 : work_w <= work_n;
+    const int rows = wide ? ROWS_W : ROWS_N;
+    p.row_blocks = (p.m + rows - 1) / rows;
     int64_t gx = p.row_blocks;
-    const int64_t cap = ((int64_t)sm_count * 2 + batch - 1) / batch;      // two CTAs per SM, grid-stride over the rest
+    const int64_t cap = ((int64_t)sm_count * (wide ? 1 : 2) + batch - 1) / batch;   // co-resident CTAs, grid-stride over the rest
     if (gx > cap) gx = cap > 0 ? cap : 1;
     const dim3 grid((unsigned)gx, (unsigned)batch);
     const int nb = (int)((p.n + 7) / 8);
-    if (nb == 1) return launch_sgemm_skinny_inst<1>(p, grid, st);
-    if (nb == 2) return launch_sgemm_skinny_inst<2>(p, grid, st);
-    if (nb == 3) return launch_sgemm_skinny_inst<3>(p, grid, st);
-    return launch_sgemm_skinny_inst<4>(p, grid, st);
+    if (wide)
+    {
+        if (nb == 1) return launch_sgemm_skinny_inst<1, SKINNY_THREADS_WIDE, 3>(p, grid, st);
+        if (nb == 2) return launch_sgemm_skinny_inst<2, SKINNY_THREADS_WIDE, 3>(p, grid, st);
+        if (nb == 3) return launch_sgemm_skinny_inst<3, SKINNY_THREADS_WIDE, 2>(p, grid, st);
+        return launch_sgemm_skinny_inst<4, SKINNY_THREADS_WIDE, 2>(p, grid, st);
+    }
+    if (nb == 1) return launch_sgemm_skinny_inst<1, SKINNY_THREADS_NARROW, 4>(p, grid, st);
+    if (nb == 2) return launch_sgemm_skinny_inst<2, SKINNY_THREADS_NARROW, 4>(p, grid, st);
+    if (nb == 3) return launch_sgemm_skinny_inst<3, SKINNY_THREADS_NARROW, 4>(p, grid, st);
+    return launch_sgemm_skinny_inst<4, SKINNY_THREADS_NARROW, 4>(p, grid, st);
 }
 
 } // namespace sushi

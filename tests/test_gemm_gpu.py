@@ -765,6 +765,44 @@ def test_tall_and_skinny_products(ctx, tb):
     check(ctx, AUTO, 0, tb, 2048, 16, 64, 1.0, 0.0, seed=851, poison_c=True)     # beta == 0: C is not read
     # unaligned leading dimension of A: the tiled kernel serves it, same answer class
     check(ctx, AUTO, 0, tb, 2100, 16, 64, 1.0, 0.5, pad=(1, 0, 0), seed=852)
+    # row counts that fill one round of the 28-warp CTA shape (448 rows per CTA, one CTA per SM) take that shape:
+    # every column count class, a ragged last row block, ragged and multi-chunk k, batches
+    for (m, n, k, batch) in [(66000, 16, 256, 1), (66001, 5, 100, 1), (66300, 32, 516, 1), (65536, 24, 132, 1),
+                             (33000, 17, 260, 2)]:
+        check(ctx, AUTO, 0, tb, m, n, k, 1.5, 0.5, batch=batch, seed=860 + n)
+
+
+@pytest.mark.parametrize("m", [4096, 66000])
+def test_tall_and_skinny_non_finite_and_huge_inputs(ctx, m):
+    """The streaming kernel rounds with integer arithmetic on the bit patterns, so the patterns that are not
+    ordinary numbers get their own treatment.  Rows holding such values stay contained: an infinity or a NaN makes its own row of C non-finite (3xTF32 multiplies the
+    infinity by both parts of the other factor, so the row holds infinities of the right sign and NaNs; never a
+    finite number), 2^120 and 3e38 give finite, accurate results, and every other row is untouched."""
+    n, k = 16, 256
+    a = og.uniform_pm1(870, m * k).reshape(m, k).copy()
+    b = (np.abs(og.uniform_pm1(871, k * n)) * 0.5 + 0.25).astype(np.float32).reshape(k, n)
+    nan = np.array([0x7fffffff], dtype=np.uint32).view(np.float32)[0]
+    special = {0: np.float32(np.inf), 1: np.float32(-np.inf), 2: nan, 3: np.float32(2.0 ** 120), 4: np.float32(3e38)}
+    base = m - 40                                            # the last, ragged row block for m = 66000
+    for i, v in special.items():
+        a[base + 5 * i, 3 + 17 * i] = v
+    c = torch.full((m * n,), float("nan"), device="cuda")
+    ctx.sgemm(0, 0, m, n, k, 1.0, dev(a.reshape(-1)), k, dev(b.reshape(-1)), n, 0.0, c, n)
+    ctx.sync()
+    got = c.cpu().numpy().reshape(m, n)
+    assert np.all((got[base] == np.inf) | np.isnan(got[base]))
+    assert np.all((got[base + 5] == -np.inf) | np.isnan(got[base + 5]))
+    assert np.all(np.isnan(got[base + 10]))
+    with np.errstate(over="ignore", invalid="ignore"):
+        ref = a.astype(np.float64) @ b.astype(np.float64)
+        absab = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    for row in (base + 15, base + 20):                       # huge but finite: as accurate as any other row
+        assert np.all(np.isfinite(got[row])), row
+        assert np.all(np.abs(got[row] - ref[row]) <= BUDGET * 8 * k * 2.0 ** -24 * absab[row]), row
+    plain = np.ones(m, dtype=bool)
+    plain[[base + 5 * i for i in special]] = False
+    r, _ = og.tolerance_ratio(got[plain][None], ref[plain][None], absab[plain][None], k, budget=BUDGET)
+    assert r <= 1.0, r
 
 
 def test_split_inside_the_kernel_equals_pre_split_planes(ctx):
