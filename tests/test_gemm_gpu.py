@@ -772,23 +772,27 @@ def test_tall_and_skinny_products(ctx, tb):
         check(ctx, AUTO, 0, tb, m, n, k, 1.5, 0.5, batch=batch, seed=860 + n)
 
 
-@pytest.mark.parametrize("m", [4096, 66000])
-def test_tall_and_skinny_non_finite_and_huge_inputs(ctx, m):
-    """The streaming kernel rounds with integer arithmetic on the bit patterns, so the patterns that are not
-    ordinary numbers get their own treatment.  Rows holding such values stay contained: an infinity or a NaN makes its own row of C non-finite (3xTF32 multiplies the
-    infinity by both parts of the other factor, so the row holds infinities of the right sign and NaNs; never a
-    finite number), 2^120 and 3e38 give finite, accurate results, and every other row is untouched."""
-    n, k = 16, 256
+@pytest.mark.parametrize("variant,m,n", [(AUTO, 4096, 16), (AUTO, 66000, 16), (TC3X, 768, 512), (TC3X, 4096, 2304)])
+def test_non_finite_and_huge_inputs_stay_in_their_rows(ctx, variant, m, n):
+    """Infinities, NaNs and values near the top of the range in A, on the 3xTF32 paths: both CTA shapes of the
+    streaming kernel (which rounds with integer arithmetic on the bit patterns), the tensor kernel splitting
+    inside the kernel (small problem) and behind the pre-pass (large one).  An infinity or a NaN makes its own row
+    of C non-finite (3xTF32 multiplies the infinity by both parts of the other factor, so the row holds infinities
+    of the right sign and NaNs; never a finite number), 2^120 and 3e38 give finite, accurate results, and every
+    other row is untouched.  B is positive."""
+    k = 256
     a = og.uniform_pm1(870, m * k).reshape(m, k).copy()
     b = (np.abs(og.uniform_pm1(871, k * n)) * 0.5 + 0.25).astype(np.float32).reshape(k, n)
     nan = np.array([0x7fffffff], dtype=np.uint32).view(np.float32)[0]
     special = {0: np.float32(np.inf), 1: np.float32(-np.inf), 2: nan, 3: np.float32(2.0 ** 120), 4: np.float32(3e38)}
-    base = m - 40                                            # the last, ragged row block for m = 66000
+    base = m - 40                                            # for m = 66000: inside the last, ragged row block
     for i, v in special.items():
         a[base + 5 * i, 3 + 17 * i] = v
     c = torch.full((m * n,), float("nan"), device="cuda")
+    ctx.set_gemm_variant(variant)
     ctx.sgemm(0, 0, m, n, k, 1.0, dev(a.reshape(-1)), k, dev(b.reshape(-1)), n, 0.0, c, n)
     ctx.sync()
+    ctx.set_gemm_variant(AUTO)
     got = c.cpu().numpy().reshape(m, n)
     assert np.all((got[base] == np.inf) | np.isnan(got[base]))
     assert np.all((got[base + 5] == -np.inf) | np.isnan(got[base + 5]))
