@@ -104,7 +104,9 @@ struct Params
     int64_t ldc, stride_c;
     int32_t num_kb;
     int32_t tiles_m, tiles_n;
-    int64_t total_tiles;           // tiles_m * tiles_n * batch
+    int64_t total_tiles;           // tiles_per_mat * batch
+    int64_t tiles_per_mat;         // tiles_m * tiles_n, or the tiles of the written triangle (tri_compact)
+    int32_t tri_compact;           // 1: tile numbers run over the tiles of the triangle only (square tile grid)
     float alpha, beta;
     int32_t act;                   // epilogue activation (ACT_* of activation.cuh) applied to alpha*acc + beta*C
     float act_param;               // its parameter (leaky_relu, elu)
@@ -344,12 +346,23 @@ constexpr uint32_t IDESC_TF32_M128_N256 =
 
 struct TileCoord { int64_t bi; int32_t tm, tn; };
 
-__device__ __forceinline__ TileCoord decode_tile(int64_t t, int32_t tiles_m, int32_t tiles_n)
+__device__ __forceinline__ TileCoord decode_tile(int64_t t, const Params& p)
 {
-    const int64_t per = (int64_t)tiles_m * tiles_n;
     TileCoord tc;
-    tc.bi = t / per;
-    const int32_t r = (int32_t)(t % per);
+    tc.bi = t / p.tiles_per_mat;
+    const int32_t r = (int32_t)(t % p.tiles_per_mat);
+    if (p.tri_compact)
+    {
+        // r-th tile of the triangle, row by row: row i holds tiles (i, 0 .. i), i (i + 1) / 2 tiles before it
+        int32_t i = (int32_t)((sqrtf(8.0f * (float)r + 1.0f) - 1.0f) * 0.5f);
+        while ((i + 1) * (i + 2) / 2 <= r) ++i;
+        while (i * (i + 1) / 2 > r) --i;
+        const int32_t j = r - i * (i + 1) / 2;
+        tc.tm = p.tri == 1 ? i : j;                  // lower: column <= row; upper: the mirror image
+        tc.tn = p.tri == 1 ? j : i;
+        return tc;
+    }
+    const int32_t tiles_m = p.tiles_m, tiles_n = p.tiles_n;
     const int32_t group = GROUP_M * tiles_n;
     const int32_t gid = r / group;
     const int32_t first_m = gid * GROUP_M;
@@ -519,7 +532,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         WorkItem w;
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
-            const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+            const TileCoord tc = decode_tile(w.tile, p);
             if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
             for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
             {
@@ -580,7 +593,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
             {
-                const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+                const TileCoord tc = decode_tile(w.tile, p);
                 if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
             }
             const uint32_t tl_now = tl++;
@@ -656,7 +669,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
             {
-                const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+                const TileCoord tc = decode_tile(w.tile, p);
                 if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
             }
             for (int32_t kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it)
@@ -731,7 +744,7 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         WorkItem w;
         for (int32_t idx = 0; ok && get_work_item(p, cta, grid, idx, w); ++idx)
         {
-            const TileCoord tc = decode_tile(w.tile, p.tiles_m, p.tiles_n);
+            const TileCoord tc = decode_tile(w.tile, p);
             if (tile_outside_triangle(p.tri, tc.tm, tc.tn)) continue;
             const uint32_t tl_now = tl++;
             int okl = mbar_wait_bounded(acc_full, tl_now & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, WAIT_LIMIT_NS);
@@ -1165,9 +1178,16 @@ inline size_t sk_area_bytes(const TailPlan& t)
     return slots ? SK_FLAG_BYTES + slots * (SK_SLOT_FLOATS * sizeof(float)) : 0;
 }
 
-inline void tile_counts(int64_t m, int64_t n, int64_t k, int64_t batch, int64_t* tiles, int64_t* num_kb)
+// Work items of a problem: tiles (of the written triangle only when `tri` and the tile grid is square, which is
+// what SYRK gives: dealing the tiles outside it too would leave the CTAs that drew them idle) and k-blocks.
+inline bool triangle_is_compact(int64_t m, int64_t n, int tri)
 {
-    *tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * batch;
+    return tri != 0 && BM == BN && (m + BM - 1) / BM == (n + BN - 1) / BN;
+}
+inline void tile_counts(int64_t m, int64_t n, int64_t k, int64_t batch, int tri, int64_t* tiles, int64_t* num_kb)
+{
+    const int64_t tm = (m + BM - 1) / BM, tn = (n + BN - 1) / BN;
+    *tiles = (triangle_is_compact(m, n, tri) ? tm * (tm + 1) / 2 : tm * tn) * batch;
     *num_kb = (k + BK - 1) / BK;
 }
 
@@ -1261,7 +1281,9 @@ inline cudaError_t launch_sgemm_tc3x(const OperandSource& a, const OperandSource
     p.c = c; p.m = m; p.n = n; p.ldc = ldc; p.stride_c = stride_c;
     p.num_kb = (int32_t)num_kb;
     p.tiles_m = (int32_t)(m_pad / BM); p.tiles_n = (int32_t)(n_pad / BN);
-    p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
+    p.tri_compact = triangle_is_compact(m, n, tri) ? 1 : 0;
+    p.tiles_per_mat = p.tri_compact ? (int64_t)p.tiles_m * (p.tiles_m + 1) / 2 : (int64_t)p.tiles_m * p.tiles_n;
+    p.total_tiles = p.tiles_per_mat * batch;
     p.alpha = alpha; p.beta = beta; p.status = status; p.act = act; p.act_param = act_param; p.tri = tri;
     p.lean_epilogue = 1;
     const TailPlan plan = plan_tail(p.total_tiles, num_kb, sm_count, sk_area != nullptr && sk_epoch != 0);

@@ -329,7 +329,7 @@ int run_gemm(sushi_cuda_ctx* ctx, DeviceState& d, int ta, int tb, int64_t m, int
         void* sk_area = nullptr;
         {
             int64_t tiles = 0, num_kb = 0;
-            sushi::tc3x::tile_counts(m, n, k, batch, &tiles, &num_kb);
+            sushi::tc3x::tile_counts(m, n, k, batch, tri, &tiles, &num_kb);
             const size_t need = sushi::tc3x::sk_area_bytes(sushi::tc3x::plan_tail(tiles, num_kb, d.sm_count, true));
             if (need > d.sk_area_bytes)
             {

@@ -435,8 +435,9 @@ def test_reference_kat_syrk(ctx):
 def test_syrk_matches_oracle_and_leaves_the_other_triangle(ctx, variant):
     rng = np.random.default_rng(23)
     ctx.set_gemm_variant(variant)
+    # (2304, 136): 45 tiles of the triangle in a 9 x 9 tile grid -- the tensor kernel numbers only those
     for (n, k, batch, pad) in [(7, 5, 1, 0), (65, 33, 2, 3), (300, 260, 1, 4), (512, 384, 3, 0), (1024, 200, 1, 0),
-                                (257, 1000, 1, 1)]:
+                                (257, 1000, 1, 1), (2304, 136, 2, 0)]:
         for upper in (0, 1):
             for trans in (0, 1):
                 alpha, beta = float(rng.choice([1.0, 1.5])), float(rng.choice([0.0, 0.5, 1.0]))
