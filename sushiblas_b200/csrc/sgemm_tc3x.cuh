@@ -158,6 +158,38 @@ __device__ __forceinline__ bool get_work_item(const Params& p, int32_t cta, int3
     return true;
 }
 
+// Cooperative split-K finish of one warp: rows [q, q+1) * 256/S of a tile are the sum of the S published slots,
+// added in slot order.  The reads are L2 round trips, so what matters is how many are in flight: a lane fetches
+// sixteen float4 (16 / S positions of the band times S slots) before it adds the first, instead of S per position
+// (which made the finish of an S = 2 tile 32 dependent round trips per warp, 35 us of a 150 us GEMM).
+template <int S, typename Store>
+__device__ __forceinline__ void coop_finish_band(const float* slot0, size_t cstride, int q_idx, int ew, int lane, Store&& store)
+{
+    constexpr int BAND = 256 / S, ROWS_PER_WARP = BAND / 8, POSITIONS = ROWS_PER_WARP * 2;   // (row, column half) per lane
+    constexpr int GROUP = (16 / S) < POSITIONS ? (16 / S) : POSITIONS;
+    static_assert(POSITIONS % GROUP == 0, "whole groups");
+    for (int p0 = 0; p0 < POSITIONS; p0 += GROUP)
+    {
+        float4 t4[GROUP][S];
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g)
+        {
+            const int trow = q_idx * BAND + ew * ROWS_PER_WARP + ((p0 + g) >> 1), col4 = lane + 32 * ((p0 + g) & 1);
+            const float* src = slot0 + (size_t)trow * 256 + col4 * 4;
+#pragma unroll
+            for (int c = 0; c < S; ++c) t4[g][c] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)c * cstride));
+        }
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g)
+        {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int c = 0; c < S; ++c) { sum.x += t4[g][c].x; sum.y += t4[g][c].y; sum.z += t4[g][c].z; sum.w += t4[g][c].w; }
+            store(q_idx * BAND + ew * ROWS_PER_WARP + ((p0 + g) >> 1), lane + 32 * ((p0 + g) & 1), sum);
+        }
+    }
+}
+
 // Triangular output (SYRK): true when tile (tm, tn) lies wholly outside the triangle that is
 // written, so that every role skips the work item.
 __device__ __forceinline__ bool tile_outside_triangle(int32_t tri, int32_t tm, int32_t tn)
@@ -1000,73 +1032,58 @@ sgemm_tc3x_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                             ST_TIMEOUT_PARTIAL_FLAG, WAIT_LIMIT_NS) ? 1 : 0;
                 ok = __all_sync(0xffffffffu, okc) != 0;
                 if (!ok) break;
-                const int band = BM / p.sk_split, rows_per_warp = band / 8;      // S in {2, 4, 8, 16}
                 const float* slot0 = p.sk_partials + (size_t)t_idx * SK_SLOT_FLOATS;
                 const size_t cstride = (size_t)p.sk_tiles * SK_SLOT_FLOATS;
-                for (int i = 0; i < rows_per_warp; ++i)
+                // one float4 of the finished tile: row `trow` of the tile, columns 4 * col4 ..
+                auto finish_store = [&](int trow, int col4, const float4& sum)
                 {
-                    const int trow = q_idx * band + ew * rows_per_warp + i;      // row inside the tile
                     const int64_t grow = (int64_t)tc.tm * BM + trow;
-                    if (grow >= p.m) break;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
+                    const int64_t gcol = col_base + col4 * 4;
+                    if (grow >= p.m || gcol >= p.n) return;
+                    float* dst = cb + grow * p.ldc + gcol;
+                    const bool tri_all = p.tri == 0 || (p.tri == 1 ? gcol + 3 <= grow : gcol >= grow);
+                    if (vec_ok && gcol + 3 < p.n && tri_all)
                     {
-                        const int col4 = lane + 32 * half;
-                        const int64_t gcol = col_base + col4 * 4;
-                        const float* src = slot0 + (size_t)trow * BN + col4 * 4;
-                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int32_t c0 = 0; c0 < p.sk_split; c0 += 8)
+                        float4 o;
+                        o.x = p.alpha * sum.x; o.y = p.alpha * sum.y; o.z = p.alpha * sum.z; o.w = p.alpha * sum.w;
+                        if (has_beta)
                         {
-                            float4 t4[8];
-#pragma unroll
-                            for (int c = 0; c < 8; ++c)
-                                if (c0 + c < p.sk_split) t4[c] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(c0 + c) * cstride));
-#pragma unroll
-                            for (int c = 0; c < 8; ++c)
-                                if (c0 + c < p.sk_split) { sum.x += t4[c].x; sum.y += t4[c].y; sum.z += t4[c].z; sum.w += t4[c].w; }
+                            const float4 old = *reinterpret_cast<const float4*>(dst);
+                            o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
+                            o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
                         }
-                        if (gcol >= p.n) continue;
-                        float* dst = cb + grow * p.ldc + gcol;
-                        const bool tri_all = p.tri == 0 || (p.tri == 1 ? gcol + 3 <= grow : gcol >= grow);
-                        if (vec_ok && gcol + 3 < p.n && tri_all)
+                        if (p.act)
                         {
-                            float4 o;
-                            o.x = p.alpha * sum.x; o.y = p.alpha * sum.y; o.z = p.alpha * sum.z; o.w = p.alpha * sum.w;
-                            if (has_beta)
-                            {
-                                const float4 old = *reinterpret_cast<const float4*>(dst);
-                                o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
-                                o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
-                            }
-                            if (p.act)
-                            {
-                                o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
-                                o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
-                            }
-                            *reinterpret_cast<float4*>(dst) = o;
-                            for (int32_t peer = 0; peer < p.n_peers; ++peer)
-                                *reinterpret_cast<float4*>(p.peer_c[peer] + tc.bi * p.stride_c + grow * p.ldc + gcol) = o;
+                            o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
+                            o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
                         }
-                        else
-                        {
-                            const float av[4] = {sum.x, sum.y, sum.z, sum.w};
+                        *reinterpret_cast<float4*>(dst) = o;
+                        for (int32_t peer = 0; peer < p.n_peers; ++peer)
+                            *reinterpret_cast<float4*>(p.peer_c[peer] + tc.bi * p.stride_c + grow * p.ldc + gcol) = o;
+                    }
+                    else
+                    {
+                        const float av[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
+                        for (int j = 0; j < 4; ++j)
+                        {
+                            const bool inside = p.tri == 0 || (p.tri == 1 ? gcol + j <= grow : gcol + j >= grow);
+                            if (gcol + j < p.n && inside)
                             {
-                                const bool inside = p.tri == 0 || (p.tri == 1 ? gcol + j <= grow : gcol + j >= grow);
-                                if (gcol + j < p.n && inside)
-                                {
-                                    float o = p.alpha * av[j];
-                                    if (has_beta) o = fmaf(p.beta, dst[j], o);
-                                    o = apply_act(o, p.act, p.act_param);
-                                    dst[j] = o;
-                                    for (int32_t peer = 0; peer < p.n_peers; ++peer)
-                                        p.peer_c[peer][tc.bi * p.stride_c + grow * p.ldc + gcol + j] = o;
-                                }
+                                float o = p.alpha * av[j];
+                                if (has_beta) o = fmaf(p.beta, dst[j], o);
+                                o = apply_act(o, p.act, p.act_param);
+                                dst[j] = o;
+                                for (int32_t peer = 0; peer < p.n_peers; ++peer)
+                                    p.peer_c[peer][tc.bi * p.stride_c + grow * p.ldc + gcol + j] = o;
                             }
                         }
                     }
-                }
+                };
+                if (p.sk_split == 2) coop_finish_band<2>(slot0, cstride, q_idx, ew, lane, finish_store);
+                else if (p.sk_split == 4) coop_finish_band<4>(slot0, cstride, q_idx, ew, lane, finish_store);
+                else if (p.sk_split == 8) coop_finish_band<8>(slot0, cstride, q_idx, ew, lane, finish_store);
+                else coop_finish_band<16>(slot0, cstride, q_idx, ew, lane, finish_store);
                 if (p.n_peers > 0) __threadfence_system();
             }
         }
